@@ -1,0 +1,6 @@
+from .cache import PAGE_SIZE, Cache
+from .paged import KVView, PagedKVGroup
+from .slots import CacheError, SlotAllocator
+from .state import StateGroup
+
+__all__ = ["PAGE_SIZE", "Cache", "KVView", "PagedKVGroup", "CacheError", "SlotAllocator", "StateGroup"]

@@ -1,0 +1,105 @@
+"""The Python entry point: a model with its cache on one GPU.
+
+It mirrors the reference's Engine interface -- Infer / InferWithCallback / Close
+(internal/engine/types_base.go:17-21) with a SamplerConfig (types_base.go:7-15) --
+as generate() with SamplingParams, and adds what the reference lacks: batches of
+sequences, and the step function that both generation and trace replay drive.
+"""
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+from .. import architectures  # noqa: F401  (registers the architectures)
+from ..cache import Cache
+from ..config.registry import architecture_of, load_config
+from ..kernels import ops
+from ..parts.base import Runtime
+from ..weights import load_weights, random_weights
+from .model import Model
+from .step import run_step
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def _dtype(name) -> torch.dtype:
+    try:
+        return _DTYPES[name]
+    except KeyError:
+        raise ValueError(f"dtype must be 'bfloat16' or 'float32', found {name!r}") from None
+
+
+def _device(device) -> torch.device:
+    if not torch.cuda.is_available():
+        raise RuntimeError("longbow-quarrel_b200 runs on a CUDA GPU (sm_100a); none is visible. "
+                           "There is no CPU path.")
+    return torch.device(device)
+
+
+class Engine:
+    def __init__(self, arch, config, model: Model, cache: Cache, runtime: Runtime):
+        self.arch, self.config, self.model, self.cache, self.runtime = arch, config, model, cache, runtime
+        self.device = runtime.device
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def _build(cls, arch, config, tensors_fn, dtype, max_tokens, max_batch, max_context, device):
+        dtype, device = _dtype(dtype), _device(device)
+        spec = arch.describe(config)
+        max_context = min(max_context or spec.max_positions, spec.max_positions)
+        max_tokens = max_tokens or max_context
+        max_context = min(max_context, -(-max_tokens // 64) * 64)
+        runtime = Runtime(device=device, dtype=dtype, max_context=max_context)
+        ops.prepare(dtype)
+        with torch.cuda.device(device):
+            model = Model(spec, runtime)
+            tensors = tensors_fn(model.weight_table(), device)
+            model.load(tensors)
+            del tensors
+            cache = Cache(model.cache_needs(), max_tokens, max_context, dtype, device, max_slots=max_batch)
+        return cls(arch, config, model, cache, runtime)
+
+    @classmethod
+    def from_pretrained(cls, folder, dtype="bfloat16", max_tokens: int | None = None, max_batch: int | None = None,
+                        max_context: int | None = None, device="cuda:0") -> "Engine":
+        """A model folder (config.json + model.safetensors); the class is chosen by config.json."""
+        folder = Path(folder)
+        arch, config = load_config(folder)
+        return cls._build(arch, config, lambda table, dev: load_weights(folder, table, dev), dtype, max_tokens,
+                          max_batch, max_context, device)
+
+    @classmethod
+    def from_config(cls, config, seed: int = 0, dtype="bfloat16", max_tokens: int | None = None,
+                    max_batch: int | None = None, max_context: int | None = None, device="cuda:0",
+                    std: float = 0.02, gain_std: float = 0.0, weight_dtype=torch.bfloat16) -> "Engine":
+        """Random weights made on the device (a dict with config.json's keys, or a typed config)."""
+        if isinstance(config, dict):
+            arch = architecture_of(config)
+            config = arch.config_from_dict(config)
+        else:
+            arch = architecture_of({"architectures": list(config.architectures)})
+        return cls._build(arch, config,
+                          lambda table, dev: random_weights(table, seed, weight_dtype, dev, std, gain_std),
+                          dtype, max_tokens, max_batch, max_context, device)
+
+    # ------------------------------------------------------------------ sequences and steps
+    def new_sequence(self) -> int:
+        """A slot for a sequence that starts now."""
+        return self.cache.alloc_slot()
+
+    def end_sequence(self, slot: int) -> None:
+        """Give back what the sequence holds."""
+        self.cache.free_slot(slot)
+
+    def step(self, entries, want=None) -> torch.Tensor | None:
+        """Run the next tokens of each sequence: entries = [(slot, tokens)], either whole
+        prompts or one token each; want = for each entry the places among its tokens whose
+        logits are asked for (None: each entry's last).  Returns float32 [n_wanted, vocab]."""
+        with torch.cuda.device(self.device):
+            return run_step(self.model, self.cache, entries, want, self.device)
+
+    def close(self) -> None:
+        self.model = None
+        self.cache = None

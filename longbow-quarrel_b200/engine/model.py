@@ -1,0 +1,99 @@
+"""A model built from its description: embedding, blocks, the order they run in,
+final norm, head.  It owns the parts and their weights; it owns no cache."""
+from __future__ import annotations
+
+import torch
+
+from ..parts.base import Runtime, StepContext
+from ..parts.registry import make_part
+from ..parts.spec import ModelSpec, PartSpec
+from ..weights.spec import WeightSpec
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, runtime: Runtime):
+        self.spec, self.runtime = spec, runtime
+        self.embedding = make_part("embedding", spec.embedding, runtime)
+        self.blocks = [make_part("block", PartSpec(layer.arrangement), runtime, layer=layer) for layer in spec.layers]
+        self.final_norm = make_part("norm", spec.final_norm, runtime)
+        self.head = make_part("head", spec.head, runtime)
+        for n, entry in enumerate(spec.schedule):
+            if not 0 <= entry.layer < len(self.blocks):
+                raise ValueError(f"schedule entry {n} names layer {entry.layer}; the model has {len(self.blocks)}")
+        writers = [e.cache for e in spec.schedule if e.writes_cache]
+        if len(set(writers)) != len(writers):
+            raise ValueError("schedule: two runs write the same cache entry")
+        for e in spec.schedule:
+            if not e.writes_cache and e.cache not in writers:
+                raise ValueError(f"schedule: a run reads cache entry {e.cache}, which no run writes")
+
+    # ------------------------------------------------------------------ weights
+    def _named_parts(self):
+        yield "", self.embedding
+        for block in self.blocks:
+            yield block.prefix, block
+        yield "", self.final_norm
+        yield "", self.head
+
+    def weight_table(self) -> dict[str, WeightSpec]:
+        """Every tensor the model reads, by its full name."""
+        table: dict[str, WeightSpec] = {}
+        for prefix, part in self._named_parts():
+            for name, spec in part.weights().items():
+                full = prefix + name
+                if full in table:
+                    raise ValueError(f"two parts name the tensor {full!r}")
+                table[full] = spec
+        return table
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        for prefix, part in self._named_parts():
+            mine = {}
+            for name, spec in part.weights().items():
+                if prefix + name in tensors:
+                    mine[name] = tensors[prefix + name]
+                elif spec.fallback is not None:
+                    mine[spec.fallback] = tensors[spec.fallback]
+                else:
+                    raise KeyError(prefix + name)
+            tied = getattr(part, "tied_to", None)
+            if tied is not None and getattr(part, "tied", False):
+                mine[tied] = tensors[tied]
+            part.load(mine)
+
+    def cache_needs(self) -> dict:
+        """Cache entry -> what the mixer that writes it needs."""
+        return {e.cache: self.blocks[e.layer].mixer.cache_need() for e in self.spec.schedule if e.writes_cache}
+
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+        for _, part in self._named_parts():
+            for t in _tensors_of(part):
+                if t.data_ptr() not in seen:
+                    seen.add(t.data_ptr())
+                    total += t.numel() * t.element_size()
+        return total
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, ctx: StepContext, cache) -> torch.Tensor | None:
+        """Run this step's rows through every scheduled layer; logits [wanted, vocab]
+        (float32) at ctx.want_rows, or None when nothing is wanted."""
+        x = self.embedding.forward(ctx.tokens)
+        for entry in self.spec.schedule:
+            self.blocks[entry.layer].forward(x, ctx, cache.view(entry.cache), entry.writes_cache)
+        if ctx.want_rows is None or ctx.want_rows.numel() == 0:
+            return None
+        h = self.final_norm.forward(x, rows=ctx.want_rows)
+        return self.head.forward(h)
+
+
+def _tensors_of(obj, depth: int = 0):
+    if depth > 3:
+        return
+    for value in vars(obj).values():
+        if isinstance(value, torch.Tensor):
+            yield value
+        elif hasattr(value, "tensor") and isinstance(getattr(value, "tensor"), torch.Tensor):
+            yield value.tensor
+        elif hasattr(value, "__dict__") and not isinstance(value, (Runtime, type)) and hasattr(value, "weights"):
+            yield from _tensors_of(value, depth + 1)

@@ -1,0 +1,105 @@
+"""The step function: a batch of sequences, each with its next tokens (a whole
+prompt, or one token), run as one packed batch from the cache; logits come back
+for the wanted rows only.
+
+The reference runs one token of one sequence per layer call
+(internal/engine/engine.go:1358-1605) and computes logits for the last prompt
+position only (engine.go:1505).  Here rows of all sequences are packed
+[T_total, D]; each row knows its sequence and its position, so padding does not
+exist and a row's result does not depend on its neighbours.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..cache import Cache, CacheError
+from ..parts.base import StepContext
+
+
+class StepError(ValueError):
+    pass
+
+
+def check_entries(entries, want, vocab_size: int) -> None:
+    """Errors that are found before anything is launched (empty input and token
+    range as in internal/engine/engine.go:1300,1327-1331)."""
+    if not entries:
+        raise StepError("a step needs at least one sequence")
+    seen = set()
+    for b, (slot, tokens) in enumerate(entries):
+        if slot in seen:
+            raise StepError(f"slot {slot} appears twice in one step")
+        seen.add(slot)
+        if len(tokens) == 0:
+            raise StepError(f"sequence {b} of the step brings no tokens")
+        for i, t in enumerate(tokens):
+            if not 0 <= int(t) < vocab_size:
+                raise StepError(f"token {t} at place {i} of sequence {b} is outside the vocabulary [0, {vocab_size})")
+    if want is not None:
+        if len(want) != len(entries):
+            raise StepError("`want` must have one list for each sequence of the step")
+        for b, (ws, (_, tokens)) in enumerate(zip(want, entries)):
+            for w in ws:
+                if not 0 <= int(w) < len(tokens):
+                    raise StepError(f"wanted place {w} of sequence {b} is outside its {len(tokens)} tokens")
+
+
+def pack_step(entries, want, past: list[int]) -> tuple[np.ndarray, dict]:
+    """All integers a step's kernels read, in one int32 array, and where each part lies.
+    `want` None asks for the last row of every sequence."""
+    B = len(entries)
+    new = [len(t) for _, t in entries]
+    T = sum(new)
+    cu = np.zeros(B + 1, dtype=np.int64)
+    np.cumsum(new, out=cu[1:])
+    tokens = np.concatenate([np.asarray(t, dtype=np.int64) for _, t in entries])
+    tok_seq = np.repeat(np.arange(B), new)
+    tok_pos = np.concatenate([np.arange(p, p + n) for p, n in zip(past, new)])
+    slots = np.asarray([s for s, _ in entries])
+    kv_len = np.asarray([p + n for p, n in zip(past, new)])
+    if want is None:
+        rows = cu[1:] - 1
+    else:
+        rows = np.asarray([cu[b] + int(w) for b, ws in enumerate(want) for w in ws], dtype=np.int64)
+    parts = {"tokens": tokens, "tok_seq": tok_seq, "tok_pos": tok_pos, "slots": slots, "kv_len": kv_len,
+             "cu_rows": cu, "want_rows": rows}
+    layout, offset = {}, 0
+    for name, arr in parts.items():
+        layout[name] = (offset, len(arr))
+        offset += -(-len(arr) // 4) * 4  # every part starts on a 16-byte boundary
+    flat = np.zeros(max(offset, 4), dtype=np.int32)
+    for name, arr in parts.items():
+        o, n = layout[name]
+        flat[o:o + n] = arr
+    info = {"layout": layout, "B": B, "T": T, "new": new, "past": list(past), "max_new": max(new),
+            "max_kv": int(kv_len.max())}
+    return flat, info
+
+
+def make_context(flat_dev: torch.Tensor, info: dict, h_slots: list[int]) -> StepContext:
+    def part(name):
+        o, n = info["layout"][name]
+        return flat_dev[o:o + n]
+    want = part("want_rows")
+    return StepContext(T=info["T"], B=info["B"], tokens=part("tokens"), tok_seq=part("tok_seq"),
+                       tok_pos=part("tok_pos"), slots=part("slots"), kv_len=part("kv_len"), cu_rows=part("cu_rows"),
+                       want_rows=want if want.numel() else None, h_slots=h_slots, h_new=info["new"],
+                       h_past=info["past"], max_new=info["max_new"], max_kv=info["max_kv"])
+
+
+def run_step(model, cache: Cache, entries, want, device) -> torch.Tensor | None:
+    """entries: [(slot, tokens)], want: [[places]] or None (= each sequence's last token).
+    Returns logits [n_wanted, vocab] float32 in the order of entries and of want."""
+    check_entries(entries, want, model.spec.vocab_size)
+    past = [cache.length(slot) for slot, _ in entries]
+    for slot, tokens in entries:
+        cache.reserve(slot, len(tokens))
+    cache.upload()
+    flat, info = pack_step(entries, want, past)
+    flat_dev = torch.from_numpy(flat).to(device)
+    ctx = make_context(flat_dev, info, [s for s, _ in entries])
+    logits = model.forward(ctx, cache)
+    for slot, tokens in entries:
+        cache.commit(slot, len(tokens))
+    return logits

@@ -1,0 +1,174 @@
+"""Python faces of the CUDA kernels.
+
+Every function takes torch tensors that live on the GPU, checks what the kernel
+cannot check itself, and launches on torch's current stream.  There is no
+fallback: a tensor on the CPU, or a library that cannot be built, is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(t: torch.Tensor | torch.dtype) -> int:
+    dt = t if isinstance(t, torch.dtype) else t.dtype
+    try:
+        return _CODES[dt]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16, not {dt}") from None
+
+
+def _p(t: torch.Tensor | None):
+    if t is None:
+        return c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("the kernels run on the GPU only: got a tensor on " + str(t.device))
+    return c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    reason = {-1: "unsupported dtype", -2: "unsupported size", -3: "CUDA driver entry point not found",
+              -4: "scratch too small"}.get(code, f"CUDA error {code}")
+    raise KernelError(f"{what}: {reason}")
+
+
+_declared: set[tuple[str, str]] = set()
+
+
+def _fn(lib: str, name: str, argtypes):
+    handle = build.load(lib)
+    fn = getattr(handle, name)
+    if (lib, name) not in _declared:
+        fn.argtypes = argtypes
+        fn.restype = c_int
+        _declared.add((lib, name))
+    return fn
+
+
+def _contig(t: torch.Tensor, what: str) -> torch.Tensor:
+    if not t.is_contiguous():
+        raise KernelError(f"{what} must be contiguous")
+    return t
+
+
+def prepare(dtype: torch.dtype, verbose: bool = True) -> None:
+    """Build and load the libraries a model of this dtype uses, before the first step."""
+    names = ["plain_kernels"]
+    for name in names:
+        build.load(name)
+
+
+# ------------------------------------------------------------------ plain kernels
+
+def embedding(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t] = table[tokens[t]] as float32 (the residual stream starts in 32-bit)."""
+    V, D = table.shape
+    T = tokens.numel()
+    if out is None:
+        out = torch.empty((T, D), dtype=torch.float32, device=table.device)
+    fn = _fn("plain_kernels", "lq_embedding", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(table, "table")), dtype_code(table), _p(tokens), _p(out), T, D, V, _stream()), "embedding")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            rows: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """RMS norm of rows of the float32 stream x [T, D]; `rows` (int32) picks rows."""
+    if x.dtype != torch.float32 or gain.dtype != torch.float32:
+        raise KernelError("rmsnorm reads a float32 stream and float32 gains")
+    D = x.shape[-1]
+    n = x.shape[0] if rows is None else rows.numel()
+    if out is None:
+        out = torch.empty((n, D), dtype=out_dtype, device=x.device)
+    fn = _fn("plain_kernels", "lq_rmsnorm", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_p(_contig(x, "x")), _p(gain), _p(rows), _p(out), dtype_code(out_dtype), n, D, float(eps), _stream()), "rmsnorm")
+    return out
+
+
+def gemm_plain(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, residual: torch.Tensor | None = None,
+               out: torch.Tensor | None = None) -> torch.Tensor:
+    """a [M, K] . w [N, K]^T (+ residual) on the CUDA cores, every product in float32."""
+    M, K = a.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"linear: input width {K} does not match weight width {K2}")
+    if residual is not None:
+        if residual.dtype != torch.float32 or tuple(residual.shape) != (M, N):
+            raise KernelError("linear: residual must be float32 [M, N]")
+        if out is None:
+            out = residual
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    fn = _fn("plain_kernels", "lq_gemm_plain", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                                c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(a, "a")), dtype_code(a), _p(_contig(w, "w")), dtype_code(w), _p(out), dtype_code(out),
+              _p(residual), M, N, K, _stream()), "linear")
+    return out
+
+
+def rope_kv_write(qkv: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tensor | None, tok_pos, tok_seq, slots,
+                  page_table: torch.Tensor | None, k_pages: torch.Tensor | None, v_pages: torch.Tensor | None,
+                  H: int, Hkv: int, hd: int, page_size: int) -> None:
+    """Rotate q and k of every token in place and store k, v into the cache pages."""
+    T = qkv.shape[0]
+    has_kv = k_pages is not None
+    width = (H + (2 * Hkv if has_kv else 0)) * hd
+    if qkv.shape[1] != width:
+        raise KernelError(f"rope: qkv rows are {qkv.shape[1]} wide, expected {width}")
+    if has_kv and (k_pages.dtype != qkv.dtype or v_pages.dtype != qkv.dtype):
+        raise KernelError("rope: the cache and the activations must have one dtype")
+    if cos is not None and (cos.dtype != torch.float32 or cos.shape[1] != hd // 2):
+        raise KernelError("rope: cos/sin tables must be float32 [positions, head_dim / 2]")
+    fn = _fn("plain_kernels", "lq_rope_kv_write", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                   c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                                   c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(qkv, "qkv")), dtype_code(qkv), _p(cos), _p(sin), _p(tok_pos), _p(tok_seq), _p(slots),
+              _p(page_table), page_table.stride(0) if page_table is not None else 0, _p(k_pages), _p(v_pages),
+              T, H, Hkv, hd, page_size, int(has_kv), _stream()), "rope_kv_write")
+
+
+def attention_plain(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq, slots, H: int, Hkv: int,
+                    hd: int, page_size: int, scale: float, window: int | None,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of every token over its own sequence's cache; q is the left
+    H*hd columns of a [T, q_stride] buffer."""
+    T = q.shape[0]
+    if hd > 256:
+        raise KernelError(f"attention: head_dim {hd} exceeds 256")
+    if out is None:
+        out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
+    fn = _fn("plain_kernels", "lq_attention_plain", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                                     c_int, c_float, c_int, c_void_p])
+    _check(fn(_p(q), q.stride(0), dtype_code(q), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0),
+              _p(tok_pos), _p(tok_seq), _p(slots), _p(out), T, H, Hkv, hd, page_size, float(scale),
+              int(window or 0), _stream()), "attention")
+    return out
+
+
+def swiglu(gu: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """gu [T, 2F] (gate columns, then up columns) -> up * silu(gate) [T, F]."""
+    T, F2 = gu.shape
+    F = F2 // 2
+    if out is None:
+        out = torch.empty((T, F), dtype=gu.dtype, device=gu.device)
+    fn = _fn("plain_kernels", "lq_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(gu, "gu")), _p(out), dtype_code(gu), T, F, _stream()), "swiglu")
+    return out

@@ -1,0 +1,113 @@
+"""What every part is: sizes and constants given at construction, the tensors it
+needs, and a forward that works on the packed rows of one step.
+
+The runtime says where and in which precision a model runs; the step context says
+which rows belong to which sequence and where they stand.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..weights.spec import WeightSpec
+
+
+@dataclass
+class Runtime:
+    """Where a model runs.  dtype float32 = every tensor and product in true 32-bit;
+    bfloat16 = bfloat16 weights, activations and cache with a 32-bit residual stream,
+    32-bit norms, softmax, rotation and accumulation."""
+    device: torch.device
+    dtype: torch.dtype
+    max_context: int
+    shared: dict = field(default_factory=dict)  # tables shared by equal parts (rope cos/sin)
+
+    @property
+    def act_dtype(self) -> torch.dtype:
+        return self.dtype
+
+
+@dataclass
+class StepContext:
+    """The packed rows of one step.  T rows of B sequences; row r belongs to sequence
+    tok_seq[r] of the batch and stands at position tok_pos[r] of that sequence; the
+    sequence lives in cache slot slots[b] and holds kv_len[b] tokens once this step's
+    rows are stored.  All tensors are int32 on the device; the `h_` twins are host lists."""
+    T: int
+    B: int
+    tokens: torch.Tensor
+    tok_seq: torch.Tensor
+    tok_pos: torch.Tensor
+    slots: torch.Tensor
+    kv_len: torch.Tensor
+    cu_rows: torch.Tensor
+    want_rows: torch.Tensor | None
+    h_slots: list[int]
+    h_new: list[int]
+    h_past: list[int]
+    max_new: int
+    max_kv: int
+
+    @property
+    def decode(self) -> bool:
+        return self.max_new == 1
+
+
+class Part:
+    """Base of all parts."""
+
+    def weights(self) -> dict[str, WeightSpec]:
+        """Tensor name (relative to the part's prefix) -> what it must look like."""
+        return {}
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        """Take the tensors named by weights() (already on the device)."""
+
+
+@dataclass(frozen=True)
+class KVNeed:
+    """A mixer that keeps keys and values of every position (or of the last `window`)."""
+    n_kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A mixer that keeps a state of fixed size for each sequence."""
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Mixer(Part):
+    def cache_need(self) -> KVNeed | StateNeed | None:
+        return None
+
+    def forward(self, h: torch.Tensor, ctx: StepContext, cache_view, residual: torch.Tensor,
+                writes_cache: bool = True) -> None:
+        """Read the normed rows h [T, D]; add the mixer's output to residual [T, D] (float32)."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, h: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
+        """Read the normed rows h [T, D]; add the output to residual [T, D] (float32)."""
+        raise NotImplementedError
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
+        """Normalise rows of the float32 stream; returns the activation dtype."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Either gives cos/sin tables for the fused rotate-and-store kernel, or rotates
+    q and k itself in `apply` (then `tables` returns None)."""
+
+    def tables(self) -> tuple[torch.Tensor, torch.Tensor] | None:
+        return None
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor | None, positions: torch.Tensor) -> None:
+        """Rotate q [T, H, hd] and k [T, Hkv, hd] in place."""

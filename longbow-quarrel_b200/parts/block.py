@@ -1,0 +1,42 @@
+"""The arrangement of parts in a layer.
+
+"pre_norm": x += mixer(norm1(x)); x += ffn(norm2(x)), the order of the reference's
+block (internal/device/metal.go:1347-1527), with the residual stream x in 32-bit
+throughout (internal/engine/engine.go:1375)."""
+from __future__ import annotations
+
+from .base import Part, Runtime, StepContext
+from .registry import make_part, register_part
+from .spec import LayerSpec
+
+
+@register_part("block", "pre_norm")
+class PreNormBlock(Part):
+    def __init__(self, runtime: Runtime, layer: LayerSpec):
+        self.prefix = layer.prefix
+        self.norm1 = make_part("norm", layer.norm1, runtime)
+        self.mixer = make_part("mixer", layer.mixer, runtime)
+        self.norm2 = make_part("norm", layer.norm2, runtime)
+        self.ffn = make_part("ffn", layer.ffn, runtime)
+
+    def parts(self):
+        return (self.norm1, self.mixer, self.norm2, self.ffn)
+
+    def weights(self):
+        out = {}
+        for part in self.parts():
+            for name, spec in part.weights().items():
+                if name in out:
+                    raise ValueError(f"layer {self.prefix}: two parts name the tensor {name!r}")
+                out[name] = spec
+        return out
+
+    def load(self, tensors):
+        for part in self.parts():
+            part.load({n: tensors[n] for n in part.weights()})
+
+    def forward(self, x, ctx: StepContext, cache_view, writes_cache: bool = True):
+        h = self.norm1.forward(x)
+        self.mixer.forward(h, ctx, cache_view, x, writes_cache)
+        h = self.norm2.forward(x)
+        self.ffn.forward(h, ctx, x)
