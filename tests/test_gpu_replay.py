@@ -1,0 +1,55 @@
+"""Trace replay through bin/trace_run: the same requests whole, with the last 32
+tokens one by one, and in batches of unequal lengths whose slots are used again,
+in 32-bit and in bfloat16, all against the plain implementation."""
+import numpy as np
+import pytest
+
+from helpers import TINY, TOL, make_model_folder, plain_logits, random_tokens, rel_err
+from trace_tools import run_trace, trace_batches, trace_last_one_by_one, trace_whole
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"r0": 40, "r1": 33, "r2": 100, "r3": 57, "r4": 71, "r5": 34, "r6": 90}
+PROMPTS = {"r0": 7, "r1": 33, "r2": 12, "r3": 1, "r4": 64, "r5": 20, "r6": 65}
+
+
+def _requests(name):
+    vocab = TINY[name]["vocab_size"]
+    return {rid: random_tokens(n, vocab, 100 + i) for i, (rid, n) in enumerate(LENGTHS.items())}
+
+
+def _compare(got, requests, folder, tol, what):
+    worst = 0.0
+    for rid, tokens in requests.items():
+        ref = plain_logits(folder, tokens)
+        for pos in range(len(tokens)):
+            if (rid, pos) in got:
+                err = rel_err(got[(rid, pos)], ref[pos])
+                worst = max(worst, err)
+                assert err < tol, f"{what}: request {rid} position {pos} of {len(tokens)}: error {err:.3g}"
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_replay_all_cuts_match_plain(tmp_path, name, dtype):
+    folder = make_model_folder(tmp_path, name, seed=11)
+    requests = _requests(name)
+    whole = run_trace(folder, dtype, trace_whole(requests), tmp_path / "whole")
+    assert len(whole) == sum(LENGTHS.values())
+    _compare(whole, requests, folder, TOL[dtype], "whole")
+
+    tail = run_trace(folder, dtype, trace_last_one_by_one(requests), tmp_path / "tail")
+    assert len(tail) == 33 * len(requests)
+    _compare(tail, requests, folder, TOL[dtype], "last 32 one by one")
+
+    batched = run_trace(folder, dtype, trace_batches(requests, PROMPTS, width=3), tmp_path / "batched")
+    assert len(batched) == sum(LENGTHS.values())
+    _compare(batched, requests, folder, TOL[dtype], "unequal batches")
+
+    # The cuts agree with one another far more closely than with the plain implementation.
+    cut_tol = 2e-5 if dtype == "float32" else TOL[dtype]
+    for key, row in tail.items():
+        assert rel_err(row, whole[key]) < cut_tol, ("tail vs whole", key)
+    for key, row in batched.items():
+        assert rel_err(row, whole[key]) < cut_tol, ("batched vs whole", key)
