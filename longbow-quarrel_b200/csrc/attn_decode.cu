@@ -1,0 +1,277 @@
+// Attention of single query tokens over the paged cache, split along the keys
+// (decoding: one new token for each sequence of the batch).
+//
+// The step is bound by reading K and V once from HBM.  A block serves one token, one
+// kv head and one slice of that sequence's keys; the query heads that share the kv
+// head are the rows of the m16n8k16 tile (grouped-query attention reads each key once
+// for the whole group).  Warps take 16-key tiles in turn.  K and V go straight from
+// global memory into mma fragments with 16-byte loads -- nothing is reused, so nothing
+// is staged in shared memory: for Q.K^T the head dimension is permuted alike in Q and
+// K, for P.V the output columns are permuted and put back in place when O is written.
+// Softmax runs online in 32-bit; the warps of a block and then the slices of a
+// sequence are merged by their running maximum and sum, in a fixed order.
+//
+// Slices write unnormalised partial outputs [token, head, slice, head_dim] with
+// (max, sum) to scratch memory; lq_attn_decode's second kernel merges them.
+//
+// Reference counterpart: att_fused_f16 (internal/device/kernels.metal:657-813), one
+// threadgroup per query head, scores in threadgroup memory.
+#include "common.cuh"
+#include <math_constants.h>
+
+namespace {
+
+constexpr int DW = 4;            // warps per block
+constexpr int TILE = 16;         // keys per warp tile
+
+__device__ __forceinline__ uint4 ldg16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t reg_of(const uint4& v, int i) {
+    return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
+}
+
+// HD: head_dim rounded up to 32, 64 or 128; the real head_dim hd is a multiple of 8.
+template <int HD>
+__global__ void __launch_bounds__(DW * 32)
+attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_pages,
+                   const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ page_table, int pt_stride,
+                   const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
+                   float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
+                   int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits) {
+    constexpr int QB = HD / 32;                    // 32-wide blocks of the head dimension (Q.K^T)
+    constexpr int VC = (HD + 63) / 64;             // 64-wide column groups (P.V)
+    __shared__ float sm_o[DW][16][HD + 1];
+    __shared__ float sm_m[DW][16], sm_l[DW][16];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int split = blockIdx.x, tok = blockIdx.z;
+    const int G = H / Hkv, gtiles = (G + 15) / 16;
+    const int kvh = blockIdx.y / gtiles, gt = blockIdx.y % gtiles;
+    const int pos = tok_pos[tok], len = pos + 1;
+    const int start = (window > 0 && pos >= window) ? pos - window + 1 : 0;
+    const int* pt = page_table + (size_t)slots[tok_seq[tok]] * pt_stride;
+
+    // Query rows of this thread: heads hq0 (row g) and hq1 (row g + 8) of the group.
+    const int r0 = gt * 16 + g, r1 = r0 + 8;
+    const bool r0ok = r0 < G, r1ok = r1 < G;
+    const __nv_bfloat16* q0p = q + (size_t)tok * q_stride + (size_t)(kvh * G + (r0ok ? r0 : 0)) * hd;
+    const __nv_bfloat16* q1p = q + (size_t)tok * q_stride + (size_t)(kvh * G + (r1ok ? r1 : 0)) * hd;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    uint4 qa[QB], qb[QB];
+#pragma unroll
+    for (int b = 0; b < QB; ++b) {
+        int d = b * 32 + t * 8;
+        qa[b] = (r0ok && d < hd) ? ldg16(q0p + d) : zero;
+        qb[b] = (r1ok && d < hd) ? ldg16(q1p + d) : zero;
+    }
+
+    float o[VC * 8][4];
+#pragma unroll
+    for (int j = 0; j < VC * 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
+    float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+
+    const int first_tile = start / TILE;
+    const int n_tiles = (len + TILE - 1) / TILE - first_tile;
+    const int per_split = (n_tiles + n_splits - 1) / n_splits;
+    const int tile_lo = first_tile + split * per_split;
+    const int tile_hi = min(first_tile + n_tiles, tile_lo + per_split);
+    const size_t head_off = (size_t)kvh * page_size * hd;
+
+    for (int tile = tile_lo + warp; tile < tile_hi; tile += DW) {
+        const int kb = tile * TILE;
+        const int page = pt[kb / page_size];
+        const size_t page_off = (size_t)page * Hkv * page_size * hd + head_off + (size_t)(kb % page_size) * hd;
+        const __nv_bfloat16* kp = k_pages + page_off;
+        const __nv_bfloat16* vp = v_pages + page_off;
+        // K: rows kb + g and kb + 8 + g; V: rows kb + {2t, 2t+1, 2t+8, 2t+9}.
+        uint4 kr[2][QB], vr[4][VC];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            int key = kb + nt * 8 + g;
+#pragma unroll
+            for (int b = 0; b < QB; ++b) {
+                int d = b * 32 + t * 8;
+                kr[nt][b] = (key < len && d < hd) ? ldg16(kp + (size_t)(nt * 8 + g) * hd + d) : zero;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            int row = 2 * t + (r & 1) + (r >> 1) * 8;
+#pragma unroll
+            for (int c = 0; c < VC; ++c) {
+                int d = c * 64 + g * 8;
+                vr[r][c] = (kb + row < len && d < hd) ? ldg16(vp + (size_t)row * hd + d) : zero;
+            }
+        }
+        // S = Q K^T for two 8-key tiles.
+        float s[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
+#pragma unroll
+            for (int b = 0; b < QB; ++b) {
+                mma_bf16(s[nt], qa[b].x, qb[b].x, qa[b].y, qb[b].y, kr[nt][b].x, kr[nt][b].y);
+                mma_bf16(s[nt], qa[b].z, qb[b].z, qa[b].w, qb[b].w, kr[nt][b].z, kr[nt][b].w);
+            }
+        }
+        float tm0 = -CUDART_INF_F, tm1 = -CUDART_INF_F;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                int key = kb + nt * 8 + 2 * t + i;
+                bool ok = key >= start && key < len;
+                s[nt][i] = ok ? s[nt][i] * scale : -CUDART_INF_F;
+                s[nt][2 + i] = ok ? s[nt][2 + i] * scale : -CUDART_INF_F;
+                tm0 = fmaxf(tm0, s[nt][i]);
+                tm1 = fmaxf(tm1, s[nt][2 + i]);
+            }
+        tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 1));
+        tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 2));
+        tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 1));
+        tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 2));
+        const float nm0 = fmaxf(m0, tm0), nm1 = fmaxf(m1, tm1);
+        // A tile of this warp always holds at least one visible key (kb <= pos, kb + 15 >= start),
+        // so nm0 and nm1 are finite.
+        const float c0 = expf(m0 - nm0), c1 = expf(m1 - nm1);
+        m0 = nm0;
+        m1 = nm1;
+        uint32_t pa[4];
+        float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            float p00 = expf(s[nt][0] - nm0), p01 = expf(s[nt][1] - nm0);
+            float p10 = expf(s[nt][2] - nm1), p11 = expf(s[nt][3] - nm1);
+            ps0 += p00 + p01;
+            ps1 += p10 + p11;
+            pa[nt * 2 + 0] = pack_bf16(p00, p01);
+            pa[nt * 2 + 1] = pack_bf16(p10, p11);
+        }
+        l0 = l0 * c0 + ps0;
+        l1 = l1 * c1 + ps1;
+#pragma unroll
+        for (int c = 0; c < VC; ++c)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float (&acc)[4] = o[c * 8 + j];
+                acc[0] *= c0; acc[1] *= c0; acc[2] *= c1; acc[3] *= c1;
+                const unsigned sel = (j & 1) ? 0x7632u : 0x5410u;
+                uint32_t b0 = __byte_perm(reg_of(vr[0][c], j >> 1), reg_of(vr[1][c], j >> 1), sel);
+                uint32_t b1 = __byte_perm(reg_of(vr[2][c], j >> 1), reg_of(vr[3][c], j >> 1), sel);
+                mma_bf16(acc, pa[0], pa[1], pa[2], pa[3], b0, b1);
+            }
+    }
+    // Row sums: add the four threads of a row.
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    // Park each warp's state; column n of an output tile belongs to d = c*64 + n*8 + j.
+#pragma unroll
+    for (int c = 0; c < VC; ++c)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int d0 = c * 64 + (2 * t) * 8 + j, d1 = d0 + 8;
+            if (d0 < HD) { sm_o[warp][g][d0] = o[c * 8 + j][0]; sm_o[warp][g + 8][d0] = o[c * 8 + j][2]; }
+            if (d1 < HD) { sm_o[warp][g][d1] = o[c * 8 + j][1]; sm_o[warp][g + 8][d1] = o[c * 8 + j][3]; }
+        }
+    if (t == 0) {
+        sm_m[warp][g] = m0; sm_m[warp][g + 8] = m1;
+        sm_l[warp][g] = l0; sm_l[warp][g + 8] = l1;
+    }
+    __syncthreads();
+    const int rows = min(16, G - gt * 16);
+    for (int i = threadIdx.x; i < rows * hd; i += DW * 32) {
+        int r = i / hd, d = i % hd;
+        float mx = -CUDART_INF_F;
+#pragma unroll
+        for (int w = 0; w < DW; ++w) mx = fmaxf(mx, sm_m[w][r]);
+        float acc = 0.f, l = 0.f;
+        if (mx > -CUDART_INF_F) {
+#pragma unroll
+            for (int w = 0; w < DW; ++w) {
+                float f = expf(sm_m[w][r] - mx);   // a warp without tiles has m = -inf: f = 0
+                acc += sm_o[w][r][d] * f;
+                l += sm_l[w][r] * f;
+            }
+        }
+        int h = kvh * G + gt * 16 + r;
+        if (n_splits == 1) {
+            out[((size_t)tok * H + h) * hd + d] = __float2bfloat16_rn(acc / l);
+        } else {
+            size_t base = ((size_t)tok * H + h) * n_splits + split;
+            part_o[base * hd + d] = acc;
+            if (d == 0) { part_ml[base * 2] = mx; part_ml[base * 2 + 1] = l; }
+        }
+    }
+}
+
+// Merge the slices of one (token, head): out = sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M).
+__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                  __nv_bfloat16* __restrict__ out, int hd, int n_splits) {
+    const size_t th = blockIdx.x;
+    const float* ml = part_ml + th * n_splits * 2;
+    float mx = -CUDART_INF_F;
+    for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, ml[2 * s]);
+    float l = 0.f;
+    for (int s = 0; s < n_splits; ++s)
+        if (ml[2 * s] > -CUDART_INF_F) l += ml[2 * s + 1] * expf(ml[2 * s] - mx);
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < n_splits; ++s)
+            if (ml[2 * s] > -CUDART_INF_F) acc += part_o[(th * n_splits + s) * hd + d] * expf(ml[2 * s] - mx);
+        out[th * hd + d] = __float2bfloat16_rn(acc / l);
+    }
+}
+
+template <int HD>
+int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages, const int* page_table, int pt_stride,
+           const int* tok_pos, const int* tok_seq, const int* slots, float* part_o, float* part_ml, void* out,
+           int T, int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits, cudaStream_t stream) {
+    int G = H / Hkv, gtiles = (G + 15) / 16;
+    dim3 grid(n_splits, Hkv * gtiles, T);
+    attn_decode_kernel<HD><<<grid, DW * 32, 0, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pages,
+        (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, part_o, part_ml,
+        (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, n_splits);
+    int rc = lq_launch_status();
+    if (rc != LQ_OK || n_splits == 1) return rc;
+    attn_merge_kernel<<<T * H, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, hd, n_splits);
+    return lq_launch_status();
+}
+
+}  // namespace
+
+// q: rows of q_stride elements whose first H*hd hold the query heads; out [T, H*hd].
+// part_o needs T*H*n_splits*hd floats and part_ml T*H*n_splits*2 floats when n_splits > 1.
+// head_dim must be a multiple of 8 and at most 128; page_size a multiple of 16.
+LQ_EXPORT int lq_attn_decode(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+                             const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
+                             const int* slots, float* part_o, float* part_ml, void* out, int T, int H, int Hkv,
+                             int hd, int page_size, float scale, int window, int n_splits, cudaStream_t stream) {
+    if (T <= 0) return LQ_OK;
+    if (hd % 8 || hd > 128 || hd <= 0 || H % Hkv || page_size % TILE || n_splits < 1 || q_stride % 8) return LQ_BAD_SIZE;
+    if (n_splits > 1 && (!part_o || !part_ml)) return LQ_BAD_SIZE;
+#define LQ_GO(HD) return launch<HD>(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, \
+                                    part_o, part_ml, out, T, H, Hkv, hd, page_size, scale, window, n_splits, stream)
+    if (hd <= 32) LQ_GO(32);
+    if (hd <= 64) LQ_GO(64);
+    LQ_GO(128);
+#undef LQ_GO
+}

@@ -1,0 +1,163 @@
+// y = x . W^T for few rows of x (decoding: one token for each sequence of the batch).
+//
+// With at most 64 rows every weight is used once, so the product is bound by
+// reading W from HBM.  Each block owns 16 rows of W and all of K; its 8 warps take
+// the 32-wide k chunks in turn, stream their part of W straight from global memory
+// into mma fragments (16-byte loads, no shared-memory staging: nothing is reused),
+// multiply on the tensor cores with the tokens as the n side of m16n8k16, and sum
+// their partial results in a fixed order through shared memory.  An output therefore
+// depends only on its own row of x and W, not on how many other rows the batch has.
+//
+// The k index inside a chunk is permuted the same way for W and x (a thread's eight
+// consecutive elements feed two mma k-slots groups), which a dot product allows and
+// which makes every global load a 16-byte one.
+//
+// Epilogues: bfloat16 store; float32 store; float32 residual add in place;
+// SwiGLU over weight rows interleaved in blocks of 8 (8 gate rows, then their 8 up
+// rows), writing up * silu(gate).
+//
+// Reference counterpart: the mat-vec kernels linear_f16 / linear_f16_f32
+// (internal/device/kernels.metal:105-132,1084-1106), one output row per SIMD group.
+#include "common.cuh"
+
+#define EPI_BF16 0
+#define EPI_F32 1
+#define EPI_RESID 2
+#define EPI_SWIGLU 3
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int ROWS = 16;     // rows of W per block
+constexpr int KC = 32;       // k per chunk
+constexpr int UNROLL = 4;    // chunks in flight per warp
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ldg_cached(const void* p) {
+    return __ldg(reinterpret_cast<const uint4*>(p));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int MT, int EPI>
+__global__ void __launch_bounds__(WARPS * 32)
+gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, void* __restrict__ Cout,
+                   const float* __restrict__ residual, int M, int N, int K) {
+    __shared__ float red[WARPS][ROWS][MT * 8 + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * ROWS;
+    const int r0 = n0 + g, r1 = n0 + g + 8;
+    const bool r0ok = r0 < N, r1ok = r1 < N;
+    const __nv_bfloat16* w0 = W + (size_t)(r0ok ? r0 : 0) * K;
+    const __nv_bfloat16* w1 = W + (size_t)(r1ok ? r1 : 0) * K;
+    const int n_chunks = (K + KC - 1) / KC;
+
+    float acc[MT][4];
+#pragma unroll
+    for (int j = 0; j < MT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int c0 = warp; c0 < n_chunks; c0 += WARPS * UNROLL) {
+        uint4 a0[UNROLL], a1[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            int c = c0 + u * WARPS;
+            int k = c * KC + t * 8;
+            bool ok = c < n_chunks && k < K;   // K is a multiple of 8, so a started 16-byte piece is whole
+            a0[u] = (ok && r0ok) ? ldg_stream(w0 + k) : zero;
+            a1[u] = (ok && r1ok) ? ldg_stream(w1 + k) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            int c = c0 + u * WARPS;
+            int k = c * KC + t * 8;
+            bool ok = c < n_chunks && k < K;
+#pragma unroll
+            for (int j = 0; j < MT; ++j) {
+                int m = j * 8 + g;
+                uint4 b = (ok && m < M) ? ldg_cached(X + (size_t)m * K + k) : zero;
+                mma_bf16(acc[j], a0[u].x, a1[u].x, a0[u].y, a1[u].y, b.x, b.y);
+                mma_bf16(acc[j], a0[u].z, a1[u].z, a0[u].w, a1[u].w, b.z, b.w);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+        red[warp][g][j * 8 + 2 * t] = acc[j][0];
+        red[warp][g][j * 8 + 2 * t + 1] = acc[j][1];
+        red[warp][g + 8][j * 8 + 2 * t] = acc[j][2];
+        red[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
+    }
+    __syncthreads();
+    // One thread per (token, row): consecutive threads write consecutive outputs of a token.
+    constexpr int OUT_ROWS = (EPI == EPI_SWIGLU) ? ROWS / 2 : ROWS;
+    for (int i = threadIdx.x; i < MT * 8 * OUT_ROWS; i += WARPS * 32) {
+        int m = i / OUT_ROWS, r = i % OUT_ROWS;
+        if (m >= M) continue;
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) s += red[w][r][m];
+        if (EPI == EPI_SWIGLU) {
+            float u = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) u += red[w][r + 8][m];
+            int f = (n0 >> 1) + r;
+            if (f < (N >> 1))
+                ((__nv_bfloat16*)Cout)[(size_t)m * (N >> 1) + f] = __float2bfloat16_rn(u * (s / (1.0f + expf(-s))));
+        } else {
+            int n = n0 + r;
+            if (n >= N) continue;
+            size_t o = (size_t)m * N + n;
+            if (EPI == EPI_BF16) ((__nv_bfloat16*)Cout)[o] = __float2bfloat16_rn(s);
+            else if (EPI == EPI_F32) ((float*)Cout)[o] = s;
+            else ((float*)Cout)[o] = residual[o] + s;
+        }
+    }
+}
+
+template <int MT>
+int launch_mt(const void* X, const void* W, void* C, const float* residual, int M, int N, int K, int epi,
+              cudaStream_t stream) {
+    dim3 grid((N + ROWS - 1) / ROWS), block(WARPS * 32);
+    const __nv_bfloat16* x = (const __nv_bfloat16*)X;
+    const __nv_bfloat16* w = (const __nv_bfloat16*)W;
+    switch (epi) {
+        case EPI_BF16: gemm_skinny_kernel<MT, EPI_BF16><<<grid, block, 0, stream>>>(x, w, C, residual, M, N, K); break;
+        case EPI_F32: gemm_skinny_kernel<MT, EPI_F32><<<grid, block, 0, stream>>>(x, w, C, residual, M, N, K); break;
+        case EPI_RESID: gemm_skinny_kernel<MT, EPI_RESID><<<grid, block, 0, stream>>>(x, w, C, residual, M, N, K); break;
+        case EPI_SWIGLU: gemm_skinny_kernel<MT, EPI_SWIGLU><<<grid, block, 0, stream>>>(x, w, C, residual, M, N, K); break;
+        default: return LQ_BAD_DTYPE;
+    }
+    return lq_launch_status();
+}
+
+}  // namespace
+
+// X [M, K] bf16, W [N, K] bf16; M <= 64, K % 8 == 0.  For EPI_SWIGLU, N counts the
+// interleaved gate and up rows (N % 16 == 0) and C is [M, N / 2].
+LQ_EXPORT int lq_gemm_skinny(const void* X, const void* W, void* C, const float* residual, int M, int N, int K,
+                             int epi, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return LQ_OK;
+    if (M > 64 || K % 8 != 0 || K <= 0) return LQ_BAD_SIZE;
+    if (epi == EPI_SWIGLU && N % 16 != 0) return LQ_BAD_SIZE;
+    if (epi == EPI_RESID && residual == nullptr) return LQ_BAD_SIZE;
+    int mt = (M + 7) / 8;
+    switch (mt) {
+        case 1: return launch_mt<1>(X, W, C, residual, M, N, K, epi, stream);
+        case 2: return launch_mt<2>(X, W, C, residual, M, N, K, epi, stream);
+        case 3: case 4: return launch_mt<4>(X, W, C, residual, M, N, K, epi, stream);
+        default: return launch_mt<8>(X, W, C, residual, M, N, K, epi, stream);
+    }
+}

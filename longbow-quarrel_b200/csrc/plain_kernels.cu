@@ -324,26 +324,30 @@ LQ_EXPORT int lq_attention_plain(const void* q, int q_stride, int dtype, const v
 }
 
 // ------------------------------------------------------------------ swiglu
-// gu [T, 2F]: gate in columns [0, F), up in [F, 2F).  out = up * gate / (1 + e^-gate).
+// out = up * gate / (1 + e^-gate) from gu [T, 2F].  block == 0: gate in columns
+// [0, F), up in [F, 2F).  block == b > 0: columns alternate b gate, b up, b gate, ...
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, size_t total, int block) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     size_t t = i / F;
     int f = (int)(i % F);
-    float g = to_f32(gu[t * 2 * F + f]);
-    float u = to_f32(gu[t * 2 * F + F + f]);
+    int gi = block ? (f / block) * 2 * block + f % block : f;
+    int ui = block ? gi + block : F + f;
+    float g = to_f32(gu[t * 2 * F + gi]);
+    float u = to_f32(gu[t * 2 * F + ui]);
     out[i] = from_f32<T>(u * (g / (1.0f + expf(-g))));
 }
 
-LQ_EXPORT int lq_swiglu(const void* gu, void* out, int dtype, int T, int F, cudaStream_t stream) {
+LQ_EXPORT int lq_swiglu(const void* gu, void* out, int dtype, int T, int F, int block, cudaStream_t stream) {
     size_t total = (size_t)T * F;
     if (total == 0) return LQ_OK;
+    if (block < 0 || (block && F % block)) return LQ_BAD_SIZE;
     unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == LQ_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, F, total);
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, F, total, block);
     else if (dtype == LQ_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, F, total);
+        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, F, total, block);
     else
         return LQ_BAD_DTYPE;
     return lq_launch_status();

@@ -1,10 +1,27 @@
 """Attention over the paged cache: the choice of kernel."""
 from __future__ import annotations
 
+import torch
+
 from . import ops
+
+TARGET_BLOCKS = 296          # two blocks for each of the 148 SMs
+MAX_SPLITS = 32
+KEYS_PER_SPLIT = 256         # a slice shorter than this is not worth a block of its own
+
+
+def decode_splits(n_tokens: int, Hkv: int, group_tiles: int, max_kv: int) -> int:
+    """How many slices to cut each sequence's keys into so that the GPU is filled."""
+    blocks = max(1, n_tokens * Hkv * group_tiles)
+    want = -(-TARGET_BLOCKS // blocks)
+    return max(1, min(want, MAX_SPLITS, -(-max_kv // KEYS_PER_SPLIT)))
 
 
 def attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window):
     """Rows of qkv hold q in their left H*hd columns.  Returns [T, H*hd]."""
+    if qkv.dtype == torch.bfloat16 and ctx.decode and hd <= 128 and hd % 8 == 0 and qkv.stride(0) % 8 == 0:
+        n_splits = decode_splits(ctx.T, Hkv, -(-(H // Hkv) // 16), ctx.max_kv)
+        return ops.attn_decode(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.tok_pos,
+                               ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window, n_splits)
     return ops.attention_plain(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.tok_pos,
                                ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window)

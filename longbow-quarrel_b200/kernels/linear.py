@@ -33,3 +33,27 @@ def linear(a: torch.Tensor, weight: LinearWeight, out_dtype: torch.dtype,
         if out is not None:
             return out
     return ops.gemm_plain(a, weight.tensor, out_dtype, residual)
+
+
+GATE_UP_BLOCK = 8
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Rows of gate and up [F, K] alternating in blocks of 8: the layout whose product
+    the fused SwiGLU epilogues read (a tile of 16 output columns holds 8 gate values and
+    the 8 up values that go with them)."""
+    F, K = gate.shape
+    b = GATE_UP_BLOCK
+    return torch.stack([gate.reshape(F // b, b, K), up.reshape(F // b, b, K)], dim=1).reshape(2 * F, K).contiguous()
+
+
+def linear_swiglu(a: torch.Tensor, weight: LinearWeight, block: int) -> torch.Tensor:
+    """act(a . Wg^T) * (a . Wu^T) for the stacked weight [2F, K]; block 0 = gate rows
+    then up rows, block 8 = interleaved."""
+    if block == GATE_UP_BLOCK and a.dtype == torch.bfloat16 and weight.tensor.dtype == torch.bfloat16:
+        from . import tensorcore
+        out = tensorcore.linear_swiglu_bf16(a, weight)
+        if out is not None:
+            return out
+    gu = linear(a, weight, a.dtype)
+    return ops.swiglu(gu, block)

@@ -70,7 +70,7 @@ def _contig(t: torch.Tensor, what: str) -> torch.Tensor:
 
 def prepare(dtype: torch.dtype, verbose: bool = True) -> None:
     """Build and load the libraries a model of this dtype uses, before the first step."""
-    names = ["plain_kernels"]
+    names = ["plain_kernels"] + (["gemm_skinny", "attn_decode"] if dtype == torch.bfloat16 else [])
     for name in names:
         build.load(name)
 
@@ -163,12 +163,73 @@ def attention_plain(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_
     return out
 
 
-def swiglu(gu: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """gu [T, 2F] (gate columns, then up columns) -> up * silu(gate) [T, F]."""
+def swiglu(gu: torch.Tensor, block: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """gu [T, 2F] -> up * silu(gate) [T, F].  block 0: gate columns, then up columns;
+    block b: b gate columns, b up columns, alternating."""
     T, F2 = gu.shape
     F = F2 // 2
     if out is None:
         out = torch.empty((T, F), dtype=gu.dtype, device=gu.device)
-    fn = _fn("plain_kernels", "lq_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(fn(_p(_contig(gu, "gu")), _p(out), dtype_code(gu), T, F, _stream()), "swiglu")
+    fn = _fn("plain_kernels", "lq_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(gu, "gu")), _p(out), dtype_code(gu), T, F, block, _stream()), "swiglu")
+    return out
+
+
+# ------------------------------------------------------------------ bfloat16 tensor-core kernels
+EPI_BF16, EPI_F32, EPI_RESID, EPI_SWIGLU = 0, 1, 2, 3
+SKINNY_MAX_ROWS = 64
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, epi: int, residual: torch.Tensor | None = None,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """a [M <= 64, K] . w [N, K]^T, both bfloat16, streaming w once from memory.
+    epi: EPI_BF16 / EPI_F32 store; EPI_RESID adds into the float32 `residual` in place;
+    EPI_SWIGLU reads w as alternating blocks of 8 gate and 8 up rows and stores
+    up * silu(gate) [M, N / 2]."""
+    M, K = a.shape
+    N = w.shape[0]
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_skinny takes bfloat16 inputs")
+    if w.shape[1] != K:
+        raise KernelError(f"linear: input width {K} does not match weight width {w.shape[1]}")
+    if M > SKINNY_MAX_ROWS or K % 8:
+        raise KernelError(f"gemm_skinny: {M} rows (at most {SKINNY_MAX_ROWS}) and width {K} (a multiple of 8)")
+    if epi == EPI_RESID:
+        if residual is None or residual.dtype != torch.float32 or tuple(residual.shape) != (M, N):
+            raise KernelError("linear: residual must be float32 [M, N]")
+        out = residual
+    elif out is None:
+        shape = (M, N // 2) if epi == EPI_SWIGLU else (M, N)
+        out = torch.empty(shape, dtype=torch.float32 if epi == EPI_F32 else torch.bfloat16, device=a.device)
+    fn = _fn("gemm_skinny", "lq_gemm_skinny", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), _p(residual), M, N, K, epi, _stream()), "gemm_skinny")
+    return out
+
+
+def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq, slots, H: int, Hkv: int, hd: int,
+                page_size: int, scale: float, window: int | None, n_splits: int,
+                out: torch.Tensor | None = None, scratch: tuple | None = None) -> torch.Tensor:
+    """Attention of single query rows over the paged bfloat16 cache, the keys of each
+    sequence cut into n_splits slices that are merged afterwards."""
+    T = q.shape[0]
+    if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
+        raise KernelError("attn_decode takes bfloat16 queries and cache")
+    if hd % 8 or hd > 128:
+        raise KernelError(f"attn_decode: head_dim {hd} must be a multiple of 8 and at most 128")
+    if out is None:
+        out = torch.empty((T, H * hd), dtype=torch.bfloat16, device=q.device)
+    part_o = part_ml = None
+    if n_splits > 1:
+        if scratch is None:
+            scratch = (torch.empty(T * H * n_splits * hd, dtype=torch.float32, device=q.device),
+                       torch.empty(T * H * n_splits * 2, dtype=torch.float32, device=q.device))
+        part_o, part_ml = scratch
+        if part_o.numel() < T * H * n_splits * hd or part_ml.numel() < T * H * n_splits * 2:
+            raise KernelError("attn_decode: scratch too small")
+    fn = _fn("attn_decode", "lq_attn_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                               c_float, c_int, c_int, c_void_p])
+    _check(fn(_p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0), _p(tok_pos),
+              _p(tok_seq), _p(slots), _p(part_o), _p(part_ml), _p(out), T, H, Hkv, hd, page_size, float(scale),
+              int(window or 0), n_splits, _stream()), "attn_decode")
     return out

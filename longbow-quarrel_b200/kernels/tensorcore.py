@@ -1,7 +1,28 @@
-"""Tensor-core paths of the bfloat16 matrix products (filled in kernel by kernel)."""
+"""Tensor-core paths of the bfloat16 matrix products."""
 from __future__ import annotations
+
+import torch
+
+from . import ops
 
 
 def linear_bf16(a, weight, out_dtype, residual):
-    """Returns None when no tensor-core kernel takes this product."""
+    """a [M, K] bf16 . W^T; returns None when no tensor-core kernel takes this product."""
+    M, K = a.shape
+    if K % 8:
+        return None
+    if M <= ops.SKINNY_MAX_ROWS:
+        if residual is not None:
+            return ops.gemm_skinny(a, weight.tensor, ops.EPI_RESID, residual)
+        if out_dtype == torch.float32:
+            return ops.gemm_skinny(a, weight.tensor, ops.EPI_F32)
+        return ops.gemm_skinny(a, weight.tensor, ops.EPI_BF16)
+    return None
+
+
+def linear_swiglu_bf16(a, weight):
+    """a . W^T over rows interleaved in blocks of 8 (gate, up), then up * silu(gate)."""
+    M, K = a.shape
+    if K % 8 == 0 and M <= ops.SKINNY_MAX_ROWS:
+        return ops.gemm_skinny(a, weight.tensor, ops.EPI_SWIGLU)
     return None

@@ -22,6 +22,7 @@ class GatedMLP(FeedForward):
         self.runtime, self.D, self.F = runtime, hidden_size, intermediate_size
         self.names = {**DEFAULT_NAMES, **(names or {})}
         self.w_gu: linear.LinearWeight | None = None
+        self.block = 0
         self.w_down: linear.LinearWeight | None = None
 
     def weights(self):
@@ -31,10 +32,16 @@ class GatedMLP(FeedForward):
 
     def load(self, tensors):
         n = self.names
-        self.w_gu = linear.LinearWeight(torch.cat([tensors[n["gate"]], tensors[n["up"]]], dim=0))
+        gate, up = tensors[n["gate"]], tensors[n["up"]]
+        if gate.dtype != up.dtype:
+            gate, up = gate.to(torch.float32), up.to(torch.float32)
+        # bfloat16 kernels apply SwiGLU in the product's epilogue over interleaved rows.
+        self.block = linear.GATE_UP_BLOCK if (self.runtime.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16
+                                              and self.F % linear.GATE_UP_BLOCK == 0) else 0
+        stacked = linear.interleave_gate_up(gate, up) if self.block else torch.cat([gate, up], dim=0)
+        self.w_gu = linear.LinearWeight(stacked)
         self.w_down = linear.LinearWeight(tensors[n["down"]])
 
     def forward(self, h, ctx: StepContext, residual):
-        gu = linear.linear(h, self.w_gu, self.runtime.act_dtype)
-        act = ops.swiglu(gu)
+        act = linear.linear_swiglu(h, self.w_gu, self.block)
         linear.linear(act, self.w_down, self.runtime.act_dtype, residual=residual)

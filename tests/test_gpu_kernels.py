@@ -1,0 +1,278 @@
+"""Each kernel alone against a plain float32 PyTorch restatement of the same
+operation, at sizes other than the engine's tiny configurations."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _ops():
+    from longbow_quarrel_b200.kernels import ops
+    return ops
+
+
+BF16_ULP = 2.0 ** -8     # a value stored in bfloat16 is within half of this, relatively, of the exact one
+
+
+def _close(got, ref, tol, rel=0.0):
+    """|got - ref| <= tol * rms(ref) + rel * |ref| everywhere.  `rel` is for results that
+    are rounded to bfloat16 on store, whose error is a fraction of each value itself."""
+    got, ref = got.float().cpu().double(), ref.float().cpu().double()
+    assert torch.isfinite(got).all()
+    rms = ref.pow(2).mean().sqrt().clamp_min(1e-30)
+    excess = ((got - ref).abs() - rel * ref.abs()) / rms
+    err = float(excess.max())
+    assert err < tol, err
+    return err
+
+
+def _rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+# ------------------------------------------------------------------ plain kernels
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding(dtype):
+    ops = _ops()
+    table = _rand((301, 72), dtype, 0)
+    tokens = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+    out = ops.embedding(table, tokens)
+    assert out.dtype == torch.float32
+    assert torch.equal(out, table[tokens.long()].float())
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("D", [72, 1000, 4096])
+def test_rmsnorm(out_dtype, D):
+    ops = _ops()
+    x = _rand((9, D), torch.float32, 1, 3.0)
+    gain = 1 + 0.1 * _rand((D,), torch.float32, 2)
+    eps = 1e-5
+    ref = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * gain
+    rel = 0.0 if out_dtype == torch.float32 else BF16_ULP
+    _close(ops.rmsnorm(x, gain, eps, out_dtype), ref, 2e-6, rel)
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
+    _close(ops.rmsnorm(x, gain, eps, out_dtype, rows=rows), ref[rows.long()], 2e-6, rel)
+
+
+@pytest.mark.parametrize("a_dtype,w_dtype", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                             (torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("M,N,K", [(1, 250, 80), (70, 130, 200), (5, 64, 1000)])
+def test_gemm_plain(a_dtype, w_dtype, M, N, K):
+    ops = _ops()
+    a, w = _rand((M, K), a_dtype, 3), _rand((N, K), w_dtype, 4)
+    ref = a.float().double() @ w.float().double().T
+    _close(ops.gemm_plain(a, w, torch.float32), ref, 1e-5)
+    res = _rand((M, N), torch.float32, 5)
+    expect = res.double() + ref
+    got = ops.gemm_plain(a, w, torch.float32, residual=res)
+    assert got.data_ptr() == res.data_ptr()
+    _close(got, expect, 1e-5)
+
+
+def test_gemm_plain_is_independent_of_other_rows():
+    """A row's result is bit-equal whether it is computed alone or among others."""
+    ops = _ops()
+    a, w = _rand((37, 328), torch.float32, 6), _rand((90, 328), torch.float32, 7)
+    full = ops.gemm_plain(a, w, torch.float32)
+    for r in (0, 11, 36):
+        assert torch.equal(ops.gemm_plain(a[r:r + 1].contiguous(), w, torch.float32)[0], full[r])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("block", [0, 8])
+def test_swiglu(dtype, block):
+    ops = _ops()
+    F = 40
+    g, u = _rand((6, F), dtype, 8, 2.0), _rand((6, F), dtype, 9)
+    if block:
+        gu = torch.stack([g.reshape(6, F // block, block), u.reshape(6, F // block, block)], dim=2).reshape(6, 2 * F)
+    else:
+        gu = torch.cat([g, u], dim=1)
+    ref = u.float() * (g.float() / (1 + torch.exp(-g.float())))
+    _close(ops.swiglu(gu.contiguous(), block), ref, 1e-6, 0.0 if dtype == torch.float32 else BF16_ULP)
+
+
+# ------------------------------------------------------------------ paged cache helpers
+class PagedCase:
+    """Random K/V for sequences of given lengths, scattered over shuffled pages."""
+
+    def __init__(self, lens, Hkv, hd, dtype, seed, page_size=64, extra_pages=3):
+        rng = np.random.default_rng(seed)
+        self.lens, self.Hkv, self.hd, self.page_size = lens, Hkv, hd, page_size
+        n_seq = len(lens)
+        pages_per = [-(-n // page_size) for n in lens]
+        n_pages = sum(pages_per) + extra_pages
+        perm = rng.permutation(n_pages)
+        self.k = [_rand((n, Hkv, hd), dtype, seed * 100 + i) for i, n in enumerate(lens)]
+        self.v = [_rand((n, Hkv, hd), dtype, seed * 100 + 50 + i) for i, n in enumerate(lens)]
+        # Unused memory is poisoned so that a read outside a sequence's keys shows.
+        self.k_pages = torch.full((n_pages, Hkv, page_size, hd), float("nan"), dtype=dtype, device=DEV)
+        self.v_pages = torch.full((n_pages, Hkv, page_size, hd), float("nan"), dtype=dtype, device=DEV)
+        self.n_slots = n_seq + 2
+        self.slot_of = [int(s) for s in rng.permutation(self.n_slots)[:n_seq]]
+        table = np.full((self.n_slots, max(pages_per) + 1), -1, dtype=np.int32)
+        nxt = 0
+        for i, n in enumerate(lens):
+            for p in range(pages_per[i]):
+                page = int(perm[nxt]); nxt += 1
+                table[self.slot_of[i], p] = page
+                lo, hi = p * page_size, min(n, (p + 1) * page_size)
+                self.k_pages[page, :, :hi - lo] = self.k[i][lo:hi].transpose(0, 1)
+                self.v_pages[page, :, :hi - lo] = self.v[i][lo:hi].transpose(0, 1)
+        self.table = torch.from_numpy(table).to(DEV)
+        self.slots = torch.tensor(self.slot_of, dtype=torch.int32, device=DEV)
+
+    def reference(self, q, tok_seq, tok_pos, H, scale, window):
+        """q [T, H, hd] float; plain softmax attention of each row over keys start..pos."""
+        out = torch.empty_like(q, dtype=torch.float64)
+        G = H // self.Hkv
+        for r in range(q.shape[0]):
+            s, p = tok_seq[r], tok_pos[r]
+            start = p - window + 1 if (window and p >= window) else 0
+            k = self.k[s][start:p + 1].double()
+            v = self.v[s][start:p + 1].double()
+            for h in range(H):
+                sc = (k[:, h // G] @ q[r, h].double()) * scale
+                out[r, h] = torch.softmax(sc, 0) @ v[:, h // G]
+        return out
+
+
+def _ints(x):
+    return torch.tensor(x, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,Hkv,hd,window", [(6, 2, 48, None), (4, 4, 16, 37), (8, 1, 128, None), (2, 1, 256, None)])
+def test_attention_plain(dtype, H, Hkv, hd, window):
+    ops = _ops()
+    lens = [130, 1, 77]
+    case = PagedCase(lens, Hkv, hd, dtype, seed=1)
+    tok_seq = [0, 0, 0, 1, 2, 2]
+    tok_pos = [129, 64, 0, 0, 76, 63]
+    q = _rand((len(tok_seq), H * hd + 16), dtype, 77)     # wider rows: q is a slice of a qkv buffer
+    scale = hd ** -0.5
+    out = ops.attention_plain(q, case.k_pages, case.v_pages, case.table, _ints(tok_pos), _ints(tok_seq), case.slots,
+                              H, Hkv, hd, case.page_size, scale, window)
+    ref = case.reference(q[:, :H * hd].reshape(-1, H, hd).float(), tok_seq, tok_pos, H, scale, window)
+    _close(out.reshape(-1, H, hd), ref, 2e-6 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_kv_write(dtype):
+    ops = _ops()
+    H, Hkv, hd, page = 3, 2, 32, 64
+    T = 5
+    tok_seq, tok_pos = [0, 0, 1, 1, 1], [63, 64, 0, 1, 130]
+    lens = [65, 131]
+    case = PagedCase(lens, Hkv, hd, dtype, seed=2)
+    k_before = case.k_pages.clone()
+    qkv = _rand((T, (H + 2 * Hkv) * hd), dtype, 5)
+    orig = qkv.clone()
+    freqs = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)
+    ang = torch.arange(200, dtype=torch.float64)[:, None] * freqs[None]
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    ops.rope_kv_write(qkv, cos, sin, _ints(tok_pos), _ints(tok_seq), case.slots, case.table, case.k_pages,
+                      case.v_pages, H, Hkv, hd, page)
+    x = orig.float().reshape(T, H + 2 * Hkv, hd)
+    c, s = cos[torch.tensor(tok_pos)].unsqueeze(1), sin[torch.tensor(tok_pos)].unsqueeze(1)
+    x0, x1 = x[:, :H + Hkv, :hd // 2], x[:, :H + Hkv, hd // 2:]
+    rot = torch.cat([x0 * c - x1 * s, x0 * s + x1 * c], dim=-1)
+    tol, rel = 1e-6, (0.0 if dtype == torch.float32 else BF16_ULP)
+    _close(qkv.reshape(T, H + 2 * Hkv, hd)[:, :H + Hkv], rot, tol, rel)
+    assert torch.equal(qkv.reshape(T, H + 2 * Hkv, hd)[:, H + Hkv:], orig.reshape(T, H + 2 * Hkv, hd)[:, H + Hkv:])
+    changed = torch.zeros_like(case.k_pages, dtype=torch.bool)
+    for r in range(T):
+        slot = case.slot_of[tok_seq[r]]
+        pg = int(case.table[slot, tok_pos[r] // page])
+        _close(case.k_pages[pg, :, tok_pos[r] % page], rot[r, H:], tol, rel)
+        assert torch.equal(case.v_pages[pg, :, tok_pos[r] % page], orig.reshape(T, H + 2 * Hkv, hd)[r, H + Hkv:])
+        changed[pg, :, tok_pos[r] % page] = True
+    # Nothing else in the cache was touched.
+    same = (case.k_pages == k_before) | (case.k_pages.isnan() & k_before.isnan())
+    assert bool((same | changed).all())
+
+
+# ------------------------------------------------------------------ bfloat16 tensor-core kernels
+@pytest.mark.parametrize("M", [1, 3, 8, 17, 33, 64])
+@pytest.mark.parametrize("N,K", [(16, 64), (100, 200), (4104, 4096), (250, 80)])
+def test_gemm_skinny(M, N, K):
+    ops = _ops()
+    a, w = _rand((M, K), torch.bfloat16, 10), _rand((N, K), torch.bfloat16, 11)
+    ref = a.float().double() @ w.float().double().T
+    _close(ops.gemm_skinny(a, w, ops.EPI_F32), ref, 2e-5)
+    _close(ops.gemm_skinny(a, w, ops.EPI_BF16), ref, 2e-5, BF16_ULP)
+    res = _rand((M, N), torch.float32, 12)
+    expect = res.double() + ref
+    _close(ops.gemm_skinny(a, w, ops.EPI_RESID, residual=res), expect, 2e-5)
+
+
+@pytest.mark.parametrize("M,F,K", [(1, 8, 64), (5, 176, 64), (64, 1000, 328)])
+def test_gemm_skinny_swiglu(M, F, K):
+    ops = _ops()
+    from longbow_quarrel_b200.kernels.linear import interleave_gate_up
+    a = _rand((M, K), torch.bfloat16, 13)
+    wg, wu = _rand((F, K), torch.bfloat16, 14, 0.2), _rand((F, K), torch.bfloat16, 15, 0.2)
+    g = a.float().double() @ wg.float().double().T
+    u = a.float().double() @ wu.float().double().T
+    ref = u * (g / (1 + torch.exp(-g)))
+    out = ops.gemm_skinny(a, interleave_gate_up(wg, wu), ops.EPI_SWIGLU)
+    assert out.shape == (M, F)
+    _close(out, ref, 1e-4, BF16_ULP)
+
+
+def test_gemm_skinny_is_independent_of_other_rows():
+    ops = _ops()
+    a, w = _rand((37, 328), torch.bfloat16, 16), _rand((90, 328), torch.bfloat16, 17)
+    full = ops.gemm_skinny(a, w, ops.EPI_F32)
+    for r in (0, 11, 36):
+        assert torch.equal(ops.gemm_skinny(a[r:r + 1].contiguous(), w, ops.EPI_F32)[0], full[r])
+
+
+@pytest.mark.parametrize("H,Hkv,hd,window", [(8, 2, 128, None), (6, 2, 48, None), (4, 4, 16, 37), (3, 1, 32, None),
+                                             (40, 2, 64, 100), (8, 8, 80, None)])
+@pytest.mark.parametrize("n_splits", [1, 3, 8])
+def test_attn_decode(H, Hkv, hd, window, n_splits):
+    ops = _ops()
+    lens = [300, 1, 77, 64, 17]
+    case = PagedCase(lens, Hkv, hd, torch.bfloat16, seed=3)
+    tok_seq = [0, 1, 2, 3, 4, 0]
+    tok_pos = [299, 0, 76, 63, 16, 150]
+    q = _rand((len(tok_seq), (H + 2 * Hkv) * hd), torch.bfloat16, 78)
+    scale = hd ** -0.5
+    out = ops.attn_decode(q, case.k_pages, case.v_pages, case.table, _ints(tok_pos), _ints(tok_seq), case.slots,
+                          H, Hkv, hd, case.page_size, scale, window, n_splits)
+    ref = case.reference(q[:, :H * hd].reshape(-1, H, hd).float(), tok_seq, tok_pos, H, scale, window)
+    _close(out.reshape(-1, H, hd), ref, 1e-2)
+
+
+@pytest.mark.parametrize("far_key", [0, 5, 250, 511, 700])
+def test_attn_decode_finds_a_far_key(far_key):
+    """One key among hundreds is made to stand out; the output must be its value."""
+    ops = _ops()
+    H, Hkv, hd = 4, 2, 64
+    n = 701
+    case = PagedCase([n], Hkv, hd, torch.bfloat16, seed=4)
+    q = _rand((1, H * hd), torch.bfloat16, 79)
+    # Put a scaled copy of each head's query into the far key of its kv head (both heads of a
+    # group then share it: use the group's first head and check that head).
+    G = H // Hkv
+    slot = case.slot_of[0]
+    page = int(case.table[slot, far_key // 64])
+    for kvh in range(Hkv):
+        qh = q[0, (kvh * G) * hd:(kvh * G + 1) * hd].float()
+        key = (qh / qh.norm() * 40.0).to(torch.bfloat16)
+        case.k_pages[page, kvh, far_key % 64] = key
+        case.k[0][far_key, kvh] = key
+    scale = 1.0
+    for n_splits in (1, 4):
+        out = ops.attn_decode(q, case.k_pages, case.v_pages, case.table, _ints([n - 1]), _ints([0]), case.slots,
+                              H, Hkv, hd, 64, scale, None, n_splits).reshape(H, hd)
+        for kvh in range(Hkv):
+            _close(out[kvh * G], case.v[0][far_key, kvh], 2e-2)
