@@ -18,7 +18,9 @@ from ..kernels import ops
 from ..parts.base import Runtime
 from ..weights import load_weights, random_weights
 from .model import Model
-from .step import run_step
+from ..sampling import SamplingParams
+from .generate import GenerationStats, generate
+from .step import Stepper
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
            torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
@@ -39,9 +41,11 @@ def _device(device) -> torch.device:
 
 
 class Engine:
-    def __init__(self, arch, config, model: Model, cache: Cache, runtime: Runtime):
+    def __init__(self, arch, config, model: Model, cache: Cache, runtime: Runtime, use_graphs: bool = True):
         self.arch, self.config, self.model, self.cache, self.runtime = arch, config, model, cache, runtime
         self.device = runtime.device
+        self.stepper = Stepper(model, cache, self.device, use_graphs=use_graphs)
+        self.last_stats: GenerationStats | None = None
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -98,7 +102,25 @@ class Engine:
         prompts or one token each; want = for each entry the places among its tokens whose
         logits are asked for (None: each entry's last).  Returns float32 [n_wanted, vocab]."""
         with torch.cuda.device(self.device):
-            return run_step(self.model, self.cache, entries, want, self.device)
+            return self.stepper.step(entries, want)
+
+    # ------------------------------------------------------------------ generation
+    def generate(self, prompts, max_new_tokens: int = 20, sampling: SamplingParams | None = None, stop_ids=None,
+                 callback=None, include_stop: bool = False, batch_size: int | None = None) -> list[list[int]]:
+        """New tokens for each prompt (lists of token ids).  Prompts are run in batches of
+        at most batch_size that start together; a sequence ends at a stop token (by default
+        the model's eos ids; the stop token is not returned), after max_new_tokens, or when
+        the context is full.  callback(prompt index, token id) is called for every token.
+        Counterpart of Infer / InferWithCallback (internal/engine/engine.go:1277-1290)."""
+        from .backend import EngineBackend
+        sampling = sampling or SamplingParams()
+        stops = tuple(self.model.spec.stop_tokens) if stop_ids is None else tuple(stop_ids)
+        with torch.cuda.device(self.device):
+            outputs, stats = generate(EngineBackend(self, sampling), prompts, max_new_tokens, stops, callback,
+                                      include_stop, batch_size or self.cache.max_slots,
+                                      self.runtime.max_context)
+        self.last_stats = stats
+        return outputs
 
     def close(self) -> None:
         self.model = None

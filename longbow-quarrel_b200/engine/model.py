@@ -61,6 +61,11 @@ class Model:
                 mine[tied] = tensors[tied]
             part.load(mine)
 
+    @property
+    def graph_safe(self) -> bool:
+        """Every part allows its steps to be captured in a CUDA graph."""
+        return all(part.graph_safe for _, part in self._named_parts())
+
     def cache_needs(self) -> dict:
         """Cache entry -> what the mixer that writes it needs."""
         return {e.cache: self.blocks[e.layer].mixer.cache_need() for e in self.spec.schedule if e.writes_cache}

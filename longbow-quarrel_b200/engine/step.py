@@ -88,18 +88,90 @@ def make_context(flat_dev: torch.Tensor, info: dict, h_slots: list[int]) -> Step
                        h_past=info["past"], max_new=info["max_new"], max_kv=info["max_kv"])
 
 
-def run_step(model, cache: Cache, entries, want, device) -> torch.Tensor | None:
-    """entries: [(slot, tokens)], want: [[places]] or None (= each sequence's last token).
-    Returns logits [n_wanted, vocab] float32 in the order of entries and of want."""
-    check_entries(entries, want, model.spec.vocab_size)
-    past = [cache.length(slot) for slot, _ in entries]
-    for slot, tokens in entries:
-        cache.reserve(slot, len(tokens))
-    cache.upload()
-    flat, info = pack_step(entries, want, past)
-    flat_dev = torch.from_numpy(flat).to(device)
-    ctx = make_context(flat_dev, info, [s for s, _ in entries])
-    logits = model.forward(ctx, cache)
-    for slot, tokens in entries:
-        cache.commit(slot, len(tokens))
-    return logits
+class Stepper:
+    """Runs steps of one model on one cache.  Steps in which every sequence brings one
+    token are captured once per batch size in a CUDA graph and replayed, because such a
+    step is a few hundred short kernels whose launches would otherwise cost more than
+    their work; all other steps launch their kernels one by one."""
+
+    def __init__(self, model, cache: Cache, device, use_graphs: bool = True):
+        self.model, self.cache, self.device = model, cache, device
+        self.use_graphs = use_graphs and model.graph_safe
+        self._graphs: dict[int, "_DecodeGraph"] = {}
+        self._seen: set[int] = set()
+
+    def step(self, entries, want=None) -> torch.Tensor | None:
+        """entries: [(slot, tokens)], want: [[places]] or None (= each sequence's last token).
+        Returns logits [n_wanted, vocab] float32 in the order of entries and of want."""
+        check_entries(entries, want, self.model.spec.vocab_size)
+        past = [self.cache.length(slot) for slot, _ in entries]
+        for slot, tokens in entries:
+            self.cache.reserve(slot, len(tokens))
+        self.cache.upload()
+        B = len(entries)
+        decode = all(len(t) == 1 for _, t in entries)
+        if decode and self.use_graphs:
+            logits = self._decode_step(entries, want, past)
+        else:
+            flat, info = pack_step(entries, want, past)
+            flat_dev = torch.from_numpy(flat).to(self.device)
+            ctx = make_context(flat_dev, info, [s for s, _ in entries])
+            logits = self.model.forward(ctx, self.cache)
+        for slot, tokens in entries:
+            self.cache.commit(slot, len(tokens))
+        return logits
+
+    def _decode_step(self, entries, want, past):
+        B = len(entries)
+        flat, info = pack_step(entries, None, past)
+        if B not in self._seen:
+            # The first step of a batch size runs eagerly: it loads kernels and sizes buffers.
+            self._seen.add(B)
+            flat_dev = torch.from_numpy(flat).to(self.device)
+            logits = self.model.forward(make_context(flat_dev, info, [s for s, _ in entries]), self.cache)
+        else:
+            graph = self._graphs.get(B)
+            if graph is None:
+                graph = self._graphs[B] = _DecodeGraph(self.model, self.cache, self.device, flat, info)
+            logits = graph.replay(flat)
+        if want is None:
+            return logits
+        rows = [b for b, ws in enumerate(want) for _ in ws]
+        if rows == list(range(B)):
+            return logits
+        if not rows:
+            return None
+        return logits[torch.tensor(rows, device=self.device)]
+
+
+class _DecodeGraph:
+    """One captured step for a batch of B sequences with one token each.  The integers
+    of a step (tokens, positions, slots) are copied into the buffer the graph reads."""
+
+    def __init__(self, model, cache, device, flat: np.ndarray, info: dict):
+        self.device = device
+        self.host = torch.empty(len(flat), dtype=torch.int32).pin_memory()
+        self.flat_dev = torch.zeros(len(flat), dtype=torch.int32, device=device)
+        self.copied = torch.cuda.Event()
+        self.info = dict(info)
+        # Kernels that size their work by the longest sequence are captured for the longest possible one.
+        self.info["max_kv"] = cache.max_context
+        self.host.numpy()[:] = flat
+        self.flat_dev.copy_(self.host, non_blocking=True)
+        ctx = make_context(self.flat_dev, self.info, list(range(info["B"])))
+        self.graph = torch.cuda.CUDAGraph()
+        stream = torch.cuda.Stream(device=device)
+        stream.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(self.graph, stream=stream):
+                self.logits = model.forward(ctx, cache)
+        torch.cuda.current_stream(device).wait_stream(stream)
+        self.copied.record()
+
+    def replay(self, flat: np.ndarray) -> torch.Tensor:
+        self.copied.synchronize()
+        self.host.numpy()[:] = flat
+        self.flat_dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
+        self.graph.replay()
+        return self.logits

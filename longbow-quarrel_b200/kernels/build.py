@@ -49,18 +49,25 @@ def _sources_hash(name: str, extra_flags: list[str]) -> str:
     return h.hexdigest()[:16]
 
 
+_dir: Path | None = None
+_dir_lock = threading.Lock()
+
+
 def _build_dir() -> Path:
-    d = CSRC / "_build"
-    try:
-        d.mkdir(exist_ok=True)
-        probe = d / f".w{os.getpid()}"
-        probe.write_text("")
-        probe.unlink()
-        return d
-    except OSError:
-        d = Path(tempfile.gettempdir()) / f"longbow_quarrel_b200_build_{os.getuid()}"
-        d.mkdir(exist_ok=True)
-        return d
+    """csrc/_build when it can be written, else a per-user folder under the temp dir."""
+    global _dir
+    with _dir_lock:
+        if _dir is None:
+            d = CSRC / "_build"
+            try:
+                d.mkdir(exist_ok=True)
+                with tempfile.NamedTemporaryFile(dir=d, prefix=".probe"):
+                    pass
+            except OSError:
+                d = Path(tempfile.gettempdir()) / f"longbow_quarrel_b200_build_{os.getuid()}"
+                d.mkdir(exist_ok=True)
+            _dir = d
+        return _dir
 
 
 def library_path(name: str, extra_flags: list[str] | None = None) -> Path:

@@ -27,6 +27,8 @@ DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight
 
 @register_part("mixer", "attention")
 class Attention(Mixer):
+    graph_safe = True
+
     def __init__(self, runtime: Runtime, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  scale: float, position: PartSpec | None = None, window: int | None = None,
                  own_kv: bool = True, names: dict | None = None):

@@ -55,7 +55,14 @@ class StepContext:
 
 
 class Part:
-    """Base of all parts."""
+    """Base of all parts.
+
+    graph_safe: the part's forward launches the same work for every step of a batch
+    size and reads positions, slots and lengths from the step context's device tensors
+    only, so a step that contains it may be captured in a CUDA graph and replayed.  A
+    part that looks at the context's host lists must leave this False."""
+
+    graph_safe = False
 
     def weights(self) -> dict[str, WeightSpec]:
         """Tensor name (relative to the part's prefix) -> what it must look like."""

@@ -22,6 +22,10 @@ class PreNormBlock(Part):
     def parts(self):
         return (self.norm1, self.mixer, self.norm2, self.ffn)
 
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts())
+
     def weights(self):
         out = {}
         for part in self.parts():

@@ -18,6 +18,8 @@ from .registry import register_part
 
 @register_part("embedding", "token_embedding")
 class TokenEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, runtime: Runtime, vocab_size: int, hidden_size: int, name: str):
         self.runtime, self.vocab_size, self.hidden_size, self.name = runtime, vocab_size, hidden_size, name
         self.table: torch.Tensor | None = None
@@ -36,6 +38,8 @@ class TokenEmbedding(Part):
 class LinearHead(Part):
     """`tied_to` names the tensor (of another part) that the head reads when it has
     none of its own; with `tied` true it never has its own."""
+
+    graph_safe = True
 
     def __init__(self, runtime: Runtime, vocab_size: int, hidden_size: int, name: str, tied_to: str | None = None,
                  tied: bool = False):

@@ -15,6 +15,8 @@ DEFAULT_NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "do
 
 @register_part("ffn", "gated_mlp")
 class GatedMLP(FeedForward):
+    graph_safe = True
+
     def __init__(self, runtime: Runtime, hidden_size: int, intermediate_size: int, activation: str = "silu",
                  names: dict | None = None):
         if activation != "silu":

@@ -13,6 +13,8 @@ from .registry import register_part
 
 @register_part("norm", "rms_norm")
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, runtime: Runtime, size: int, eps: float, name: str = "weight"):
         self.runtime, self.size, self.eps, self.name = runtime, size, float(eps), name
         self.gain: torch.Tensor | None = None

@@ -35,6 +35,8 @@ def rope_frequencies(head_dim: int, theta: float, scaling=None) -> torch.Tensor:
 
 @register_part("position", "rope")
 class Rope(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, runtime: Runtime, head_dim: int, theta: float, scaling=None):
         self.runtime, self.head_dim, self.theta, self.scaling = runtime, head_dim, float(theta), scaling
         self._tables = None

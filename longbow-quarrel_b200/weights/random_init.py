@@ -48,9 +48,8 @@ def _numel(shape) -> int:
 
 def random_weights(table: dict[str, WeightSpec], seed: int, dtype: torch.dtype = torch.bfloat16,
                    device="cpu", std: float = 0.02, gain_std: float = 0.1) -> dict[str, torch.Tensor]:
-    """Every tensor of `table`; a tensor with a fallback (a tied head) is not made."""
-    return {name: random_tensor(name, spec, seed, dtype, device, std, gain_std)
-            for name, spec in table.items() if spec.fallback is None}
+    """Every tensor of `table` (a tied head has no entry in its model's table)."""
+    return {name: random_tensor(name, spec, seed, dtype, device, std, gain_std) for name, spec in table.items()}
 
 
 def write_random_model(folder, config_dict: dict, table: dict[str, WeightSpec], seed: int,

@@ -221,16 +221,13 @@ def greedy(cfg: dict, weights: dict, prompt, n_new: int, stop=()) -> list[int]:
 
 # --------------------------------------------------------------------------- sampling
 
-def sample_reference(logits, temperature, top_k, top_p, u: float) -> int:
-    """The reference sampler's decision for one uniform draw u in [0, 1):
-    greedy at temperature 0; softmax(logits / T) in float64; drop p <= 1e-10; sort
-    by falling probability; keep the first k; keep the shortest prefix whose sum
-    reaches top_p and renormalise; walk the cumulative sum until r < acc:
-    internal/engine/sampler.go:72-105,125-184,309-339.  Ties are ordered by index
-    here (the reference's sort leaves them unspecified)."""
+def kept_set(logits, temperature, top_k, top_p):
+    """The tokens the reference sampler keeps, and their probabilities:
+    softmax(logits / T) in float64; drop p <= 1e-10; sort by falling probability; keep
+    the first k; keep the shortest prefix whose sum reaches top_p and renormalise:
+    internal/engine/sampler.go:125-166,309-339.  Ties are ordered by index here (the
+    reference's sort leaves their order open).  Returned in index order."""
     logits = np.asarray(logits, dtype=np.float64)
-    if temperature == 0:
-        return int(np.argmax(logits))
     z = logits / temperature
     p = np.exp(z - z.max())
     p /= p.sum()
@@ -241,16 +238,43 @@ def sample_reference(logits, temperature, top_k, top_p, u: float) -> int:
     probs = np.array([p[i] for i in ids])
     if 0.0 < top_p < 1.0:
         c = np.cumsum(probs)
-        n = int(np.searchsorted(c, top_p, side="left")) + 1
-        n = min(n, len(ids))
-        ids, probs = ids[:n], probs[:n] / probs[:n].sum()
-    r = u * probs.sum()
+        if c[-1] >= top_p:
+            n = int(np.searchsorted(c, top_p, side="left")) + 1
+            ids, probs = ids[:n], probs[:n] / probs[:n].sum()
+    order = np.argsort(ids)
+    return [int(ids[i]) for i in order], [float(probs[i]) for i in order]
+
+
+def sample_reference(logits, temperature, top_k, top_p, u: float) -> int:
+    """The decision for one uniform draw u in [0, 1): greedy at temperature 0
+    (internal/engine/sampler.go:81-84); else r = u * sum of the kept probabilities and a
+    walk along their cumulative sum until r < acc (sampler.go:168-184).  The reference
+    walks in sorted order; the walk here is in index order, which draws from the same
+    distribution."""
+    if temperature == 0:
+        return int(np.argmax(np.asarray(logits, dtype=np.float64)))
+    ids, probs = kept_set(logits, temperature, top_k, top_p)
+    r = u * sum(probs)
     acc = 0.0
     for i, pi in zip(ids, probs):
         acc += pi
         if r < acc:
             return int(i)
-    return int(ids[0])
+    return int(ids[-1])
+
+
+def philox_uniform(seed: int, sequence: int, step: int) -> float:
+    """Philox4x32-10 with key = seed and counter = (sequence, step, 0, 0); the first two
+    output words give a 53-bit uniform number in [0, 1) (public algorithm of Salmon et al.,
+    "Parallel random numbers: as easy as 1, 2, 3")."""
+    M0, M1, W0, W1 = 0xD2511F53, 0xCD9E8D57, 0x9E3779B9, 0xBB67AE85
+    c = [sequence & 0xFFFFFFFF, step & 0xFFFFFFFF, 0, 0]
+    k0, k1 = seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF
+    for _ in range(10):
+        p0, p1 = M0 * c[0], M1 * c[2]
+        c = [(p1 >> 32) ^ c[1] ^ k0, p1 & 0xFFFFFFFF, (p0 >> 32) ^ c[3] ^ k1, p0 & 0xFFFFFFFF]
+        k0, k1 = (k0 + W0) & 0xFFFFFFFF, (k1 + W1) & 0xFFFFFFFF
+    return (((c[0] >> 5) << 26) | (c[1] >> 6)) / float(1 << 53)
 
 
 def repetition_penalty(logits, history, penalty: float):

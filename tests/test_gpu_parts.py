@@ -1,0 +1,231 @@
+"""Each part alone against the plain implementation's function for it, and a toy
+mixer with state of its own that is registered from here."""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+from helpers import rel_err
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def _runtime(dtype, max_context=256):
+    from longbow_quarrel_b200.parts.base import Runtime
+    return Runtime(DEV, dtype, max_context)
+
+
+def _ctx(entries, past):
+    from longbow_quarrel_b200.engine.step import make_context, pack_step
+    flat, info = pack_step(entries, None, past)
+    return make_context(torch.from_numpy(flat).to(DEV), info, [s for s, _ in entries])
+
+
+def _rand(shape, seed, std=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * std).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from longbow_quarrel_b200.parts.norm import RMSNorm
+    part = RMSNorm(_runtime(dtype), size=88, eps=3e-4, name="g")
+    assert part.weights()["g"].shape == (88,)
+    gain = 1 + 0.1 * _rand((88,), 1)
+    part.load({"g": gain.to(torch.bfloat16).to(DEV)})          # gains stored in bfloat16 are read as such
+    x = _rand((5, 88), 2, 2.0)
+    ref = pl.rms_norm(x.double(), gain.to(torch.bfloat16).double(), 3e-4)
+    out = part.forward(x.to(DEV))
+    assert out.dtype == dtype
+    assert rel_err(out.float().cpu().numpy(), ref.numpy()) < (1e-6 if dtype == torch.float32 else 2e-2)
+
+
+def test_rope_part_tables():
+    from longbow_quarrel_b200.config import RopeScaling
+    from longbow_quarrel_b200.parts.rope import Rope, rope_frequencies
+    sc = RopeScaling("llama3", 8.0, 1.0, 4.0, 64)
+    f = rope_frequencies(32, 500000.0, sc).numpy()
+    ref = pl.rope_frequencies(32, 500000.0, dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0,
+                                                 high_freq_factor=4.0, original_max_position_embeddings=64))
+    assert np.allclose(f, ref, rtol=1e-14)
+    part = Rope(_runtime(torch.float32, 200), head_dim=32, theta=500000.0, scaling=sc)
+    cos, sin = part.tables()
+    assert cos.shape == (200, 16) and cos.dtype == torch.float32
+    ang = np.arange(200)[:, None] * ref[None]
+    assert np.abs(cos.cpu().numpy() - np.cos(ang)).max() < 1e-7 and np.abs(sin.cpu().numpy() - np.sin(ang)).max() < 1e-7
+    assert Rope(part.runtime, 32, 500000.0, sc).tables()[0] is cos        # equal parts share one table
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 20])
+def test_attention_part(dtype, window):
+    """Two sequences of unequal length in one step, then one more token each."""
+    from longbow_quarrel_b200.cache import Cache
+    from longbow_quarrel_b200.parts.attention import Attention
+    from longbow_quarrel_b200.parts.spec import PartSpec
+    D, H, Hkv, hd = 72, 6, 2, 16
+    rt = _runtime(dtype)
+    part = Attention(rt, hidden_size=D, n_heads=H, n_kv_heads=Hkv, head_dim=hd, scale=0.31, window=window,
+                     position=PartSpec("rope", {"head_dim": hd, "theta": 10000.0, "scaling": None}))
+    w = {n: _rand(s.shape, i, 0.15, torch.bfloat16) for i, (n, s) in enumerate(part.weights().items())}
+    part.load({n: t.to(DEV) for n, t in w.items()})
+    cache = Cache({0: part.cache_need()}, 1024, 256, dtype, DEV)
+    lens = [37, 70]
+    xs = [_rand((n + 1, D), 10 + i, 1.0, torch.bfloat16).float() for i, n in enumerate(lens)]
+
+    def plain(x):
+        T = x.shape[0]
+        x = x.double()
+        q = pl.linear(x, w["q_proj.weight"].double()).reshape(T, H, hd)
+        k = pl.linear(x, w["k_proj.weight"].double()).reshape(T, Hkv, hd)
+        v = pl.linear(x, w["v_proj.weight"].double()).reshape(T, Hkv, hd)
+        f = pl.rope_frequencies(hd, 10000.0, None)
+        a = pl.attention(pl.rope(q, np.arange(T), f), pl.rope(k, np.arange(T), f), v, 0.31, window)
+        return pl.linear(a.reshape(T, H * hd), w["o_proj.weight"].double())
+
+    refs = [plain(x) for x in xs]
+    slots = [cache.alloc_slot() for _ in lens]
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    # the prompts together
+    for s, n in zip(slots, lens):
+        cache.reserve(s, n)
+    cache.upload()
+    ctx = _ctx([(s, [0] * n) for s, n in zip(slots, lens)], [0, 0])
+    h = torch.cat([x[:n] for x, n in zip(xs, lens)]).to(dtype).to(DEV)
+    resid = torch.zeros((sum(lens), D), dtype=torch.float32, device=DEV)
+    part.forward(h, ctx, cache.view(0), resid)
+    for s, n in zip(slots, lens):
+        cache.commit(s, n)
+    got = resid.cpu().numpy()
+    assert rel_err(got[:lens[0]], refs[0][:lens[0]].numpy()) < tol
+    assert rel_err(got[lens[0]:], refs[1][:lens[1]].numpy()) < tol
+    # one more token each, added onto a residual that is not zero
+    for s in slots:
+        cache.reserve(s, 1)
+    cache.upload()
+    ctx = _ctx([(s, [0]) for s in slots], lens)
+    h = torch.stack([x[n] for x, n in zip(xs, lens)]).to(dtype).to(DEV)
+    resid = torch.ones((2, D), dtype=torch.float32, device=DEV)
+    part.forward(h, ctx, cache.view(0), resid)
+    got = resid.cpu().numpy() - 1.0
+    for i in range(2):
+        assert rel_err(got[i], refs[i][lens[i]].numpy()) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,F", [(3, 176), (70, 44)])
+def test_feed_forward_part(dtype, T, F):
+    from longbow_quarrel_b200.parts.mlp import GatedMLP
+    D = 56
+    part = GatedMLP(_runtime(dtype), hidden_size=D, intermediate_size=F)
+    w = {n: _rand(s.shape, i, 0.2, torch.bfloat16) for i, (n, s) in enumerate(part.weights().items())}
+    part.load({n: t.to(DEV) for n, t in w.items()})
+    x = _rand((T, D), 7, 1.0, torch.bfloat16).float()
+    ref = pl.linear(pl.swiglu(pl.linear(x.double(), w["gate_proj.weight"].double()),
+                              pl.linear(x.double(), w["up_proj.weight"].double())), w["down_proj.weight"].double())
+    resid = torch.full((T, D), 2.0, dtype=torch.float32, device=DEV)
+    part.forward(x.to(dtype).to(DEV), None, resid)
+    assert rel_err(resid.cpu().numpy() - 2.0, ref.numpy()) < (2e-5 if dtype == torch.float32 else 3e-2)
+
+
+def test_embedding_and_head_parts():
+    from longbow_quarrel_b200.parts.embedding import LinearHead, TokenEmbedding
+    rt = _runtime(torch.float32)
+    emb = TokenEmbedding(rt, vocab_size=50, hidden_size=24, name="E")
+    table = _rand((50, 24), 1, 1.0, torch.bfloat16)
+    emb.load({"E": table.to(DEV)})
+    toks = torch.tensor([3, 49, 0], dtype=torch.int32, device=DEV)
+    assert torch.equal(emb.forward(toks).cpu(), table[[3, 49, 0]].float())
+    tied = LinearHead(rt, vocab_size=50, hidden_size=24, name="H", tied_to="E", tied=True)
+    assert tied.weights() == {}
+    tied.load({"E": table.to(DEV)})
+    h = _rand((4, 24), 2)
+    assert rel_err(tied.forward(h.to(DEV)).cpu().numpy(), (h.double() @ table.double().T).numpy()) < 1e-5
+    own = LinearHead(rt, vocab_size=50, hidden_size=24, name="H", tied_to="E")
+    assert own.weights()["H"].fallback == "E"
+
+
+# ------------------------------------------------------------------ a toy mixer with state of its own
+def test_a_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    """A mixer that keeps a running sum of its inputs per sequence (fixed-size state, no
+    keys or values) is defined here, registered, put into a two-layer model beside an
+    attention layer, and stepped in every way of cutting -- no framework file changes."""
+    from dataclasses import dataclass
+
+    from longbow_quarrel_b200.config import register_architecture
+    from longbow_quarrel_b200.engine import Engine
+    from longbow_quarrel_b200.parts import (LayerSpec, Mixer, ModelSpec, PartSpec, ScheduleEntry, StateNeed,
+                                            register_part)
+    from longbow_quarrel_b200.weights import WeightSpec
+
+    @register_part("mixer", "toy_running_sum")
+    class RunningSum(Mixer):
+        """out_t = (state + sum of inputs up to t) * mix / (position + 1); state carries over."""
+
+        def __init__(self, runtime, hidden_size):
+            self.runtime, self.D, self.mix = runtime, hidden_size, None
+
+        def weights(self):
+            return {"mix": WeightSpec((self.D,), init="gain")}
+
+        def load(self, tensors):
+            self.mix = tensors["mix"].float()
+
+        def cache_need(self):
+            return StateNeed((self.D,), torch.float32)
+
+        def forward(self, h, ctx, state, residual, writes_cache=True):
+            h = h.float()
+            row = 0
+            for b, n in enumerate(ctx.h_new):
+                slot = ctx.h_slots[b]
+                run = state[slot] + torch.cumsum(h[row:row + n], dim=0)
+                pos = torch.arange(ctx.h_past[b], ctx.h_past[b] + n, device=h.device, dtype=torch.float32)
+                residual[row:row + n] += run * self.mix / (pos[:, None] + 1.0)
+                state[slot] = run[-1]
+                row += n
+
+    @dataclass(frozen=True)
+    class ToyConfig:
+        hidden_size: int
+        vocab_size: int
+        architectures: tuple = ("ToyStateLM",)
+
+    def describe(cfg):
+        norm = lambda name: PartSpec("rms_norm", {"size": cfg.hidden_size, "eps": 1e-5, "name": name})  # noqa: E731
+        ffn = PartSpec("gated_mlp", {"hidden_size": cfg.hidden_size, "intermediate_size": 48})
+        attn = PartSpec("attention", {"hidden_size": cfg.hidden_size, "n_heads": 2, "n_kv_heads": 1, "head_dim": 16,
+                                      "scale": 0.25, "position": PartSpec("rope", {"head_dim": 16, "theta": 1e4})})
+        layers = (LayerSpec("l0.", PartSpec("toy_running_sum", {"hidden_size": cfg.hidden_size}), ffn, norm("n1"), norm("n2")),
+                  LayerSpec("l1.", attn, ffn, norm("n1"), norm("n2")))
+        return ModelSpec(name="ToyStateLM", hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size,
+                         embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size,
+                                                                "hidden_size": cfg.hidden_size, "name": "emb"}),
+                         layers=layers, schedule=(ScheduleEntry(0, 0), ScheduleEntry(1, 1)),
+                         final_norm=norm("fn"),
+                         head=PartSpec("linear_head", {"vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size,
+                                                       "name": "head", "tied_to": "emb", "tied": True}),
+                         max_positions=256)
+
+    register_architecture("ToyStateLM", lambda d: ToyConfig(d["hidden_size"], d["vocab_size"]), describe)
+    eng = Engine.from_config({"architectures": ["ToyStateLM"], "hidden_size": 32, "vocab_size": 100}, seed=3,
+                             dtype="float32", max_tokens=1024, gain_std=0.1)
+    assert len(eng.cache.state_groups) == 1 and len(eng.cache.kv_groups) == 1
+    assert not eng.model.graph_safe and not eng.stepper.use_graphs     # the toy reads host lists
+    toks = [[5, 9, 33, 2, 71, 8, 40], [11, 3, 6]]
+    s = [eng.new_sequence() for _ in toks]
+    whole = eng.step([(s[0], toks[0]), (s[1], toks[1])], want=[list(range(7)), list(range(3))]).cpu().numpy()
+    for slot in s:
+        eng.end_sequence(slot)
+    # the same tokens cut differently, in slots that are used again: state must start from zero and carry over
+    s = [eng.new_sequence() for _ in toks]
+    first = eng.step([(s[0], toks[0][:4]), (s[1], toks[1][:1])], want=[[0, 1, 2, 3], [0]]).cpu().numpy()
+    rest = [eng.step([(s[0], [toks[0][4 + i]])] + ([(s[1], [toks[1][1 + i]])] if i < 2 else [])).cpu().numpy()
+            for i in range(3)]
+    assert np.allclose(first[:4], whole[:4], atol=1e-5) and np.allclose(first[4], whole[7], atol=1e-5)
+    for i in range(3):
+        assert np.allclose(rest[i][0], whole[4 + i], atol=1e-5)
+        if i < 2:
+            assert np.allclose(rest[i][1], whole[8 + i], atol=1e-5)
+    assert not np.allclose(whole[1], whole[0])
