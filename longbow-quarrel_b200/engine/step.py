@@ -14,6 +14,7 @@ import numpy as np
 import torch
 
 from ..cache import Cache, CacheError
+from ..kernels import ops
 from ..parts.base import StepContext
 
 
@@ -162,9 +163,12 @@ class _DecodeGraph:
         self.graph = torch.cuda.CUDAGraph()
         stream = torch.cuda.Stream(device=device)
         stream.wait_stream(torch.cuda.current_stream(device))
+        before = ops.launch_count()
         with torch.cuda.stream(stream):
             with torch.cuda.graph(self.graph, stream=stream):
                 self.logits = model.forward(ctx, cache)
+        self.kernels = ops.launch_count() - before
+        ops.add_launches(-self.kernels)      # recorded, not run
         torch.cuda.current_stream(device).wait_stream(stream)
         self.copied.record()
 
@@ -174,4 +178,5 @@ class _DecodeGraph:
         self.flat_dev.copy_(self.host, non_blocking=True)
         self.copied.record()
         self.graph.replay()
+        ops.add_launches(self.kernels)
         return self.logits

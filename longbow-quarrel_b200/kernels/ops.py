@@ -41,8 +41,24 @@ def _stream():
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _check(code: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels launched so far by this process (replays of a captured step count the
+    kernels the capture recorded)."""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    global _launches
     if code == 0:
+        _launches += kernels
         return
     reason = {-1: "unsupported dtype", -2: "unsupported size", -3: "CUDA driver entry point not found",
               -4: "scratch too small"}.get(code, f"CUDA error {code}")
@@ -231,5 +247,5 @@ def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq,
                                                c_float, c_int, c_int, c_void_p])
     _check(fn(_p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0), _p(tok_pos),
               _p(tok_seq), _p(slots), _p(part_o), _p(part_ml), _p(out), T, H, Hkv, hd, page_size, float(scale),
-              int(window or 0), n_splits, _stream()), "attn_decode")
+              int(window or 0), n_splits, _stream()), "attn_decode", 2 if n_splits > 1 else 1)
     return out
