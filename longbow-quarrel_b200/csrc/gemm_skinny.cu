@@ -50,8 +50,8 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
 
 template <int MT, int EPI>
 __global__ void __launch_bounds__(WARPS * 32)
-gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, void* __restrict__ Cout,
-                   const float* __restrict__ residual, int M, int N, int K) {
+gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, void* Cout,
+                   const float* residual, int M, int N, int K) {
     __shared__ float red[WARPS][ROWS][MT * 8 + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;

@@ -1,0 +1,400 @@
+// y = x . W^T on the fifth-generation tensor cores (tcgen05) for many rows of x
+// (prefill): bfloat16 operands, float32 accumulation in tensor memory.
+//
+// One persistent block per SM walks over 128 x BN output tiles.  Inside a block
+//   warp 0      one lane issues TMA loads (cp.async.bulk.tensor) of the x tile [128, 64] and
+//               the W tile [BN, 64] into a ring of shared-memory stages (128-byte swizzle);
+//   warp 1      one lane issues tcgen05.mma (M 128, N BN, K 16; four per stage) into one of
+//               two accumulators in tensor memory, and frees a stage with tcgen05.commit;
+//   warps 2..5  read a finished accumulator with tcgen05.ld (each thread one row) and store
+//               it, while the next tile's products already run into the other accumulator.
+// Stages and accumulators are handed over through mbarriers.  Every wait is bounded: after
+// about two seconds a role records a code in the status word, leaves its loop, and the
+// block still waits (bounded) for its copies in flight, frees its tensor memory and ends.
+//
+// Epilogues: bfloat16 store; float32 store; float32 residual add in place; SwiGLU over
+// weight rows interleaved in blocks of 8 (8 gate rows, then their 8 up rows).
+//
+// Reference counterpart: the per-row linear_f16 kernels and the library GEMM of
+// internal/device/metal.go:886-964; its CUDA path calls cublasSgemmEx (internal/device/cuda.go:293-318).
+#include "common.cuh"
+#include <cuda.h>
+
+#define EPI_BF16 0
+#define EPI_F32 1
+#define EPI_RESID 2
+#define EPI_SWIGLU 3
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                 // 64 bf16 = 128 bytes: one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int N_THREADS = 192;
+constexpr unsigned long long WAIT_NS = 2000000000ull;
+
+__device__ int g_status = 0;           // 0 = fine; else the code of the wait that gave up
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the phase did not complete within WAIT_NS.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer();
+    for (;;) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try(bar, parity)) return true;
+        if (globaltimer() - t0 > WAIT_NS) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled in
+// 8-row groups of 1024 bytes (what a TMA load with 128-byte swizzle writes).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = (uint64_t)((addr & 0x3FFFFu) >> 4);   // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                            // leading byte offset: unused with a swizzle (1)
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset: 8 rows x 128 bytes
+    d |= (uint64_t)1 << 46;                            // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                            // layout: 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M 128, N n.
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int BN, int STAGES>
+struct Smem {
+    alignas(1024) uint8_t a[STAGES][BM * BK * 2];
+    alignas(1024) uint8_t b[STAGES][BN * BK * 2];
+    alignas(8) uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint32_t tmem_base;
+};
+
+// ------------------------------------------------------------------ epilogue of 32 columns of one row
+template <int EPI>
+__device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], void* Cout,
+                                            const float* residual, int m, int n, int M, int N) {
+    if (m >= M || n >= N) return;
+    if (EPI == EPI_SWIGLU) {
+        // 32 columns = [8 gate, 8 up, 8 gate, 8 up] -> 16 outputs at column n / 2 of [M, N / 2].
+        const int NO = N >> 1, no = n >> 1;
+        float o[16];
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float g = __uint_as_float(r[h * 16 + i]), u = __uint_as_float(r[h * 16 + 8 + i]);
+                o[h * 8 + i] = u * (g / (1.0f + __expf(-g)));
+            }
+        __nv_bfloat16* dst = (__nv_bfloat16*)Cout + (size_t)m * NO + no;
+        if (no + 16 <= NO && (NO & 7) == 0) {
+            uint4* d4 = reinterpret_cast<uint4*>(dst);
+            d4[0] = make_uint4(pack2(o[0], o[1]), pack2(o[2], o[3]), pack2(o[4], o[5]), pack2(o[6], o[7]));
+            d4[1] = make_uint4(pack2(o[8], o[9]), pack2(o[10], o[11]), pack2(o[12], o[13]), pack2(o[14], o[15]));
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if (no + i < NO) dst[i] = __float2bfloat16_rn(o[i]);
+        }
+        return;
+    }
+    const bool whole = n + 32 <= N;
+    if (EPI == EPI_BF16) {
+        __nv_bfloat16* dst = (__nv_bfloat16*)Cout + (size_t)m * N + n;
+        if (whole && (N & 7) == 0) {
+            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                d4[i] = make_uint4(pack2(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
+                                   pack2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
+                                   pack2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
+                                   pack2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7])));
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (n + i < N) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
+        }
+    } else {
+        float* dst = (float*)Cout + (size_t)m * N + n;
+        const float* res = (EPI == EPI_RESID) ? residual + (size_t)m * N + n : nullptr;
+        if (whole && (N & 3) == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float4 v = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                       __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                if (EPI == EPI_RESID) {
+                    float4 q = reinterpret_cast<const float4*>(res)[i];
+                    v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+                }
+                reinterpret_cast<float4*>(dst)[i] = v;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (n + i < N) dst[i] = __uint_as_float(r[i]) + (EPI == EPI_RESID ? res[i] : 0.f);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ the kernel
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(N_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               void* Cout, const float* residual, int M, int N, int K) {
+    extern __shared__ uint8_t smem_raw[];
+    using S = Smem<BN, STAGES>;
+    S& sm = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+    const int total = m_tiles * n_tiles;
+    const int n_kb = (K + BK - 1) / BK;
+    constexpr uint32_t STAGE_BYTES = (BM + BN) * BK * 2;
+    constexpr uint32_t TMEM_COLS = 2 * BN;             // two accumulators of BN float32 columns
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&sm.full[s]), 1); mbar_init(smem_u32(&sm.empty[s]), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&sm.acc_full[a]), 1); mbar_init(smem_u32(&sm.acc_empty[a]), 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sm.tmem_base;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(smem_u32(&sm.empty[s]), ((it / STAGES) & 1) ^ 1)) { atomicExch(&g_status, 1); ok = false; break; }
+                    const uint32_t full = smem_u32(&sm.full[s]);
+                    mbar_expect_tx(full, STAGE_BYTES);
+                    tma_load_2d(smem_u32(sm.a[s]), &map_a, kb * BK, m0, full);
+                    tma_load_2d(smem_u32(sm.b[s]), &map_b, kb * BK, n0, full);
+                }
+            }
+            if (!ok) {
+                // Copies that were started must land before the block's shared memory goes away.
+                for (uint32_t back = 1; back <= (uint32_t)STAGES && back <= it; ++back) {
+                    uint32_t j = it - back;
+                    mbar_wait(smem_u32(&sm.full[j % STAGES]), (j / STAGES) & 1);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BN);
+            uint32_t it = 0, t = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++t) {
+                const uint32_t acc = t & 1;
+                if (!mbar_wait(smem_u32(&sm.acc_empty[acc]), ((t >> 1) & 1) ^ 1)) { atomicExch(&g_status, 2); ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(smem_u32(&sm.full[s]), (it / STAGES) & 1)) { atomicExch(&g_status, 3); ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t da = smem_desc(smem_u32(sm.a[s])), db = smem_desc(smem_u32(sm.b[s]));
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)   // 32 bytes further along K: 2 units of 16 bytes
+                        tc_mma(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tc_commit(smem_u32(&sm.empty[s]));      // the stage is free once these products have read it
+                }
+                if (ok) tc_commit(smem_u32(&sm.acc_full[acc]));
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------------------------------------------------------- epilogue (warps 2..5)
+        const int quarter = warp & 3;                     // the 32 lanes of tensor memory this warp may read
+        uint32_t t = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++t) {
+            const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+            const uint32_t acc = t & 1;
+            if (!mbar_wait(smem_u32(&sm.acc_full[acc]), (t >> 1) & 1)) { atomicExch(&g_status, 4); ok = false; break; }
+            tc_fence_after();
+            const int m = m0 + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tc_ld32(taddr + c * 32, r);
+                tc_wait_ld();
+                store_chunk<EPI>(r, Cout, residual, m, n0 + c * 32, M, N);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sm.acc_empty[acc]));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// A row-major bf16 matrix [rows, K] as a 2-D tensor map with boxes of [box_rows, 64].
+int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    EncodeTiled fn = encode_fn();
+    if (!fn) return LQ_NO_DRIVER;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? LQ_OK : LQ_BAD_SIZE;
+}
+
+template <int BN, int STAGES, int EPI>
+int launch_epi(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const float* residual, int M, int N, int K,
+               int n_sms, cudaStream_t stream) {
+    constexpr size_t smem = sizeof(Smem<BN, STAGES>) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return lq_launch_status();
+        configured = true;
+    }
+    int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    int grid = tiles < n_sms ? tiles : n_sms;
+    gemm_tc_kernel<BN, STAGES, EPI><<<grid, N_THREADS, smem, stream>>>(ma, mb, C, residual, M, N, K);
+    return lq_launch_status();
+}
+
+template <int BN, int STAGES>
+int launch_bn(const void* A, const void* W, void* C, const float* residual, int M, int N, int K, int epi, int n_sms,
+              cudaStream_t stream) {
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, A, M, K, BM);
+    if (rc != LQ_OK) return rc;
+    rc = make_map(&mb, W, N, K, BN);
+    if (rc != LQ_OK) return rc;
+    switch (epi) {
+        case EPI_BF16: return launch_epi<BN, STAGES, EPI_BF16>(ma, mb, C, residual, M, N, K, n_sms, stream);
+        case EPI_F32: return launch_epi<BN, STAGES, EPI_F32>(ma, mb, C, residual, M, N, K, n_sms, stream);
+        case EPI_RESID: return launch_epi<BN, STAGES, EPI_RESID>(ma, mb, C, residual, M, N, K, n_sms, stream);
+        case EPI_SWIGLU: return launch_epi<BN, STAGES, EPI_SWIGLU>(ma, mb, C, residual, M, N, K, n_sms, stream);
+    }
+    return LQ_BAD_DTYPE;
+}
+
+}  // namespace
+
+// A [M, K] and W [N, K] bfloat16, row-major, 16-byte aligned, K % 8 == 0.
+// For EPI_SWIGLU, N counts the interleaved gate and up rows (N % 16 == 0) and C is [M, N / 2].
+LQ_EXPORT int lq_gemm_tc(const void* A, const void* W, void* C, const float* residual, int M, int N, int K, int epi,
+                         cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return LQ_OK;
+    if (K <= 0 || K % 8 != 0) return LQ_BAD_SIZE;
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return LQ_BAD_SIZE;
+    if (epi == EPI_SWIGLU && N % 16 != 0) return LQ_BAD_SIZE;
+    if (epi == EPI_RESID && residual == nullptr) return LQ_BAD_SIZE;
+    static int n_sms = 0;
+    if (!n_sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    // Wide tiles when they still fill the GPU, narrower ones otherwise.
+    long tiles256 = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
+    if (tiles256 >= n_sms) return launch_bn<256, 4>(A, W, C, residual, M, N, K, epi, n_sms, stream);
+    return launch_bn<128, 6>(A, W, C, residual, M, N, K, epi, n_sms, stream);
+}
+
+// The status word of the bounded waits: 0, or the code of the first wait that gave up
+// (1 producer, 2 accumulator free, 3 stage full, 4 accumulator full).  Reading it resets it.
+LQ_EXPORT int lq_gemm_tc_status() {
+    int v = 0, zero = 0;
+    cudaMemcpyFromSymbol(&v, g_status, sizeof(int));
+    if (v) cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+    return v;
+}

@@ -86,7 +86,7 @@ def _contig(t: torch.Tensor, what: str) -> torch.Tensor:
 
 def prepare(dtype: torch.dtype, verbose: bool = True) -> None:
     """Build and load the libraries a model of this dtype uses, before the first step."""
-    names = ["plain_kernels"] + (["gemm_skinny", "attn_decode"] if dtype == torch.bfloat16 else [])
+    names = ["plain_kernels"] + (["gemm_skinny", "gemm_tc", "attn_decode"] if dtype == torch.bfloat16 else [])
     for name in names:
         build.load(name)
 
@@ -220,6 +220,37 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, epi: int, residual: torch.Tens
     fn = _fn("gemm_skinny", "lq_gemm_skinny", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
     _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), _p(residual), M, N, K, epi, _stream()), "gemm_skinny")
     return out
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, epi: int, residual: torch.Tensor | None = None,
+            out: torch.Tensor | None = None) -> torch.Tensor:
+    """a [M, K] . w [N, K]^T on the tcgen05 tensor cores (TMA-fed, float32 accumulation in
+    tensor memory), with the epilogues of gemm_skinny.  For many rows."""
+    M, K = a.shape
+    N = w.shape[0]
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc takes bfloat16 inputs")
+    if w.shape[1] != K:
+        raise KernelError(f"linear: input width {K} does not match weight width {w.shape[1]}")
+    if K % 8:
+        raise KernelError(f"gemm_tc: width {K} must be a multiple of 8 (16-byte rows for TMA)")
+    if epi == EPI_RESID:
+        if residual is None or residual.dtype != torch.float32 or tuple(residual.shape) != (M, N):
+            raise KernelError("linear: residual must be float32 [M, N]")
+        out = residual
+    elif out is None:
+        shape = (M, N // 2) if epi == EPI_SWIGLU else (M, N)
+        out = torch.empty(shape, dtype=torch.float32 if epi == EPI_F32 else torch.bfloat16, device=a.device)
+    fn = _fn("gemm_tc", "lq_gemm_tc", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), _p(residual), M, N, K, epi, _stream()), "gemm_tc")
+    return out
+
+
+def gemm_tc_status() -> int:
+    """0, or the code of a wait inside gemm_tc that gave up (after a synchronize)."""
+    fn = build.load("gemm_tc").lq_gemm_tc_status
+    fn.restype = c_int
+    return int(fn())
 
 
 def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq, slots, H: int, Hkv: int, hd: int,

@@ -17,12 +17,16 @@ def linear_bf16(a, weight, out_dtype, residual):
         if out_dtype == torch.float32:
             return ops.gemm_skinny(a, weight.tensor, ops.EPI_F32)
         return ops.gemm_skinny(a, weight.tensor, ops.EPI_BF16)
-    return None
+    if residual is not None:
+        return ops.gemm_tc(a, weight.tensor, ops.EPI_RESID, residual)
+    return ops.gemm_tc(a, weight.tensor, ops.EPI_F32 if out_dtype == torch.float32 else ops.EPI_BF16)
 
 
 def linear_swiglu_bf16(a, weight):
     """a . W^T over rows interleaved in blocks of 8 (gate, up), then up * silu(gate)."""
     M, K = a.shape
-    if K % 8 == 0 and M <= ops.SKINNY_MAX_ROWS:
+    if K % 8:
+        return None
+    if M <= ops.SKINNY_MAX_ROWS:
         return ops.gemm_skinny(a, weight.tensor, ops.EPI_SWIGLU)
-    return None
+    return ops.gemm_tc(a, weight.tensor, ops.EPI_SWIGLU)

@@ -31,6 +31,12 @@ def _close(got, ref, tol, rel=0.0):
     return err
 
 
+def _acc_tol(K):
+    """Float32 accumulation of K products: a few times sqrt(K) roundings of 2^-24, relative to
+    the result's root mean square."""
+    return 8.0 * math.sqrt(K) * 2.0 ** -24
+
+
 def _rand(shape, dtype, seed, scale=1.0):
     g = torch.Generator(device="cpu").manual_seed(seed)
     return (torch.randn(shape, generator=g) * scale).to(dtype).to(DEV)
@@ -206,11 +212,11 @@ def test_gemm_skinny(M, N, K):
     ops = _ops()
     a, w = _rand((M, K), torch.bfloat16, 10), _rand((N, K), torch.bfloat16, 11)
     ref = a.float().double() @ w.float().double().T
-    _close(ops.gemm_skinny(a, w, ops.EPI_F32), ref, 2e-5)
-    _close(ops.gemm_skinny(a, w, ops.EPI_BF16), ref, 2e-5, BF16_ULP)
+    _close(ops.gemm_skinny(a, w, ops.EPI_F32), ref, _acc_tol(K))
+    _close(ops.gemm_skinny(a, w, ops.EPI_BF16), ref, _acc_tol(K), BF16_ULP)
     res = _rand((M, N), torch.float32, 12)
     expect = res.double() + ref
-    _close(ops.gemm_skinny(a, w, ops.EPI_RESID, residual=res), expect, 2e-5)
+    _close(ops.gemm_skinny(a, w, ops.EPI_RESID, residual=res), expect, _acc_tol(K))
 
 
 @pytest.mark.parametrize("M,F,K", [(1, 8, 64), (5, 176, 64), (64, 1000, 328)])
@@ -233,6 +239,48 @@ def test_gemm_skinny_is_independent_of_other_rows():
     full = ops.gemm_skinny(a, w, ops.EPI_F32)
     for r in (0, 11, 36):
         assert torch.equal(ops.gemm_skinny(a[r:r + 1].contiguous(), w, ops.EPI_F32)[0], full[r])
+
+
+@pytest.mark.parametrize("M", [65, 128, 300, 1111])
+@pytest.mark.parametrize("N,K", [(16, 64), (250, 80), (1000, 200), (4104, 1024), (520, 4096)])
+def test_gemm_tc(M, N, K):
+    ops = _ops()
+    a, w = _rand((M, K), torch.bfloat16, 20), _rand((N, K), torch.bfloat16, 21)
+    ref = a.float().double() @ w.float().double().T
+    _close(ops.gemm_tc(a, w, ops.EPI_F32), ref, _acc_tol(K))
+    _close(ops.gemm_tc(a, w, ops.EPI_BF16), ref, _acc_tol(K), BF16_ULP)
+    res = _rand((M, N), torch.float32, 22)
+    expect = res.double() + ref
+    _close(ops.gemm_tc(a, w, ops.EPI_RESID, residual=res), expect, _acc_tol(K))
+    torch.cuda.synchronize()
+    assert ops.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("M,F,K", [(70, 8, 64), (200, 176, 64), (513, 1000, 328), (2048, 2048, 512)])
+def test_gemm_tc_swiglu(M, F, K):
+    ops = _ops()
+    from longbow_quarrel_b200.kernels.linear import interleave_gate_up
+    a = _rand((M, K), torch.bfloat16, 23)
+    wg, wu = _rand((F, K), torch.bfloat16, 24, 0.2), _rand((F, K), torch.bfloat16, 25, 0.2)
+    g = a.float().double() @ wg.float().double().T
+    u = a.float().double() @ wu.float().double().T
+    ref = u * (g / (1 + torch.exp(-g)))
+    out = ops.gemm_tc(a, interleave_gate_up(wg, wu), ops.EPI_SWIGLU)
+    assert out.shape == (M, F)
+    _close(out, ref, 1e-4, BF16_ULP)
+    torch.cuda.synchronize()
+    assert ops.gemm_tc_status() == 0
+
+
+def test_gemm_tc_large_many_tiles_per_block():
+    """More tiles than SMs: blocks walk over several tiles and both accumulators are used."""
+    ops = _ops()
+    M, N, K = 2048, 6144, 512
+    a, w = _rand((M, K), torch.bfloat16, 26), _rand((N, K), torch.bfloat16, 27)
+    ref = (a.float() @ w.float().T).double()
+    _close(ops.gemm_tc(a, w, ops.EPI_F32), ref, _acc_tol(K))
+    torch.cuda.synchronize()
+    assert ops.gemm_tc_status() == 0
 
 
 @pytest.mark.parametrize("H,Hkv,hd,window", [(8, 2, 128, None), (6, 2, 48, None), (4, 4, 16, 37), (3, 1, 32, None),
