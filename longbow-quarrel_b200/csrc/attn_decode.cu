@@ -36,6 +36,7 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -157,8 +158,10 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
         float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-            float p00 = expf(s[nt][0] - nm0), p01 = expf(s[nt][1] - nm0);
-            float p10 = expf(s[nt][2] - nm1), p11 = expf(s[nt][3] - nm1);
+            // The sum runs over the probabilities as the product will see them (rounded to
+            // bfloat16), so that the weights of a row add up to one exactly.
+            float p00 = round_bf16(expf(s[nt][0] - nm0)), p01 = round_bf16(expf(s[nt][1] - nm0));
+            float p10 = round_bf16(expf(s[nt][2] - nm1)), p11 = round_bf16(expf(s[nt][3] - nm1));
             ps0 += p00 + p01;
             ps1 += p10 + p11;
             pa[nt * 2 + 0] = pack_bf16(p00, p01);

@@ -19,7 +19,11 @@ def decode_splits(n_tokens: int, Hkv: int, group_tiles: int, max_kv: int) -> int
 
 def attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window):
     """Rows of qkv hold q in their left H*hd columns.  Returns [T, H*hd]."""
-    if qkv.dtype == torch.bfloat16 and ctx.decode and hd <= 128 and hd % 8 == 0 and qkv.stride(0) % 8 == 0:
+    fast = qkv.dtype == torch.bfloat16 and hd <= 128 and hd % 8 == 0 and qkv.stride(0) % 8 == 0
+    if fast and not ctx.decode and cache_view.page_size == 64 and ctx.query_blocks is not None:
+        return ops.attn_prefill(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.slots,
+                                ctx.kv_len, ctx.query_blocks, H, Hkv, hd, cache_view.page_size, scale, window)
+    if fast and ctx.decode:
         n_splits = decode_splits(ctx.T, Hkv, -(-(H // Hkv) // 16), ctx.max_kv)
         return ops.attn_decode(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.tok_pos,
                                ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window, n_splits)

@@ -86,7 +86,7 @@ def _contig(t: torch.Tensor, what: str) -> torch.Tensor:
 
 def prepare(dtype: torch.dtype, verbose: bool = True) -> None:
     """Build and load the libraries a model of this dtype uses, before the first step."""
-    names = ["plain_kernels"] + (["gemm_skinny", "gemm_tc", "attn_decode"] if dtype == torch.bfloat16 else [])
+    names = ["plain_kernels"] + (["gemm_skinny", "gemm_tc", "attn_decode", "attn_prefill"] if dtype == torch.bfloat16 else [])
     for name in names:
         build.load(name)
 
@@ -251,6 +251,28 @@ def gemm_tc_status() -> int:
     fn = build.load("gemm_tc").lq_gemm_tc_status
     fn.restype = c_int
     return int(fn())
+
+
+def attn_prefill(q: torch.Tensor, k_pages, v_pages, page_table, slots, kv_len, query_blocks, H: int, Hkv: int, hd: int,
+                 page_size: int, scale: float, window: int | None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of blocks of query rows over the paged bfloat16 cache (flash style:
+    tensor-core products, online softmax in float32).  query_blocks = (sequence, first row,
+    rows, first position) int32 tensors, one entry for each block of at most 64 rows."""
+    T = q.shape[0]
+    if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
+        raise KernelError("attn_prefill takes bfloat16 queries and cache")
+    if hd % 8 or hd > 128 or page_size != 64:
+        raise KernelError(f"attn_prefill: head_dim {hd} (multiple of 8, at most 128), page size {page_size} (64)")
+    if out is None:
+        out = torch.empty((T, H * hd), dtype=torch.bfloat16, device=q.device)
+    qb_seq, qb_row, qb_rows, qb_pos = query_blocks
+    fn = _fn("attn_prefill", "lq_attn_prefill", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                 c_int, c_int, c_float, c_int, c_void_p])
+    _check(fn(_p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0), _p(slots), _p(kv_len),
+              _p(qb_seq), _p(qb_row), _p(qb_rows), _p(qb_pos), _p(out), qb_seq.numel(), H, Hkv, hd, page_size,
+              float(scale), int(window or 0), _stream()), "attn_prefill")
+    return out
 
 
 def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq, slots, H: int, Hkv: int, hd: int,

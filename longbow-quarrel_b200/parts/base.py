@@ -43,6 +43,7 @@ class StepContext:
     kv_len: torch.Tensor
     cu_rows: torch.Tensor
     want_rows: torch.Tensor | None
+    query_blocks: tuple | None      # (sequence, first row, rows, first position) of each 64-row block, int32
     h_slots: list[int]
     h_new: list[int]
     h_past: list[int]

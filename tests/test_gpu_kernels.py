@@ -150,6 +150,15 @@ class PagedCase:
         return out
 
 
+def _attn_tol(case, ref):
+    """Attention through bfloat16 probabilities: each output is a weighted mean of values whose
+    weights carry a relative rounding of 2^-9, so it is off by at most about 2^-8 of the largest
+    value; expressed relative to the root mean square of the reference, as _close wants it."""
+    vmax = max(float(v.float().abs().max()) for v in case.v)
+    rms = float(ref.double().pow(2).mean().sqrt())
+    return 2.0 ** -8 * vmax / rms
+
+
 def _ints(x):
     return torch.tensor(x, dtype=torch.int32, device=DEV)
 
@@ -297,7 +306,7 @@ def test_attn_decode(H, Hkv, hd, window, n_splits):
     out = ops.attn_decode(q, case.k_pages, case.v_pages, case.table, _ints(tok_pos), _ints(tok_seq), case.slots,
                           H, Hkv, hd, case.page_size, scale, window, n_splits)
     ref = case.reference(q[:, :H * hd].reshape(-1, H, hd).float(), tok_seq, tok_pos, H, scale, window)
-    _close(out.reshape(-1, H, hd), ref, 1e-2)
+    _close(out.reshape(-1, H, hd), ref, _attn_tol(case, ref), BF16_ULP)
 
 
 @pytest.mark.parametrize("far_key", [0, 5, 250, 511, 700])
@@ -324,3 +333,66 @@ def test_attn_decode_finds_a_far_key(far_key):
                               H, Hkv, hd, 64, scale, None, n_splits).reshape(H, hd)
         for kvh in range(Hkv):
             _close(out[kvh * G], case.v[0][far_key, kvh], 2e-2)
+
+
+def _query_blocks(tok_seq_lens, past):
+    """Blocks of at most 64 rows: (sequence, first packed row, rows, first position)."""
+    out, row = [], 0
+    for b, (n, p) in enumerate(zip(tok_seq_lens, past)):
+        for r in range(0, n, 64):
+            out.append((b, row + r, min(64, n - r), p + r))
+        row += n
+    arr = np.asarray(out, dtype=np.int32)
+    return tuple(torch.from_numpy(np.ascontiguousarray(arr[:, i])).to(DEV) for i in range(4))
+
+
+@pytest.mark.parametrize("H,Hkv,hd,window", [(8, 2, 128, None), (6, 2, 48, None), (4, 4, 16, 37), (3, 1, 32, None),
+                                             (4, 2, 64, 100), (2, 2, 80, 64)])
+def test_attn_prefill(H, Hkv, hd, window):
+    """Three sequences in one call: one whole from position 0, one single token, one that
+    continues after 70 cached tokens."""
+    ops = _ops()
+    lens = [300, 1, 200]            # keys in the cache after the step
+    new = [300, 1, 130]             # rows of this step
+    past = [0, 0, 70]
+    case = PagedCase(lens, Hkv, hd, torch.bfloat16, seed=6)
+    tok_seq = [b for b, n in enumerate(new) for _ in range(n)]
+    tok_pos = [p + i for n, p in zip(new, past) for i in range(n)]
+    q = _rand((sum(new), (H + 2 * Hkv) * hd), torch.bfloat16, 81)
+    scale = hd ** -0.5
+    out = ops.attn_prefill(q, case.k_pages, case.v_pages, case.table, case.slots, _ints(lens), _query_blocks(new, past),
+                           H, Hkv, hd, 64, scale, window)
+    ref = case.reference(q[:, :H * hd].reshape(-1, H, hd).float(), tok_seq, tok_pos, H, scale, window)
+    _close(out.reshape(-1, H, hd), ref, _attn_tol(case, ref), BF16_ULP)
+
+
+def test_attn_prefill_window_edge_and_far_key():
+    """Keys made to stand out just inside and just outside the window, and at position 0
+    of a long sequence: the row's output must be the value of the visible one."""
+    ops = _ops()
+    H = Hkv = 1
+    hd, n, W = 64, 400, 50
+    case = PagedCase([n], Hkv, hd, torch.bfloat16, seed=7)
+    q = _rand((n, hd), torch.bfloat16, 82)
+    slot = case.slot_of[0]
+
+    def plant(key_pos, query_row):
+        qh = q[query_row].float()
+        key = (qh / qh.norm() * 40.0).to(torch.bfloat16)
+        case.k_pages[int(case.table[slot, key_pos // 64]), 0, key_pos % 64] = key
+        case.k[0][key_pos, 0] = key
+
+    plant(0, 399)            # far key: visible to row 399 without a window, hidden with one
+    plant(300, 349)          # distance 49: the last key inside a window of 50
+    plant(250, 300)          # distance 50: just outside
+    blocks = _query_blocks([n], [0])
+    full = ops.attn_prefill(q, case.k_pages, case.v_pages, case.table, case.slots, _ints([n]), blocks, 1, 1, hd, 64,
+                            1.0, None)
+    win = ops.attn_prefill(q, case.k_pages, case.v_pages, case.table, case.slots, _ints([n]), blocks, 1, 1, hd, 64,
+                           1.0, W)
+    _close(full[399], case.v[0][0, 0], 2e-2)
+    _close(win[349], case.v[0][300, 0], 2e-2)
+    ref = case.reference(q.reshape(n, 1, hd).float(), [0] * n, list(range(n)), 1, 1.0, W)
+    _close(win.reshape(n, 1, hd), ref, _attn_tol(case, ref), BF16_ULP)
+    assert float((win[300].float() - case.v[0][250, 0].float()).abs().max()) > 0.5     # the key outside is not seen
+    assert float((win[399].float() - case.v[0][0, 0].float()).abs().max()) > 0.5
