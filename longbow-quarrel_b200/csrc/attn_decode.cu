@@ -47,7 +47,7 @@ __device__ __forceinline__ uint32_t reg_of(const uint4& v, int i) {
 
 // HD: head_dim rounded up to 32, 64 or 128; the real head_dim hd is a multiple of 8.
 template <int HD>
-__global__ void __launch_bounds__(DW * 32)
+__global__ void __launch_bounds__(DW * 32, 2)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_pages,
                    const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ page_table, int pt_stride,
                    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
@@ -62,6 +62,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
     const int split = blockIdx.x, tok = blockIdx.z;
     const int G = H / Hkv, gtiles = (G + 15) / 16;
     const int kvh = blockIdx.y / gtiles, gt = blockIdx.y % gtiles;
+    pdl_launch_dependents();
+    pdl_wait();
     const int pos = tok_pos[tok], len = pos + 1;
     const int start = (window > 0 && pos >= window) ? pos - window + 1 : 0;
     const int* pt = page_table + (size_t)slots[tok_seq[tok]] * pt_stride;
@@ -94,21 +96,22 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
     const int tile_hi = min(first_tile + n_tiles, tile_lo + per_split);
     const size_t head_off = (size_t)kvh * page_size * hd;
 
-    for (int tile = tile_lo + warp; tile < tile_hi; tile += DW) {
+    // A tile's K and V as this thread's mma fragments.  K: rows kb + g and kb + 8 + g;
+    // V: rows kb + {2t, 2t+1, 2t+8, 2t+9}.
+    struct Tile { uint4 kr[2][QB]; uint4 vr[4][VC]; };
+    auto load_tile = [&](int tile, Tile& T) {
         const int kb = tile * TILE;
         const int page = pt[kb / page_size];
         const size_t page_off = (size_t)page * Hkv * page_size * hd + head_off + (size_t)(kb % page_size) * hd;
         const __nv_bfloat16* kp = k_pages + page_off;
         const __nv_bfloat16* vp = v_pages + page_off;
-        // K: rows kb + g and kb + 8 + g; V: rows kb + {2t, 2t+1, 2t+8, 2t+9}.
-        uint4 kr[2][QB], vr[4][VC];
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
             int key = kb + nt * 8 + g;
 #pragma unroll
             for (int b = 0; b < QB; ++b) {
                 int d = b * 32 + t * 8;
-                kr[nt][b] = (key < len && d < hd) ? ldg16(kp + (size_t)(nt * 8 + g) * hd + d) : zero;
+                T.kr[nt][b] = (key < len && d < hd) ? ldg16(kp + (size_t)(nt * 8 + g) * hd + d) : zero;
             }
         }
 #pragma unroll
@@ -117,9 +120,12 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
 #pragma unroll
             for (int c = 0; c < VC; ++c) {
                 int d = c * 64 + g * 8;
-                vr[r][c] = (kb + row < len && d < hd) ? ldg16(vp + (size_t)row * hd + d) : zero;
+                T.vr[r][c] = (kb + row < len && d < hd) ? ldg16(vp + (size_t)row * hd + d) : zero;
             }
         }
+    };
+    auto compute_tile = [&](int tile, const Tile& T) {
+        const int kb = tile * TILE;
         // S = Q K^T for two 8-key tiles.
         float s[2][4];
 #pragma unroll
@@ -128,8 +134,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
             for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
 #pragma unroll
             for (int b = 0; b < QB; ++b) {
-                mma_bf16(s[nt], qa[b].x, qb[b].x, qa[b].y, qb[b].y, kr[nt][b].x, kr[nt][b].y);
-                mma_bf16(s[nt], qa[b].z, qb[b].z, qa[b].w, qb[b].w, kr[nt][b].z, kr[nt][b].w);
+                mma_bf16(s[nt], qa[b].x, qb[b].x, qa[b].y, qb[b].y, T.kr[nt][b].x, T.kr[nt][b].y);
+                mma_bf16(s[nt], qa[b].z, qb[b].z, qa[b].w, qb[b].w, T.kr[nt][b].z, T.kr[nt][b].w);
             }
         }
         float tm0 = -CUDART_INF_F, tm1 = -CUDART_INF_F;
@@ -176,10 +182,23 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
                 float (&acc)[4] = o[c * 8 + j];
                 acc[0] *= c0; acc[1] *= c0; acc[2] *= c1; acc[3] *= c1;
                 const unsigned sel = (j & 1) ? 0x7632u : 0x5410u;
-                uint32_t b0 = __byte_perm(reg_of(vr[0][c], j >> 1), reg_of(vr[1][c], j >> 1), sel);
-                uint32_t b1 = __byte_perm(reg_of(vr[2][c], j >> 1), reg_of(vr[3][c], j >> 1), sel);
+                uint32_t b0 = __byte_perm(reg_of(T.vr[0][c], j >> 1), reg_of(T.vr[1][c], j >> 1), sel);
+                uint32_t b1 = __byte_perm(reg_of(T.vr[2][c], j >> 1), reg_of(T.vr[3][c], j >> 1), sel);
                 mma_bf16(acc, pa[0], pa[1], pa[2], pa[3], b0, b1);
             }
+    };
+    // The loads of the next tile are in flight while the current one is computed.
+    Tile ta, tb;
+    int tile = tile_lo + warp;
+    if (tile < tile_hi) load_tile(tile, ta);
+    while (tile < tile_hi) {
+        if (tile + DW < tile_hi) load_tile(tile + DW, tb);
+        compute_tile(tile, ta);
+        tile += DW;
+        if (tile >= tile_hi) break;
+        if (tile + DW < tile_hi) load_tile(tile + DW, ta);
+        compute_tile(tile, tb);
+        tile += DW;
     }
     // Row sums: add the four threads of a row.
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -230,6 +249,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   __nv_bfloat16* __restrict__ out, int hd, int n_splits) {
     const size_t th = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const float* ml = part_ml + th * n_splits * 2;
     float mx = -CUDART_INF_F;
     for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, ml[2 * s]);
@@ -250,13 +271,12 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
            int T, int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits, cudaStream_t stream) {
     int G = H / Hkv, gtiles = (G + 15) / 16;
     dim3 grid(n_splits, Hkv * gtiles, T);
-    attn_decode_kernel<HD><<<grid, DW * 32, 0, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pages,
-        (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, part_o, part_ml,
-        (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, n_splits);
-    int rc = lq_launch_status();
+    int rc = launch_pdl(attn_decode_kernel<HD>, grid, dim3(DW * 32), 0, stream, (const __nv_bfloat16*)q, q_stride,
+        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots,
+        part_o, part_ml, (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, n_splits);
     if (rc != LQ_OK || n_splits == 1) return rc;
-    attn_merge_kernel<<<T * H, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, hd, n_splits);
-    return lq_launch_status();
+    return launch_pdl(attn_merge_kernel, dim3(T * H), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml,
+                      (__nv_bfloat16*)out, hd, n_splits);
 }
 
 }  // namespace

@@ -66,6 +66,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int blk = blockIdx.x, h = blockIdx.y;
+    pdl_launch_dependents();
+    pdl_wait();
     const int seq = qb_seq[blk], row0 = qb_row[blk], n_rows = qb_rows[blk], pos0 = qb_pos[blk];
     const int kvh = h / (H / Hkv);
     const int len = kv_len[seq];
@@ -237,10 +239,9 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
         configured = true;
     }
     dim3 grid(n_blocks, H);
-    attn_prefill_kernel<HD><<<grid, NT, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pages,
-        (const __nv_bfloat16*)v_pages, page_table, pt_stride, slots, kv_len, qb_seq, qb_row, qb_rows, qb_pos,
-        (__nv_bfloat16*)out, H, Hkv, hd, scale * 1.4426950408889634f, window);
-    return lq_launch_status();
+    return launch_pdl(attn_prefill_kernel<HD>, grid, dim3(NT), smem, stream, (const __nv_bfloat16*)q, q_stride,
+        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, slots, kv_len, qb_seq, qb_row,
+        qb_rows, qb_pos, (__nv_bfloat16*)out, H, Hkv, hd, scale * 1.4426950408889634f, window);
 }
 
 }  // namespace

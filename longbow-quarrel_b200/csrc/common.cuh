@@ -3,6 +3,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define LQ_F32 0
 #define LQ_BF16 1
@@ -35,4 +36,33 @@ __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
+}
+
+// ------------------------------------------------------------------ programmatic dependent launch
+// Kernels of a step follow one another on one stream.  Launched with launch_pdl, a kernel's
+// blocks may be scheduled while the kernel before it is still draining; they run up to
+// pdl_wait(), which returns once that kernel has completed and its writes are visible.  What a
+// block does before pdl_wait() must not read anything an earlier kernel of the step writes, and
+// must write nothing: index arithmetic, and prefetching of weights, which no kernel writes.
+// pdl_launch_dependents() lets the kernel after this one be scheduled as early as possible.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    // LQ_PDL=0 in the environment launches every kernel strictly after the one before it.
+    static const bool enabled = [] { const char* v = getenv("LQ_PDL"); return !(v && v[0] == '0'); }();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = enabled ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    return e == cudaSuccess ? LQ_OK : (int)e;
 }

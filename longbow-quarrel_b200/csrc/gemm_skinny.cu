@@ -5,7 +5,8 @@
 // the 32-wide k chunks in turn, stream their part of W straight from global memory
 // into mma fragments (16-byte loads, no shared-memory staging: nothing is reused),
 // multiply on the tensor cores with the tokens as the n side of m16n8k16, and sum
-// their partial results in a fixed order through shared memory.  An output therefore
+// their partial results in a fixed order through shared memory.  A block keeps all of
+// K: measured on B200, cutting K between blocks made every shape slower.  An output therefore
 // depends only on its own row of x and W, not on how many other rows the batch has.
 //
 // The k index inside a chunk is permuted the same way for W and x (a thread's eight
@@ -30,7 +31,7 @@ namespace {
 constexpr int WARPS = 8;
 constexpr int ROWS = 16;     // rows of W per block
 constexpr int KC = 32;       // k per chunk
-constexpr int UNROLL = 4;    // chunks in flight per warp
+constexpr int UNROLL = 4;    // chunks per warp and round
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     uint4 v;
@@ -48,8 +49,16 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Work of one warp on `UNROLL` chunks: the W rows of the block as mma A fragments, and (for
+// few tokens) the tokens' x as B fragments, all loaded before any of it is used.
+template <int MT>
+struct Frags {
+    uint4 a0[UNROLL], a1[UNROLL];
+    uint4 b[UNROLL];                    // x of the tokens, kept only when there is one group of 8 tokens
+};
+
 template <int MT, int EPI>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, 2)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, void* Cout,
                    const float* residual, int M, int N, int K) {
     __shared__ float red[WARPS][ROWS][MT * 8 + 1];
@@ -60,7 +69,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
     const bool r0ok = r0 < N, r1ok = r1 < N;
     const __nv_bfloat16* w0 = W + (size_t)(r0ok ? r0 : 0) * K;
     const __nv_bfloat16* w1 = W + (size_t)(r1ok ? r1 : 0) * K;
-    const int n_chunks = (K + KC - 1) / KC;
+    const int c_lo = 0, c_hi = (K + KC - 1) / KC;      // the block's chunks of K: all of them
+    constexpr int STEP = WARPS * UNROLL;
 
     float acc[MT][4];
 #pragma unroll
@@ -69,28 +79,76 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
 
     const uint4 zero = make_uint4(0, 0, 0, 0);
-    for (int c0 = warp; c0 < n_chunks; c0 += WARPS * UNROLL) {
-        uint4 a0[UNROLL], a1[UNROLL];
+    auto load_w = [&](int c0, Frags<MT>& f) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             int c = c0 + u * WARPS;
             int k = c * KC + t * 8;
-            bool ok = c < n_chunks && k < K;   // K is a multiple of 8, so a started 16-byte piece is whole
-            a0[u] = (ok && r0ok) ? ldg_stream(w0 + k) : zero;
-            a1[u] = (ok && r1ok) ? ldg_stream(w1 + k) : zero;
+            bool ok = c < c_hi && k < K;       // K is a multiple of 8, so a started 16-byte piece is whole
+            f.a0[u] = (ok && r0ok) ? ldg_stream(w0 + k) : zero;
+            f.a1[u] = (ok && r1ok) ? ldg_stream(w1 + k) : zero;
         }
+    };
+    auto load_x = [&](int c0, Frags<MT>& f) {
+        if (MT == 1) {
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                int c = c0 + u * WARPS;
+                int k = c * KC + t * 8;
+                bool ok = c < c_hi && k < K;
+                f.b[u] = (ok && g < M) ? ldg_cached(X + (size_t)g * K + k) : zero;
+            }
+        }
+    };
+    auto load = [&](int c0, Frags<MT>& f) { load_w(c0, f); load_x(c0, f); };
+    // Weights are written by no kernel, so the first round of them is loaded before the kernel
+    // ahead of this one is known to have finished; x and the output wait for pdl_wait().
+    pdl_launch_dependents();
+    auto compute = [&](int c0, const Frags<MT>& f) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             int c = c0 + u * WARPS;
             int k = c * KC + t * 8;
-            bool ok = c < n_chunks && k < K;
+            bool ok = c < c_hi && k < K;
 #pragma unroll
             for (int j = 0; j < MT; ++j) {
-                int m = j * 8 + g;
-                uint4 b = (ok && m < M) ? ldg_cached(X + (size_t)m * K + k) : zero;
-                mma_bf16(acc[j], a0[u].x, a1[u].x, a0[u].y, a1[u].y, b.x, b.y);
-                mma_bf16(acc[j], a0[u].z, a1[u].z, a0[u].w, a1[u].w, b.z, b.w);
+                uint4 b;
+                if (MT == 1) {
+                    b = f.b[u];
+                } else {
+                    int m = j * 8 + g;
+                    b = (ok && m < M) ? ldg_cached(X + (size_t)m * K + k) : zero;
+                }
+                mma_bf16(acc[j], f.a0[u].x, f.a1[u].x, f.a0[u].y, f.a1[u].y, b.x, b.y);
+                mma_bf16(acc[j], f.a0[u].z, f.a1[u].z, f.a0[u].w, f.a1[u].w, b.z, b.w);
             }
+        }
+    };
+    if (MT <= 2) {
+        // Few tokens: the loads of the next round are in flight while the current one is multiplied.
+        Frags<MT> fa, fb;
+        int c0 = c_lo + warp;
+        if (c0 < c_hi) load_w(c0, fa);
+        pdl_wait();
+        if (c0 < c_hi) load_x(c0, fa);
+        while (c0 < c_hi) {
+            if (c0 + STEP < c_hi) load(c0 + STEP, fb);
+            compute(c0, fa);
+            c0 += STEP;
+            if (c0 >= c_hi) break;
+            if (c0 + STEP < c_hi) load(c0 + STEP, fa);
+            compute(c0, fb);
+            c0 += STEP;
+        }
+    } else {
+        // More tokens need the registers for their sums: one round at a time.
+        Frags<MT> fa;
+        int c0 = c_lo + warp;
+        if (c0 < c_hi) load_w(c0, fa);
+        pdl_wait();
+        for (; c0 < c_hi; c0 += STEP) {
+            if (c0 != c_lo + warp) load_w(c0, fa);
+            compute(c0, fa);
         }
     }
 #pragma unroll
@@ -103,16 +161,18 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
     __syncthreads();
     // One thread per (token, row): consecutive threads write consecutive outputs of a token.
     constexpr int OUT_ROWS = (EPI == EPI_SWIGLU) ? ROWS / 2 : ROWS;
+    auto total = [&](int r, int m) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) v += red[w][r][m];
+        return v;
+    };
     for (int i = threadIdx.x; i < MT * 8 * OUT_ROWS; i += WARPS * 32) {
         int m = i / OUT_ROWS, r = i % OUT_ROWS;
         if (m >= M) continue;
-        float s = 0.f;
-#pragma unroll
-        for (int w = 0; w < WARPS; ++w) s += red[w][r][m];
+        float s = total(r, m);
         if (EPI == EPI_SWIGLU) {
-            float u = 0.f;
-#pragma unroll
-            for (int w = 0; w < WARPS; ++w) u += red[w][r + 8][m];
+            float u = total(r + 8, m);
             int f = (n0 >> 1) + r;
             if (f < (N >> 1))
                 ((__nv_bfloat16*)Cout)[(size_t)m * (N >> 1) + f] = __float2bfloat16_rn(u * (s / (1.0f + expf(-s))));
@@ -134,10 +194,10 @@ int launch_mt(const void* X, const void* W, void* C, const float* residual, int 
     const __nv_bfloat16* x = (const __nv_bfloat16*)X;
     const __nv_bfloat16* w = (const __nv_bfloat16*)W;
     switch (epi) {
-        case EPI_BF16: gemm_skinny_kernel<MT, EPI_BF16><<<grid, block, 0, stream>>>(x, w, C, residual, M, N, K); break;
-        case EPI_F32: gemm_skinny_kernel<MT, EPI_F32><<<grid, block, 0, stream>>>(x, w, C, residual, M, N, K); break;
-        case EPI_RESID: gemm_skinny_kernel<MT, EPI_RESID><<<grid, block, 0, stream>>>(x, w, C, residual, M, N, K); break;
-        case EPI_SWIGLU: gemm_skinny_kernel<MT, EPI_SWIGLU><<<grid, block, 0, stream>>>(x, w, C, residual, M, N, K); break;
+        case EPI_BF16: return launch_pdl(gemm_skinny_kernel<MT, EPI_BF16>, grid, block, 0, stream, x, w, C, residual, M, N, K);
+        case EPI_F32: return launch_pdl(gemm_skinny_kernel<MT, EPI_F32>, grid, block, 0, stream, x, w, C, residual, M, N, K);
+        case EPI_RESID: return launch_pdl(gemm_skinny_kernel<MT, EPI_RESID>, grid, block, 0, stream, x, w, C, residual, M, N, K);
+        case EPI_SWIGLU: return launch_pdl(gemm_skinny_kernel<MT, EPI_SWIGLU>, grid, block, 0, stream, x, w, C, residual, M, N, K);
         default: return LQ_BAD_DTYPE;
     }
     return lq_launch_status();

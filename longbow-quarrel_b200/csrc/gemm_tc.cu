@@ -216,10 +216,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    pdl_launch_dependents();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = sm.tmem_base;
+    pdl_wait();     // barriers and tensor memory were set up while the kernel ahead was draining
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
@@ -346,8 +348,7 @@ int launch_epi(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const floa
     }
     int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     int grid = tiles < n_sms ? tiles : n_sms;
-    gemm_tc_kernel<BN, STAGES, EPI><<<grid, N_THREADS, smem, stream>>>(ma, mb, C, residual, M, N, K);
-    return lq_launch_status();
+    return launch_pdl(gemm_tc_kernel<BN, STAGES, EPI>, dim3(grid), dim3(N_THREADS), smem, stream, ma, mb, C, residual, M, N, K);
 }
 
 template <int BN, int STAGES>

@@ -21,6 +21,8 @@
 template <typename TW>
 __global__ void embedding_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                                  float* __restrict__ out, int D, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
     int t = blockIdx.x;
     int tok = tokens[t];
     if (tok < 0 || tok >= V) tok = 0;  // range is checked on the host before launch
@@ -32,9 +34,9 @@ LQ_EXPORT int lq_embedding(const void* table, int table_dtype, const int* tokens
                            int T, int D, int V, cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
     if (table_dtype == LQ_F32)
-        embedding_kernel<float><<<T, 256, 0, stream>>>((const float*)table, tokens, out, D, V);
+        return launch_pdl(embedding_kernel<float>, dim3(T), dim3(256), 0, stream, (const float*)table, tokens, out, D, V);
     else if (table_dtype == LQ_BF16)
-        embedding_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, D, V);
+        return launch_pdl(embedding_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (const __nv_bfloat16*)table, tokens, out, D, V);
     else
         return LQ_BAD_DTYPE;
     return lq_launch_status();
@@ -45,6 +47,8 @@ LQ_EXPORT int lq_embedding(const void* table, int table_dtype, const int* tokens
 template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
                                const int* __restrict__ rows, TO* __restrict__ out, int D, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float partial[32];
     __shared__ float scale_s;
     int r = blockIdx.x;
@@ -72,9 +76,9 @@ LQ_EXPORT int lq_rmsnorm(const float* x, const float* gain, const int* rows, voi
                          int n_rows, int D, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return LQ_OK;
     if (out_dtype == LQ_F32)
-        rmsnorm_kernel<float><<<n_rows, 256, 0, stream>>>(x, gain, rows, (float*)out, D, eps);
+        return launch_pdl(rmsnorm_kernel<float>, dim3(n_rows), dim3(256), 0, stream, x, gain, rows, (float*)out, D, eps);
     else if (out_dtype == LQ_BF16)
-        rmsnorm_kernel<__nv_bfloat16><<<n_rows, 256, 0, stream>>>(x, gain, rows, (__nv_bfloat16*)out, D, eps);
+        return launch_pdl(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, x, gain, rows, (__nv_bfloat16*)out, D, eps);
     else
         return LQ_BAD_DTYPE;
     return lq_launch_status();
@@ -90,6 +94,8 @@ template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_plain_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restrict__ C,
                   const float* __restrict__ residual, int M, int N, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float As[GK][GT + 1];
     __shared__ float Ws[GK][GT + 1];
     int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -137,9 +143,9 @@ static int gemm_plain_c(const void* A, const void* W, void* C, int c_dtype, cons
                         int M, int N, int K, cudaStream_t stream) {
     dim3 grid((N + GT - 1) / GT, (M + GT - 1) / GT);
     if (c_dtype == LQ_F32)
-        gemm_plain_kernel<TA, TW, float><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, (float*)C, residual, M, N, K);
+        return launch_pdl(gemm_plain_kernel<TA, TW, float>, grid, dim3(256), 0, stream, (const TA*)A, (const TW*)W, (float*)C, residual, M, N, K);
     else if (c_dtype == LQ_BF16)
-        gemm_plain_kernel<TA, TW, __nv_bfloat16><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, (__nv_bfloat16*)C, residual, M, N, K);
+        return launch_pdl(gemm_plain_kernel<TA, TW, __nv_bfloat16>, grid, dim3(256), 0, stream, (const TA*)A, (const TW*)W, (__nv_bfloat16*)C, residual, M, N, K);
     else
         return LQ_BAD_DTYPE;
     return lq_launch_status();
@@ -168,6 +174,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
                                      const int* __restrict__ page_table, int pt_stride,
                                      T* __restrict__ k_pages, T* __restrict__ v_pages,
                                      int H, int Hkv, int hd, int page_size, int has_kv) {
+    pdl_launch_dependents();
+    pdl_wait();
     int t = blockIdx.x;
     int pos = tok_pos[t];
     int half = hd >> 1;
@@ -221,10 +229,10 @@ LQ_EXPORT int lq_rope_kv_write(void* qkv, int dtype, const float* cos_t, const f
     if (T <= 0) return LQ_OK;
     if (hd % 2) return LQ_BAD_SIZE;
     if (dtype == LQ_F32)
-        rope_kv_write_kernel<float><<<T, 256, 0, stream>>>((float*)qkv, cos_t, sin_t, tok_pos, tok_seq, slots,
+        return launch_pdl(rope_kv_write_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)qkv, cos_t, sin_t, tok_pos, tok_seq, slots,
             page_table, pt_stride, (float*)k_pages, (float*)v_pages, H, Hkv, hd, page_size, has_kv);
     else if (dtype == LQ_BF16)
-        rope_kv_write_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((__nv_bfloat16*)qkv, cos_t, sin_t, tok_pos, tok_seq, slots,
+        return launch_pdl(rope_kv_write_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)qkv, cos_t, sin_t, tok_pos, tok_seq, slots,
             page_table, pt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, H, Hkv, hd, page_size, has_kv);
     else
         return LQ_BAD_DTYPE;
@@ -246,6 +254,8 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
                        const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                        const int* __restrict__ slots, T* __restrict__ out, int H, int Hkv, int hd,
                        int page_size, float scale, int window) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float sm[];
     float* qs = sm;              // [hd]
     float* sc = sm + hd;         // [ATT_CHUNK]
@@ -312,10 +322,10 @@ LQ_EXPORT int lq_attention_plain(const void* q, int q_stride, int dtype, const v
     dim3 grid(T, H);
     size_t smem = (hd + 2 * ATT_CHUNK) * sizeof(float);
     if (dtype == LQ_F32)
-        attention_plain_kernel<float><<<grid, ATT_CHUNK, smem, stream>>>((const float*)q, q_stride, (const float*)k_pages,
+        return launch_pdl(attention_plain_kernel<float>, grid, dim3(ATT_CHUNK), smem, stream, (const float*)q, q_stride, (const float*)k_pages,
             (const float*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, (float*)out, H, Hkv, hd, page_size, scale, window);
     else if (dtype == LQ_BF16)
-        attention_plain_kernel<__nv_bfloat16><<<grid, ATT_CHUNK, smem, stream>>>((const __nv_bfloat16*)q, q_stride,
+        return launch_pdl(attention_plain_kernel<__nv_bfloat16>, grid, dim3(ATT_CHUNK), smem, stream, (const __nv_bfloat16*)q, q_stride,
             (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots,
             (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window);
     else
@@ -328,6 +338,8 @@ LQ_EXPORT int lq_attention_plain(const void* q, int q_stride, int dtype, const v
 // [0, F), up in [F, 2F).  block == b > 0: columns alternate b gate, b up, b gate, ...
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, size_t total, int block) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     size_t t = i / F;
@@ -345,9 +357,9 @@ LQ_EXPORT int lq_swiglu(const void* gu, void* out, int dtype, int T, int F, int 
     if (block < 0 || (block && F % block)) return LQ_BAD_SIZE;
     unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == LQ_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, F, total, block);
+        return launch_pdl(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, F, total, block);
     else if (dtype == LQ_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, F, total, block);
+        return launch_pdl(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, F, total, block);
     else
         return LQ_BAD_DTYPE;
     return lq_launch_status();

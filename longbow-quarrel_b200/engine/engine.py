@@ -49,7 +49,7 @@ class Engine:
 
     # ------------------------------------------------------------------ construction
     @classmethod
-    def _build(cls, arch, config, tensors_fn, dtype, max_tokens, max_batch, max_context, device):
+    def _build(cls, arch, config, tensors_fn, dtype, max_tokens, max_batch, max_context, device, use_graphs=True):
         dtype, device = _dtype(dtype), _device(device)
         spec = arch.describe(config)
         max_context = min(max_context or spec.max_positions, spec.max_positions)
@@ -63,21 +63,22 @@ class Engine:
             model.load(tensors)
             del tensors
             cache = Cache(model.cache_needs(), max_tokens, max_context, dtype, device, max_slots=max_batch)
-        return cls(arch, config, model, cache, runtime)
+        return cls(arch, config, model, cache, runtime, use_graphs)
 
     @classmethod
     def from_pretrained(cls, folder, dtype="bfloat16", max_tokens: int | None = None, max_batch: int | None = None,
-                        max_context: int | None = None, device="cuda:0") -> "Engine":
+                        max_context: int | None = None, device="cuda:0", use_graphs: bool = True) -> "Engine":
         """A model folder (config.json + model.safetensors); the class is chosen by config.json."""
         folder = Path(folder)
         arch, config = load_config(folder)
         return cls._build(arch, config, lambda table, dev: load_weights(folder, table, dev), dtype, max_tokens,
-                          max_batch, max_context, device)
+                          max_batch, max_context, device, use_graphs)
 
     @classmethod
     def from_config(cls, config, seed: int = 0, dtype="bfloat16", max_tokens: int | None = None,
                     max_batch: int | None = None, max_context: int | None = None, device="cuda:0",
-                    std: float = 0.02, gain_std: float = 0.0, weight_dtype=torch.bfloat16) -> "Engine":
+                    std: float = 0.02, gain_std: float = 0.0, weight_dtype=torch.bfloat16,
+                    use_graphs: bool = True) -> "Engine":
         """Random weights made on the device (a dict with config.json's keys, or a typed config)."""
         if isinstance(config, dict):
             arch = architecture_of(config)
@@ -86,7 +87,7 @@ class Engine:
             arch = architecture_of({"architectures": list(config.architectures)})
         return cls._build(arch, config,
                           lambda table, dev: random_weights(table, seed, weight_dtype, dev, std, gain_std),
-                          dtype, max_tokens, max_batch, max_context, device)
+                          dtype, max_tokens, max_batch, max_context, device, use_graphs)
 
     # ------------------------------------------------------------------ sequences and steps
     def new_sequence(self) -> int:

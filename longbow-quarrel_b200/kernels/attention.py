@@ -5,16 +5,15 @@ import torch
 
 from . import ops
 
-TARGET_BLOCKS = 296          # two blocks for each of the 148 SMs
+RESIDENT_BLOCKS = 296        # two blocks of the decode kernel fit on each of the 148 SMs
 MAX_SPLITS = 32
-KEYS_PER_SPLIT = 256         # a slice shorter than this is not worth a block of its own
+KEYS_PER_SPLIT = 128         # a slice shorter than this is not worth a block of its own
 
 
 def decode_splits(n_tokens: int, Hkv: int, group_tiles: int, max_kv: int) -> int:
-    """How many slices to cut each sequence's keys into so that the GPU is filled."""
+    """How many slices to cut each sequence's keys into: as many as still run in one wave."""
     blocks = max(1, n_tokens * Hkv * group_tiles)
-    want = -(-TARGET_BLOCKS // blocks)
-    return max(1, min(want, MAX_SPLITS, -(-max_kv // KEYS_PER_SPLIT)))
+    return max(1, min(RESIDENT_BLOCKS // blocks, MAX_SPLITS, -(-max_kv // KEYS_PER_SPLIT)))
 
 
 def attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window):

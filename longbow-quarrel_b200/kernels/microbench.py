@@ -1,0 +1,179 @@
+"""Timing single kernels and single steps, for roofline work and for profilers.
+
+    python -m longbow_quarrel_b200.kernels.microbench gemm_stream --m 8 --n 28672 --k 4096 --epi swiglu
+    python -m longbow_quarrel_b200.kernels.microbench gemm_tc --m 2048 --n 6144 --k 4096
+    python -m longbow_quarrel_b200.kernels.microbench attn_decode --batch 8 --context 4096
+    python -m longbow_quarrel_b200.kernels.microbench attn_prefill --tokens 2048
+    python -m longbow_quarrel_b200.kernels.microbench step --batch 8 --context 4096 --layers 4
+
+Each kernel is timed with CUDA events over `--iters` launches after `--warmup`; operands
+are rotated through enough copies to exceed the 126 MB L2, so every launch reads from
+HBM.  One JSON line is printed: time, bytes or flops moved, achieved GB/s and TFLOP/s.
+`step` builds a model of Llama-3.1-8B layer sizes with `--layers` layers, fills the cache
+of `--batch` sequences to `--context` tokens with random keys and values (no prefill),
+and runs decode steps; with `--eager` the step's kernels are launched one by one instead
+of replaying a captured graph, which is what a launch-by-launch profile wants.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+
+L2_BYTES = 126 * 1024 * 1024
+EPIS = {"bf16": 0, "f32": 1, "resid": 2, "swiglu": 3}
+
+
+def _time(fn, iters: int, warmup: int) -> float:
+    for i in range(warmup):
+        fn(i)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for i in range(iters):
+        fn(warmup + i)
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def _copies(nbytes: int) -> int:
+    return max(2, -(-2 * L2_BYTES // max(nbytes, 1)))
+
+
+def bench_gemm(kind: str, args) -> dict:
+    from . import ops
+    M, N, K, epi = args.m, args.n, args.k, EPIS[args.epi]
+    dev = "cuda"
+    n = min(_copies(N * K * 2), 64)
+    ws = [torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(n)]
+    xs = [torch.randn(M, K, device=dev, dtype=torch.bfloat16) for _ in range(n)]
+    res = torch.zeros(M, N, device=dev, dtype=torch.float32) if args.epi == "resid" else None
+    fn = {"gemm_skinny": ops.gemm_skinny, "gemm_stream": ops.gemm_stream, "gemm_tc": ops.gemm_tc}[kind]
+    outs = {}
+
+    def run(i):
+        outs["o"] = fn(xs[i % n], ws[i % n], epi, res)
+    ms = _time(run, args.iters, args.warmup)
+    out_bytes = outs["o"].numel() * outs["o"].element_size() * (2 if args.epi == "resid" else 1)
+    nbytes = N * K * 2 + M * K * 2 + out_bytes
+    flops = 2.0 * M * N * K
+    return {"kernel": kind, "M": M, "N": N, "K": K, "epi": args.epi, "ms": ms, "bytes": nbytes,
+            "gbs": nbytes / ms / 1e6, "tflops": flops / ms / 1e9, "weight_copies": n}
+
+
+def _paged(batch: int, context: int, Hkv: int, hd: int, dev):
+    pages_per = -(-context // 64)
+    n_pages = batch * pages_per
+    k = torch.randn(n_pages, Hkv, 64, hd, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(n_pages, Hkv, 64, hd, device=dev, dtype=torch.bfloat16)
+    table = torch.randperm(n_pages, device=dev).to(torch.int32).reshape(batch, pages_per).contiguous()
+    return k, v, table
+
+
+def bench_attn_decode(args) -> dict:
+    from . import attention, ops
+    B, C, H, Hkv, hd = args.batch, args.context, args.heads, args.kv_heads, args.head_dim
+    dev = "cuda"
+    n = min(_copies(B * C * Hkv * hd * 4), 16)
+    caches = [_paged(B, C, Hkv, hd, dev) for _ in range(n)]
+    q = torch.randn(B, (H + 2 * Hkv) * hd, device=dev, dtype=torch.bfloat16)
+    pos = torch.full((B,), C - 1, dtype=torch.int32, device=dev)
+    seq = torch.arange(B, dtype=torch.int32, device=dev)
+    splits = args.splits or attention.decode_splits(B, Hkv, -(-(H // Hkv) // 16), C)
+
+    def run(i):
+        k, v, table = caches[i % n]
+        ops.attn_decode(q, k, v, table, pos, seq, seq, H, Hkv, hd, 64, hd ** -0.5, None, splits)
+    ms = _time(run, args.iters, args.warmup)
+    nbytes = B * C * Hkv * hd * 2 * 2
+    return {"kernel": "attn_decode", "batch": B, "context": C, "heads": H, "kv_heads": Hkv, "head_dim": hd,
+            "splits": splits, "ms": ms, "bytes": nbytes, "gbs": nbytes / ms / 1e6}
+
+
+def bench_attn_prefill(args) -> dict:
+    from . import ops
+    T, H, Hkv, hd = args.tokens, args.heads, args.kv_heads, args.head_dim
+    dev = "cuda"
+    k, v, table = _paged(1, T, Hkv, hd, dev)
+    q = torch.randn(T, (H + 2 * Hkv) * hd, device=dev, dtype=torch.bfloat16)
+    nb = -(-T // 64)
+    starts = torch.arange(nb - 1, -1, -1, dtype=torch.int32, device=dev) * 64
+    blocks = (torch.zeros(nb, dtype=torch.int32, device=dev), starts.contiguous(),
+              torch.minimum(torch.full_like(starts, 64), T - starts).contiguous(), starts.clone())
+    slots = torch.zeros(1, dtype=torch.int32, device=dev)
+    kv_len = torch.full((1,), T, dtype=torch.int32, device=dev)
+
+    def run(i):
+        ops.attn_prefill(q, k, v, table, slots, kv_len, blocks, H, Hkv, hd, 64, hd ** -0.5, None)
+    ms = _time(run, args.iters, args.warmup)
+    flops = 4.0 * H * hd * T * (T + 1) / 2.0
+    return {"kernel": "attn_prefill", "tokens": T, "heads": H, "kv_heads": Hkv, "head_dim": hd, "ms": ms,
+            "tflops": flops / ms / 1e9}
+
+
+def bench_step(args) -> dict:
+    import numpy as np
+
+    from ..engine import Engine
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, num_hidden_layers=args.layers,
+               num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336,
+               vocab_size=128256, rope_theta=500000.0, rms_norm_eps=1e-5, max_position_embeddings=131072,
+               rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                 original_max_position_embeddings=8192))
+    B, C = args.batch, args.context
+    eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=B * (C + 64), max_batch=B,
+                             max_context=C + 64, use_graphs=not args.eager)
+    for g in eng.cache.kv_groups:
+        g.k_pages.normal_()
+        g.v_pages.normal_()
+    slots = [eng.new_sequence() for _ in range(B)]
+    start = C - args.iters - args.warmup
+    for s in slots:                       # the cache holds `start` tokens of random keys and values
+        eng.cache.reserve(s, start)
+        eng.cache.commit(s, start)
+    rng = np.random.default_rng(0)
+    feed = rng.integers(0, cfg["vocab_size"], (args.iters + args.warmup, B))
+
+    def run(i):
+        eng.step([(s, [int(t)]) for s, t in zip(slots, feed[i])])
+    ms = _time(run, args.iters, args.warmup)
+    return {"kernel": "decode step", "batch": B, "context": C, "layers": args.layers, "graph": not args.eager,
+            "ms": ms, "tokens_per_s": B / ms * 1e3}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("what", choices=["gemm_skinny", "gemm_stream", "gemm_tc", "attn_decode", "attn_prefill", "step"])
+    ap.add_argument("--m", type=int, default=8)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--epi", default="bf16", choices=sorted(EPIS))
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--eager", action="store_true")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args(argv)
+    if args.what in ("gemm_skinny", "gemm_stream", "gemm_tc"):
+        out = bench_gemm(args.what, args)
+    elif args.what == "attn_decode":
+        out = bench_attn_decode(args)
+    elif args.what == "attn_prefill":
+        out = bench_attn_prefill(args)
+    else:
+        out = bench_step(args)
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,4 +1,10 @@
-"""Tensor-core paths of the bfloat16 matrix products."""
+"""Tensor-core paths of the bfloat16 matrix products: which kernel takes which shape.
+
+rows <= 16   gemm_skinny: W streamed through registers into mma.sync (fastest measured stream
+             of W: the loads of all warps keep more bytes in flight than one TMA unit does)
+rows <= 64   gemm_stream: W streamed by TMA in equal shares over all SMs into tcgen05
+more rows    gemm_tc: 128 x 256 tiles, TMA ring, tcgen05 with two accumulators in tensor memory
+"""
 from __future__ import annotations
 
 import torch
@@ -6,20 +12,19 @@ import torch
 from . import ops
 
 
+def _decode_kernel(M: int):
+    return ops.gemm_skinny if M <= ops.SKINNY_BEST_ROWS else ops.gemm_stream
+
+
 def linear_bf16(a, weight, out_dtype, residual):
     """a [M, K] bf16 . W^T; returns None when no tensor-core kernel takes this product."""
     M, K = a.shape
     if K % 8:
         return None
-    if M <= ops.SKINNY_MAX_ROWS:
-        if residual is not None:
-            return ops.gemm_skinny(a, weight.tensor, ops.EPI_RESID, residual)
-        if out_dtype == torch.float32:
-            return ops.gemm_skinny(a, weight.tensor, ops.EPI_F32)
-        return ops.gemm_skinny(a, weight.tensor, ops.EPI_BF16)
+    fn = _decode_kernel(M) if M <= ops.SKINNY_MAX_ROWS else ops.gemm_tc
     if residual is not None:
-        return ops.gemm_tc(a, weight.tensor, ops.EPI_RESID, residual)
-    return ops.gemm_tc(a, weight.tensor, ops.EPI_F32 if out_dtype == torch.float32 else ops.EPI_BF16)
+        return fn(a, weight.tensor, ops.EPI_RESID, residual)
+    return fn(a, weight.tensor, ops.EPI_F32 if out_dtype == torch.float32 else ops.EPI_BF16)
 
 
 def linear_swiglu_bf16(a, weight):
@@ -27,6 +32,5 @@ def linear_swiglu_bf16(a, weight):
     M, K = a.shape
     if K % 8:
         return None
-    if M <= ops.SKINNY_MAX_ROWS:
-        return ops.gemm_skinny(a, weight.tensor, ops.EPI_SWIGLU)
-    return ops.gemm_tc(a, weight.tensor, ops.EPI_SWIGLU)
+    fn = _decode_kernel(M) if M <= ops.SKINNY_MAX_ROWS else ops.gemm_tc
+    return fn(a, weight.tensor, ops.EPI_SWIGLU)
