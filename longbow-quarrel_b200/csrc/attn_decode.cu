@@ -298,3 +298,56 @@ LQ_EXPORT int lq_attn_decode(const void* q, int q_stride, const void* k_pages, c
     LQ_GO(128);
 #undef LQ_GO
 }
+
+// ------------------------------------------------------------------ the entry point that allocates nothing
+// Declared and described in attn_decode_static.h.  No counterpart in the reference.
+#include "attn_decode_static.h"
+
+namespace {
+
+constexpr int STATIC_MAX_DEVICES = 64;
+
+// The scratch of lq_attn_decode_static.  In host code this name is a handle for the runtime,
+// not a device address: the address comes from cudaGetSymbolAddress, once per device.
+static __device__ __align__(256) float lq_attn_static_scratch[LQ_ATTN_STATIC_FLOATS];
+
+float* static_scratch_of_current_device(int* error) {
+    static float* address[STATIC_MAX_DEVICES] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { *error = (int)e; return nullptr; }
+    if (dev < 0 || dev >= STATIC_MAX_DEVICES) { *error = LQ_BAD_SIZE; return nullptr; }
+    if (!address[dev]) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, lq_attn_static_scratch);   // the current device's copy of the array
+        if (e != cudaSuccess) { *error = (int)e; return nullptr; }
+        address[dev] = p;
+    }
+    *error = LQ_OK;
+    return address[dev];
+}
+
+}  // namespace
+
+LQ_EXPORT long lq_attn_decode_static_floats(void) { return LQ_ATTN_STATIC_FLOATS; }
+
+LQ_EXPORT int lq_attn_decode_static(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+                                    const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
+                                    const int* slots, void* out, int T, int H, int Hkv, int head_dim, int page_size,
+                                    float scale, int window, int n_splits, cudaStream_t stream) {
+    if (T <= 0) return LQ_OK;
+    if (H <= 0 || Hkv <= 0 || head_dim <= 0 || n_splits < 1) return LQ_BAD_SIZE;
+    float* part_o = nullptr;
+    float* part_ml = nullptr;
+    if (n_splits > 1) {
+        const long long rows = (long long)T * H * n_splits;
+        if (rows * (head_dim + 2) > (long long)LQ_ATTN_STATIC_FLOATS) return LQ_STATIC_TOO_SMALL;
+        int error = LQ_OK;
+        float* base = static_scratch_of_current_device(&error);
+        if (!base) return error;
+        part_o = base;                               // [T, H, n_splits, head_dim]
+        part_ml = base + rows * head_dim;            // [T, H, n_splits, 2]
+    }
+    return lq_attn_decode(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, part_o,
+                          part_ml, out, T, H, Hkv, head_dim, page_size, scale, window, n_splits, stream);
+}

@@ -42,7 +42,7 @@ def _nvcc() -> str:
 
 def _sources_hash(name: str, extra_flags: list[str]) -> str:
     h = hashlib.sha256()
-    for path in [CSRC / f"{name}.cu", *sorted(CSRC.glob("*.cuh"))]:
+    for path in [CSRC / f"{name}.cu", *sorted(CSRC.glob("*.cuh")), *sorted(CSRC.glob("*.h"))]:
         h.update(path.name.encode())
         h.update(path.read_bytes())
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + extra_flags).encode())
