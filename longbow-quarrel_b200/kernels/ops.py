@@ -87,7 +87,7 @@ def _contig(t: torch.Tensor, what: str) -> torch.Tensor:
 def prepare(dtype: torch.dtype, verbose: bool = True) -> None:
     """Build and load the libraries a model of this dtype uses, before the first step."""
     from concurrent.futures import ThreadPoolExecutor
-    names = ["plain_kernels", "sampling"] + (["gemm_skinny", "gemm_stream", "gemm_tc", "attn_decode", "attn_prefill"]
+    names = ["plain_kernels"] + (["gemm_skinny", "gemm_stream", "gemm_tc", "attn_decode", "attn_prefill"]
                                              if dtype == torch.bfloat16 else [])
     with ThreadPoolExecutor(max_workers=len(names)) as pool:
         list(pool.map(build.build, names))

@@ -190,3 +190,28 @@ def test_temperature_generation_is_reproducible_and_independent_of_the_batch(tmp
 def test_smoke_entry_point():
     import __graft_entry__
     __graft_entry__.smoke()
+
+
+def test_command_line_generates_the_plain_implementations_tokens(tmp_path):
+    """bin/quarrel with the reference's option names, greedy, two prompts, JSON output."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    folder = make_model_folder(tmp_path, "A", seed=25)
+    cfg, weights = plain_llama.load_folder(folder)
+    exe = Path(__file__).resolve().parent.parent / "bin" / "quarrel"
+    proc = subprocess.run([str(exe), "-model", str(folder), "-prompt-ids", "3,1,4,1,5;9,2,6", "-n", "6", "-temp", "0",
+                           "-dtype", "float32", "-output", "json", "-kv-cache-size", "64"],
+                          capture_output=True, text=True, timeout=300, env={**os.environ, "LQ_PYTHON": sys.executable})
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    out = json.loads(proc.stdout.strip().splitlines()[-1])
+    assert out["tokens_generated"] == 12 and set(out) >= {"throughput_tokens_per_sec", "prefill_duration_seconds",
+                                                          "generation_duration_seconds", "total_duration_seconds"}
+    for prompt, new in zip(([3, 1, 4, 1, 5], [9, 2, 6]), out["output"]):
+        assert new == plain_llama.greedy(cfg, weights, prompt, 6)       # config A names no bos token: none is added
+    text = subprocess.run([str(exe), "-model", str(folder), "-prompt", "Hi", "-n", "3", "-temp", "0.7", "-topk", "40",
+                           "-topp", "0.95", "-penalty", "1.1", "-seed", "7", "-stream"], capture_output=True, text=True,
+                          timeout=300, env={**os.environ, "LQ_PYTHON": sys.executable})
+    assert text.returncode == 0 and "3 tokens in" in text.stdout and "Longbow-Quarrel" in text.stdout

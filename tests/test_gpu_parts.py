@@ -229,3 +229,99 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
         if i < 2:
             assert np.allclose(rest[i][1], whole[8 + i], atol=1e-5)
     assert not np.allclose(whole[1], whole[0])
+
+
+# ------------------------------------------------------------------ the order of layers is data
+def test_a_layer_run_twice_and_a_layer_that_reads_anothers_cache():
+    """Schedule: layer 0 (cache entry 0), layer 1 reading entry 0 without keys and values of its
+    own, then layer 0 once more (cache entry 1).  Compared with the same computation spelled out
+    with the plain functions, whole and token by token."""
+    from dataclasses import dataclass
+
+    from longbow_quarrel_b200.config import register_architecture
+    from longbow_quarrel_b200.engine import Engine
+    from longbow_quarrel_b200.parts import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+
+    D, H, Hkv, hd, F, V = 64, 4, 2, 16, 96, 120
+
+    @dataclass(frozen=True)
+    class Cfg:
+        architectures: tuple = ("ToyScheduleLM",)
+
+    def describe(cfg):
+        norm = lambda name: PartSpec("rms_norm", {"size": D, "eps": 1e-5, "name": name})  # noqa: E731
+        rope = PartSpec("rope", {"head_dim": hd, "theta": 1e4})
+        attn = lambda own: PartSpec("attention", {"hidden_size": D, "n_heads": H, "n_kv_heads": Hkv, "head_dim": hd,  # noqa: E731
+                                                  "scale": hd ** -0.5, "position": rope, "own_kv": own})
+        ffn = PartSpec("gated_mlp", {"hidden_size": D, "intermediate_size": F})
+        layers = (LayerSpec("a.", attn(True), ffn, norm("n1"), norm("n2")),
+                  LayerSpec("b.", attn(False), ffn, norm("n1"), norm("n2")))
+        return ModelSpec(name="ToyScheduleLM", hidden_size=D, vocab_size=V,
+                         embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": D, "name": "emb"}),
+                         layers=layers,
+                         schedule=(ScheduleEntry(0, 0), ScheduleEntry(1, 0, writes_cache=False), ScheduleEntry(0, 1)),
+                         final_norm=norm("fn"),
+                         head=PartSpec("linear_head", {"vocab_size": V, "hidden_size": D, "name": "head",
+                                                       "tied_to": "emb", "tied": True}),
+                         max_positions=256)
+
+    register_architecture("ToyScheduleLM", lambda d: Cfg(), describe)
+    tokens = [int(t) for t in np.random.default_rng(3).integers(0, V, 45)]
+    for dtype, tol in (("float32", 1e-4), ("bfloat16", 6e-2)):
+        eng = Engine.from_config({"architectures": ["ToyScheduleLM"]}, seed=5, dtype=dtype, max_tokens=512,
+                                 gain_std=0.1)
+        assert "b.k_proj.weight" not in eng.model.weight_table() and "b.q_proj.weight" in eng.model.weight_table()
+        assert sorted(eng.model.cache_needs()) == [0, 1]
+        # the same weights for the plain computation
+        W = {}
+        for blk in eng.model.blocks:
+            m = blk.mixer
+            wq = m.w_qkv.tensor.double().cpu()
+            W[blk.prefix + "q"] = wq[:H * hd]
+            if m.own_kv:
+                W[blk.prefix + "k"], W[blk.prefix + "v"] = wq[H * hd:(H + Hkv) * hd], wq[(H + Hkv) * hd:]
+            W[blk.prefix + "o"] = m.w_o.tensor.double().cpu()
+            gu = blk.ffn.w_gu.tensor.double().cpu()
+            if blk.ffn.block:
+                gu = gu.reshape(F // 8, 2, 8, D)
+                W[blk.prefix + "g"], W[blk.prefix + "u"] = gu[:, 0].reshape(F, D), gu[:, 1].reshape(F, D)
+            else:
+                W[blk.prefix + "g"], W[blk.prefix + "u"] = gu[:F], gu[F:]
+            W[blk.prefix + "d"] = blk.ffn.w_down.tensor.double().cpu()
+            W[blk.prefix + "n1"], W[blk.prefix + "n2"] = blk.norm1.gain.double().cpu(), blk.norm2.gain.double().cpu()
+        emb = eng.model.embedding.table.double().cpu()
+        fn = eng.model.final_norm.gain.double().cpu()
+        T = len(tokens)
+        f = pl.rope_frequencies(hd, 1e4, None)
+        pos = np.arange(T)
+
+        def block(p, x, shared_kv=None):
+            n = pl.rms_norm(x, W[p + "n1"], 1e-5)
+            q = pl.rope(pl.linear(n, W[p + "q"]).reshape(T, H, hd), pos, f)
+            if shared_kv is None:
+                k = pl.rope(pl.linear(n, W[p + "k"]).reshape(T, Hkv, hd), pos, f)
+                v = pl.linear(n, W[p + "v"]).reshape(T, Hkv, hd)
+            else:
+                k, v = shared_kv
+            x = x + pl.linear(pl.attention(q, k, v, hd ** -0.5).reshape(T, H * hd), W[p + "o"])
+            n = pl.rms_norm(x, W[p + "n2"], 1e-5)
+            x = x + pl.linear(pl.swiglu(pl.linear(n, W[p + "g"]), pl.linear(n, W[p + "u"])), W[p + "d"])
+            return x, (k, v)
+
+        x = pl.embedding(emb, tokens)
+        x, kv0 = block("a.", x)
+        x, _ = block("b.", x, shared_kv=kv0)
+        x, _ = block("a.", x)
+        ref = pl.linear(pl.rms_norm(x, fn, 1e-5), emb).numpy()
+
+        slot = eng.new_sequence()
+        whole = eng.step([(slot, tokens)], want=[list(range(T))]).cpu().numpy()
+        eng.end_sequence(slot)
+        assert rel_err(whole, ref) < tol, dtype
+        slot = eng.new_sequence()
+        head = eng.step([(slot, tokens[:20])], want=[[19]]).cpu().numpy()
+        assert rel_err(head[0], ref[19]) < tol
+        for i in range(20, T):
+            got = eng.step([(slot, [tokens[i]])]).cpu().numpy()[0]
+            assert rel_err(got, ref[i]) < tol, (dtype, i)
+        eng.end_sequence(slot)

@@ -53,3 +53,32 @@ def test_replay_all_cuts_match_plain(tmp_path, name, dtype):
         assert rel_err(row, whole[key]) < cut_tol, ("tail vs whole", key)
     for key, row in batched.items():
         assert rel_err(row, whole[key]) < cut_tol, ("batched vs whole", key)
+
+
+def test_max_tokens_sizes_the_cache_exactly(tmp_path):
+    """--max-tokens is the most tokens live requests hold, each rounded up to 64: the trace runs
+    with exactly that, and is refused with one page less."""
+    import subprocess
+    import sys
+
+    from trace_tools import TRACE_RUN, Trace
+    folder = make_model_folder(tmp_path, "A", seed=12)
+    tr = Trace()
+    a, b, c = random_tokens(70, 256, 1), random_tokens(64, 256, 2), random_tokens(10, 256, 3)
+    tr.add([("a", a, [69]), ("b", b, [63])])                  # 128 + 64 tokens held
+    tr.add([("a", [5], [0]), ("b", [6], [0])], end=["a"])     # b grows into a second page: 128 + 128
+    tr.add([("b", [7], [0]), ] , end=[])                      # a's pages are back: 128 held
+    tr.add([("c", c, [9])], end=["b", "c"])                   # a new request takes freed pages: 128 + 64
+    assert tr.max_tokens == 256
+    got = run_trace(folder, "float32", tr, tmp_path / "exact", max_tokens=256)
+    ref = plain_logits(folder, a + [5])
+    assert rel_err(got[("a", 70)], ref[70]) < TOL["float32"]
+    ref = plain_logits(folder, c)
+    assert rel_err(got[("c", 9)], ref[9]) < TOL["float32"]
+    import json
+    text = "".join(json.dumps(s) + "\n" for s in tr.steps)
+    proc = subprocess.run([str(TRACE_RUN), "--model", str(folder), "--dtype", "float32", "--out", str(tmp_path / "small"),
+                           "--max-tokens", "192"], input=text, capture_output=True, text=True, timeout=300,
+                          env={**__import__("os").environ, "LQ_PYTHON": sys.executable})
+    assert proc.returncode != 0 and "cache is full" in proc.stderr
+    assert proc.stdout.splitlines() == ["done 0"]             # the first step fits; the second does not

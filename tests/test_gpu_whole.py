@@ -22,3 +22,44 @@ def test_whole_sequence_matches_plain(tmp_path, name, dtype):
         ref = plain_logits(folder, tokens)
         assert rel_err(got, ref) < TOL[dtype], (name, dtype, n)
     assert eng.cache.pages_in_use() == 0
+
+
+def test_weights_stored_in_32_bit_stay_32_bit(tmp_path):
+    """A checkpoint stored in float32 is read as float32: the 32-bit path then agrees with the
+    plain implementation on weights that bfloat16 could not hold."""
+    import torch
+    from longbow_quarrel_b200.engine import Engine
+    folder = make_model_folder(tmp_path, "A", seed=4, dtype=torch.float32)
+    eng = Engine.from_pretrained(folder, dtype="float32", max_tokens=256)
+    assert eng.model.embedding.table.dtype == torch.float32
+    assert eng.model.blocks[0].mixer.w_qkv.tensor.dtype == torch.float32
+    tokens = random_tokens(50, 256, 8)
+    slot = eng.new_sequence()
+    got = eng.step([(slot, tokens)], want=[list(range(50))]).cpu().numpy()
+    assert rel_err(got, plain_logits(folder, tokens)) < TOL["float32"]
+    # the bfloat16 engine takes the same folder: 32-bit weights go through the plain product
+    eng16 = Engine.from_pretrained(folder, dtype="bfloat16", max_tokens=256)
+    slot = eng16.new_sequence()
+    got = eng16.step([(slot, tokens)], want=[list(range(50))]).cpu().numpy()
+    assert rel_err(got, plain_logits(folder, tokens)) < TOL["bfloat16"]
+
+
+def test_step_errors_are_raised_before_anything_runs(tmp_path):
+    from longbow_quarrel_b200.cache import CacheError
+    from longbow_quarrel_b200.engine import Engine, StepError
+    folder = make_model_folder(tmp_path, "A", seed=5)
+    eng = Engine.from_pretrained(folder, dtype="float32", max_tokens=128)
+    slot = eng.new_sequence()
+    with pytest.raises(StepError, match="outside the vocabulary"):
+        eng.step([(slot, [1, 256])])
+    with pytest.raises(StepError, match="no tokens"):
+        eng.step([(slot, [])])
+    with pytest.raises(StepError, match="twice"):
+        eng.step([(slot, [1]), (slot, [2])])
+    with pytest.raises(StepError, match="wanted place"):
+        eng.step([(slot, [1, 2])], want=[[2]])
+    with pytest.raises(CacheError, match="context limit|cache is full"):
+        eng.step([(slot, [1] * 129)])
+    assert eng.cache.length(slot) == 0
+    eng.step([(slot, [1, 2, 3])])
+    assert eng.cache.length(slot) == 3
