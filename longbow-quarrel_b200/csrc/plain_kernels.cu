@@ -72,16 +72,67 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
         out[(size_t)r * D + i] = from_f32<TO>(xr[i] * scale * gain[i]);
 }
 
+// Rows whose length is a multiple of 4 and at most 256 * 4 * RMS_VEC: each thread keeps its
+// part of the row in registers (one read of x), float4 loads, packed stores.  The sum of squares
+// runs in an order fixed by the row length alone.
+constexpr int RMS_VEC = 8;   // float4 pieces per thread
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ gain, const int* __restrict__ rows,
+                   TO* __restrict__ out, int D, float eps) {
+    __shared__ float partial[8];
+    __shared__ float scale_s;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x, n4 = D >> 2;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * D);
+    float4 v[RMS_VEC];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < RMS_VEC; ++i) {
+        int c = threadIdx.x + i * 256;
+        v[i] = c < n4 ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        s = fmaf(v[i].x, v[i].x, s); s = fmaf(v[i].y, v[i].y, s);
+        s = fmaf(v[i].z, v[i].z, s); s = fmaf(v[i].w, v[i].w, s);
+    }
+    s = warp_sum(s);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < 8; ++w) t += partial[w];
+        scale_s = 1.0f / sqrtf(t / (float)D + eps);
+    }
+    __syncthreads();
+    const float scale = scale_s;
+    const float4* g4 = reinterpret_cast<const float4*>(gain);
+#pragma unroll
+    for (int i = 0; i < RMS_VEC; ++i) {
+        int c = threadIdx.x + i * 256;
+        if (c >= n4) break;
+        float4 g = g4[c];
+        float o0 = v[i].x * scale * g.x, o1 = v[i].y * scale * g.y, o2 = v[i].z * scale * g.z, o3 = v[i].w * scale * g.w;
+        if (sizeof(TO) == 4) {
+            reinterpret_cast<float4*>(out + (size_t)r * D)[c] = make_float4(o0, o1, o2, o3);
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(o0, o1), hi = __floats2bfloat162_rn(o2, o3);
+            uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            reinterpret_cast<uint2*>(out + (size_t)r * D)[c] = packed;
+        }
+    }
+}
+
 LQ_EXPORT int lq_rmsnorm(const float* x, const float* gain, const int* rows, void* out, int out_dtype,
                          int n_rows, int D, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return LQ_OK;
+    if (out_dtype != LQ_F32 && out_dtype != LQ_BF16) return LQ_BAD_DTYPE;
+    const bool vec = D % 4 == 0 && D <= 256 * 4 * RMS_VEC && (((uintptr_t)x | (uintptr_t)gain | (uintptr_t)out) & 15) == 0;
     if (out_dtype == LQ_F32)
-        return launch_pdl(rmsnorm_kernel<float>, dim3(n_rows), dim3(256), 0, stream, x, gain, rows, (float*)out, D, eps);
-    else if (out_dtype == LQ_BF16)
-        return launch_pdl(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, x, gain, rows, (__nv_bfloat16*)out, D, eps);
-    else
-        return LQ_BAD_DTYPE;
-    return lq_launch_status();
+        return vec ? launch_pdl(rmsnorm_vec_kernel<float>, dim3(n_rows), dim3(256), 0, stream, x, gain, rows, (float*)out, D, eps)
+                   : launch_pdl(rmsnorm_kernel<float>, dim3(n_rows), dim3(256), 0, stream, x, gain, rows, (float*)out, D, eps);
+    return vec ? launch_pdl(rmsnorm_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, x, gain, rows, (__nv_bfloat16*)out, D, eps)
+               : launch_pdl(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, x, gain, rows, (__nv_bfloat16*)out, D, eps);
 }
 
 // ------------------------------------------------------------------ linear (FFMA)
@@ -221,6 +272,82 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
     }
 }
 
+// The same work with 16-byte accesses, for half head sizes that are a multiple of the vector
+// length (8 bfloat16 or 4 float32): a thread rotates VEC pairs of one head at a time.
+template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_kv_write_vec_kernel(T* __restrict__ qkv, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                         const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
+                         const int* __restrict__ page_table, int pt_stride, T* __restrict__ k_pages,
+                         T* __restrict__ v_pages, int H, int Hkv, int hd, int page_size, int has_kv) {
+    constexpr int VEC = Vec16<T>::N;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    const int half = hd >> 1, pieces = half / VEC;
+    const int row_w = (H + (has_kv ? 2 * Hkv : 0)) * hd;
+    T* row = qkv + (size_t)t * row_w;
+    const float* cs = cos_t ? cos_t + (size_t)pos * half : nullptr;
+    const float* sn = sin_t ? sin_t + (size_t)pos * half : nullptr;
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (has_kv) {
+        int slot = slots[tok_seq[t]];
+        int page = page_table[(size_t)slot * pt_stride + pos / page_size];
+        size_t base = ((size_t)page * Hkv * page_size + (pos % page_size)) * hd;
+        kdst = k_pages + base;
+        vdst = v_pages + base;
+    }
+    const int n_rot = (H + (has_kv ? Hkv : 0)) * pieces;
+    for (int i = threadIdx.x; i < n_rot; i += blockDim.x) {
+        const int head = i / pieces, j = (i % pieces) * VEC;
+        T* p = row + (size_t)head * hd;
+        uint4 a = *reinterpret_cast<const uint4*>(p + j), b = *reinterpret_cast<const uint4*>(p + j + half);
+        const T* x0 = reinterpret_cast<const T*>(&a);
+        const T* x1 = reinterpret_cast<const T*>(&b);
+        uint4 oa, ob;
+        T* y0 = reinterpret_cast<T*>(&oa);
+        T* y1 = reinterpret_cast<T*>(&ob);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            float u = to_f32(x0[e]), w = to_f32(x1[e]);
+            float c = cs ? cs[j + e] : 1.f, s = sn ? sn[j + e] : 0.f;
+            y0[e] = from_f32<T>(u * c - w * s);
+            y1[e] = from_f32<T>(u * s + w * c);
+        }
+        *reinterpret_cast<uint4*>(p + j) = oa;
+        *reinterpret_cast<uint4*>(p + j + half) = ob;
+        if (head >= H) {
+            T* d = kdst + (size_t)(head - H) * page_size * hd;
+            *reinterpret_cast<uint4*>(d + j) = oa;
+            *reinterpret_cast<uint4*>(d + j + half) = ob;
+        }
+    }
+    if (has_kv) {
+        const T* vsrc = row + (size_t)(H + Hkv) * hd;
+        const int per_head = hd / VEC;
+        for (int i = threadIdx.x; i < Hkv * per_head; i += blockDim.x) {
+            int head = i / per_head, j = (i % per_head) * VEC;
+            *reinterpret_cast<uint4*>(vdst + (size_t)head * page_size * hd + j) =
+                *reinterpret_cast<const uint4*>(vsrc + (size_t)head * hd + j);
+        }
+    }
+}
+
+template <typename T>
+static int rope_launch(void* qkv, const float* cos_t, const float* sin_t, const int* tok_pos, const int* tok_seq,
+                       const int* slots, const int* page_table, int pt_stride, void* k_pages, void* v_pages, int Tn,
+                       int H, int Hkv, int hd, int page_size, int has_kv, cudaStream_t stream) {
+    constexpr int VEC = Vec16<T>::N;
+    const bool vec = (hd / 2) % VEC == 0 && (((uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0;
+    auto kernel = vec ? rope_kv_write_vec_kernel<T> : rope_kv_write_kernel<T>;
+    return launch_pdl(kernel, dim3(Tn), dim3(256), 0, stream, (T*)qkv, cos_t, sin_t, tok_pos, tok_seq, slots, page_table,
+                      pt_stride, (T*)k_pages, (T*)v_pages, H, Hkv, hd, page_size, has_kv);
+}
+
 LQ_EXPORT int lq_rope_kv_write(void* qkv, int dtype, const float* cos_t, const float* sin_t,
                                const int* tok_pos, const int* tok_seq, const int* slots,
                                const int* page_table, int pt_stride, void* k_pages, void* v_pages,
@@ -229,14 +356,12 @@ LQ_EXPORT int lq_rope_kv_write(void* qkv, int dtype, const float* cos_t, const f
     if (T <= 0) return LQ_OK;
     if (hd % 2) return LQ_BAD_SIZE;
     if (dtype == LQ_F32)
-        return launch_pdl(rope_kv_write_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)qkv, cos_t, sin_t, tok_pos, tok_seq, slots,
-            page_table, pt_stride, (float*)k_pages, (float*)v_pages, H, Hkv, hd, page_size, has_kv);
-    else if (dtype == LQ_BF16)
-        return launch_pdl(rope_kv_write_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)qkv, cos_t, sin_t, tok_pos, tok_seq, slots,
-            page_table, pt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, H, Hkv, hd, page_size, has_kv);
-    else
-        return LQ_BAD_DTYPE;
-    return lq_launch_status();
+        return rope_launch<float>(qkv, cos_t, sin_t, tok_pos, tok_seq, slots, page_table, pt_stride, k_pages, v_pages,
+                                  T, H, Hkv, hd, page_size, has_kv, stream);
+    if (dtype == LQ_BF16)
+        return rope_launch<__nv_bfloat16>(qkv, cos_t, sin_t, tok_pos, tok_seq, slots, page_table, pt_stride, k_pages,
+                                          v_pages, T, H, Hkv, hd, page_size, has_kv, stream);
+    return LQ_BAD_DTYPE;
 }
 
 // ------------------------------------------------------------------ attention over the cache

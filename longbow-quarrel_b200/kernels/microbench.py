@@ -5,6 +5,7 @@
     python -m longbow_quarrel_b200.kernels.microbench attn_decode --batch 8 --context 4096
     python -m longbow_quarrel_b200.kernels.microbench attn_prefill --tokens 2048
     python -m longbow_quarrel_b200.kernels.microbench step --batch 8 --context 4096 --layers 4
+    python -m longbow_quarrel_b200.kernels.microbench prefill --tokens 2048 --layers 4
 
 Each kernel is timed with CUDA events over `--iters` launches after `--warmup`; operands
 are rotated through enough copies to exceed the 126 MB L2, so every launch reads from
@@ -144,9 +145,30 @@ def bench_step(args) -> dict:
             "ms": ms, "tokens_per_s": B / ms * 1e3}
 
 
+def bench_prefill(args) -> dict:
+    import numpy as np
+
+    from ..engine import Engine
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, num_hidden_layers=args.layers,
+               num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336,
+               vocab_size=128256, rope_theta=500000.0, rms_norm_eps=1e-5, max_position_embeddings=131072,
+               rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                 original_max_position_embeddings=8192))
+    T = args.tokens
+    eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=T + 64, max_batch=1, max_context=T + 64)
+    rng = np.random.default_rng(0)
+
+    def run(i):
+        slot = eng.new_sequence()
+        eng.step([(slot, rng.integers(0, cfg["vocab_size"], T).tolist())])
+        eng.end_sequence(slot)
+    ms = _time(run, args.iters, args.warmup)
+    return {"kernel": "prefill step", "tokens": T, "layers": args.layers, "ms": ms, "tokens_per_s": T / ms * 1e3}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("what", choices=["gemm_skinny", "gemm_stream", "gemm_tc", "attn_decode", "attn_prefill", "step"])
+    ap.add_argument("what", choices=["gemm_skinny", "gemm_stream", "gemm_tc", "attn_decode", "attn_prefill", "step", "prefill"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -169,6 +191,8 @@ def main(argv=None) -> int:
         out = bench_attn_decode(args)
     elif args.what == "attn_prefill":
         out = bench_attn_prefill(args)
+    elif args.what == "prefill":
+        out = bench_prefill(args)
     else:
         out = bench_step(args)
     print(json.dumps(out))

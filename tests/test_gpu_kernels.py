@@ -54,7 +54,7 @@ def test_embedding(dtype):
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("D", [72, 1000, 4096])
+@pytest.mark.parametrize("D", [72, 1000, 4096, 70, 8192, 10000])      # 70 and 10000 take the scalar kernel
 def test_rmsnorm(out_dtype, D):
     ops = _ops()
     x = _rand((9, D), torch.float32, 1, 3.0)
@@ -180,9 +180,10 @@ def test_attention_plain(dtype, H, Hkv, hd, window):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_rope_kv_write(dtype):
+@pytest.mark.parametrize("hd", [32, 128, 20])            # 20: pairs that no 16-byte access covers
+def test_rope_kv_write(dtype, hd):
     ops = _ops()
-    H, Hkv, hd, page = 3, 2, 32, 64
+    H, Hkv, page = 3, 2, 64
     T = 5
     tok_seq, tok_pos = [0, 0, 1, 1, 1], [63, 64, 0, 1, 130]
     lens = [65, 131]
