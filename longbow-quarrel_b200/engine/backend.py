@@ -1,17 +1,48 @@
 """What the generation loop drives when it runs on the engine: the step function,
-then the sampler on the logits, then the sampled ids back to the host."""
+then the sampler on the logits, then the sampled ids back to the host.
+
+The loop asks for one step at a time and needs the sampled ids on the host to decide
+who stops.  So that the GPU does not idle while the host decides and prepares, the backend
+queues the step after the one asked for before it hands the ids back: that step takes its
+tokens on the device, straight from the sampler's output, and assumes that every sequence
+goes on.  When the loop then asks for that step, its work is already running; a sequence
+that stopped meanwhile has cost one unused row.  Sampling that needs the token history on
+the host (a repetition penalty) does not run ahead.
+"""
 from __future__ import annotations
+
+from dataclasses import dataclass
 
 import torch
 
+from ..cache import CacheError
 from ..sampling import SamplingParams, history_window, sample
 
 
+@dataclass
+class _Sampled:
+    """The sampled ids of one step: on the device, and on their way to pinned host memory (the
+    copy is queued right behind the sampler, before any later step, so that waiting for it does
+    not wait for a step that was queued ahead)."""
+    handles: tuple[int, ...]
+    device: torch.Tensor          # int32 [len(handles)]
+    host: torch.Tensor            # pinned int32 [>= len(handles)]
+    ready: torch.cuda.Event
+
+    def ids(self) -> list[int]:
+        self.ready.synchronize()
+        return self.host[:len(self.handles)].tolist()
+
+
 class EngineBackend:
-    def __init__(self, engine, params: SamplingParams):
+    def __init__(self, engine, params: SamplingParams, run_ahead: bool = True):
         self.engine, self.params = engine, params
         self.seed = params.resolved_seed()
+        self.run_ahead = run_ahead and not params.uses_history
         self._scratch = None
+        self._ahead: _Sampled | None = None
+        self._pinned: list[torch.Tensor] = []      # a small ring of pinned buffers for the sampled ids
+        self._turn = 0
 
     def start(self) -> int:
         return self.engine.new_sequence()
@@ -19,8 +50,8 @@ class EngineBackend:
     def finish(self, handle: int) -> None:
         self.engine.end_sequence(handle)
 
-    def run(self, entries, requests, steps, histories) -> list[int]:
-        logits = self.engine.stepper.step(entries, None)
+    # ------------------------------------------------------------------ one step and its sampling
+    def _sample(self, logits, requests, steps, histories):
         dev = logits.device
         seq_ids = step_ids = hist = hist_len = None
         if not self.params.greedy:
@@ -33,4 +64,32 @@ class EngineBackend:
             self._scratch = torch.empty_like(logits)
         tokens = sample(logits, self.params, self.seed, seq_ids, step_ids, hist, hist_len,
                         scratch=self._scratch[:logits.shape[0]])
-        return tokens.tolist()
+        n = tokens.numel()
+        if len(self._pinned) < 4:
+            self._pinned.append(torch.empty(max(n, self.engine.cache.max_slots), dtype=torch.int32).pin_memory())
+        self._turn = (self._turn + 1) % 4
+        host = self._pinned[min(self._turn, len(self._pinned) - 1)]
+        if host.numel() < n:
+            host = self._pinned[min(self._turn, len(self._pinned) - 1)] = torch.empty(n, dtype=torch.int32).pin_memory()
+        host[:n].copy_(tokens, non_blocking=True)
+        ready = torch.cuda.Event()
+        ready.record()
+        return tokens, host, ready
+
+    def run(self, entries, requests, steps, histories) -> list[int]:
+        handles = tuple(h for h, _ in entries)
+        ahead, self._ahead = self._ahead, None
+        single = all(len(t) == 1 for _, t in entries)
+        if ahead is not None and single and set(handles) <= set(ahead.handles):
+            current, rows = ahead, [ahead.handles.index(h) for h in handles]   # queued during the last call
+        else:
+            logits = self.engine.stepper.step(entries, None)
+            current, rows = _Sampled(handles, *self._sample(logits, requests, steps, histories)), list(range(len(handles)))
+        if self.run_ahead:
+            try:
+                logits = self.engine.stepper.step_fed(list(handles), current.device, rows)
+                self._ahead = _Sampled(handles, *self._sample(logits, requests, [s + 1 for s in steps], None))
+            except CacheError:
+                self._ahead = None       # no room for one more token: the loop will end these sequences or fail itself
+        ids = current.ids()
+        return [ids[r] for r in rows]

@@ -133,19 +133,48 @@ class Stepper:
             self.cache.commit(slot, len(tokens))
         return logits
 
-    def _decode_step(self, entries, want, past):
+    def step_fed(self, slots: list[int], source: torch.Tensor, rows: list[int] | None = None) -> torch.Tensor:
+        """One more token for each sequence in `slots`, the tokens taken on the device from
+        `source` (int32, e.g. what the sampler wrote for the step before): sequence b gets
+        source[rows[b]] (source[b] without rows).  The host never sees these tokens before the
+        step is launched, so the step can be queued while the one before it still runs."""
+        entries = [(s, [0]) for s in slots]
+        past = [self.cache.length(s) for s in slots]
+        for s in slots:
+            self.cache.reserve(s, 1)
+        self.cache.upload()
+        if rows is not None and rows != list(range(len(rows))):
+            source = source[torch.tensor(rows, dtype=torch.long, device=self.device)]
+        elif source.numel() != len(slots):
+            source = source[:len(slots)]
+        if self.use_graphs:
+            logits = self._decode_step(entries, None, past, fed=source)
+        else:
+            flat, info = pack_step(entries, None, past)
+            flat_dev = torch.from_numpy(flat).to(self.device)
+            ctx = make_context(flat_dev, info, slots)
+            ctx.tokens.copy_(source)
+            logits = self.model.forward(ctx, self.cache)
+        for s in slots:
+            self.cache.commit(s, 1)
+        return logits
+
+    def _decode_step(self, entries, want, past, fed: torch.Tensor | None = None):
         B = len(entries)
         flat, info = pack_step(entries, None, past)
         if B not in self._seen:
             # The first step of a batch size runs eagerly: it loads kernels and sizes buffers.
             self._seen.add(B)
             flat_dev = torch.from_numpy(flat).to(self.device)
-            logits = self.model.forward(make_context(flat_dev, info, [s for s, _ in entries]), self.cache)
+            ctx = make_context(flat_dev, info, [s for s, _ in entries])
+            if fed is not None:
+                ctx.tokens.copy_(fed)
+            logits = self.model.forward(ctx, self.cache)
         else:
             graph = self._graphs.get(B)
             if graph is None:
                 graph = self._graphs[B] = _DecodeGraph(self.model, self.cache, self.device, flat, info)
-            logits = graph.replay(flat)
+            logits = graph.replay(flat, fed)
         if want is None:
             return logits
         rows = [b for b, ws in enumerate(want) for _ in ws]
@@ -183,11 +212,14 @@ class _DecodeGraph:
         torch.cuda.current_stream(device).wait_stream(stream)
         self.copied.record()
 
-    def replay(self, flat: np.ndarray) -> torch.Tensor:
+    def replay(self, flat: np.ndarray, fed: torch.Tensor | None = None) -> torch.Tensor:
         self.copied.synchronize()
         self.host.numpy()[:] = flat
         self.flat_dev.copy_(self.host, non_blocking=True)
         self.copied.record()
+        if fed is not None:
+            o, n = self.info["layout"]["tokens"]
+            self.flat_dev[o:o + n].copy_(fed)
         self.graph.replay()
         ops.add_launches(self.kernels)
         return self.logits
