@@ -23,6 +23,7 @@ namespace {
 
 constexpr int DW = 4;            // warps per block
 constexpr int TILE = 16;         // keys per warp tile
+constexpr int MAX_SPLITS = 32;   // most slices a sequence's keys are cut into
 
 __device__ __forceinline__ uint4 ldg16(const void* p) {
     uint4 v;
@@ -51,12 +52,16 @@ __global__ void __launch_bounds__(DW * 32, 2)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_pages,
                    const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ page_table, int pt_stride,
                    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
-                   float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
-                   int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits) {
+                   float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
+                   __nv_bfloat16* __restrict__ out, int H, int Hkv, int hd, int page_size, float scale, int window,
+                   int n_splits) {
     constexpr int QB = HD / 32;                    // 32-wide blocks of the head dimension (Q.K^T)
     constexpr int VC = (HD + 63) / 64;             // 64-wide column groups (P.V)
     __shared__ float sm_o[DW][16][HD + 1];
     __shared__ float sm_m[DW][16], sm_l[DW][16];
+    __shared__ float sm_w[16][MAX_SPLITS];       // weights of the slices when this block merges them
+    __shared__ float sm_inv[16];
+    __shared__ int sm_last;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, tok = blockIdx.z;
@@ -243,38 +248,82 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
             if (d == 0) { part_ml[base * 2] = mx; part_ml[base * 2 + 1] = l; }
         }
     }
+    if (n_splits == 1 || counters == nullptr) return;
+    // The block that parks its slice last merges all slices of its (token, kv head, row tile):
+    // out = sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M), slices in their order.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* counter = counters + (size_t)tok * gridDim.y + blockIdx.y;
+        int old = atomicAdd(counter, 1);
+        sm_last = (old == n_splits - 1);
+        if (sm_last) *counter = 0;                  // ready for the next call
+    }
+    __syncthreads();
+    if (!sm_last) return;
+    __threadfence();
+    // Weights of the slices, one warp per row and one lane per slice (at most 32 slices).
+    for (int r = warp; r < rows; r += DW) {
+        const float* ml = part_ml + ((size_t)tok * H + kvh * G + gt * 16 + r) * n_splits * 2;
+        const float m = lane < n_splits ? __ldcg(ml + 2 * lane) : -CUDART_INF_F;
+        const float ls = lane < n_splits ? __ldcg(ml + 2 * lane + 1) : 0.f;
+        const float mx = warp_max(m);
+        const float w = m > -CUDART_INF_F ? expf(m - mx) : 0.f;
+        const float l = warp_sum(ls * w);        // the same order of additions whichever block merges
+        if (lane < n_splits) sm_w[r][lane] = w;
+        if (lane == 0) sm_inv[r] = 1.0f / l;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < rows * hd; i += DW * 32) {
+        const int r = i / hd, d = i % hd;
+        const int h = kvh * G + gt * 16 + r;
+        const float* po = part_o + ((size_t)tok * H + h) * n_splits * hd + d;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int s2 = 0; s2 < n_splits; ++s2) acc += __ldcg(po + (size_t)s2 * hd) * sm_w[r][s2];
+        out[((size_t)tok * H + h) * hd + d] = __float2bfloat16_rn(acc * sm_inv[r]);
+    }
 }
 
 // Merge the slices of one (token, head): out = sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M).
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   __nv_bfloat16* __restrict__ out, int hd, int n_splits) {
+    __shared__ float w[MAX_SPLITS];
+    __shared__ float inv;
     const size_t th = blockIdx.x;
     pdl_launch_dependents();
     pdl_wait();
     const float* ml = part_ml + th * n_splits * 2;
-    float mx = -CUDART_INF_F;
-    for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, ml[2 * s]);
-    float l = 0.f;
-    for (int s = 0; s < n_splits; ++s)
-        if (ml[2 * s] > -CUDART_INF_F) l += ml[2 * s + 1] * expf(ml[2 * s] - mx);
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        const float m = lane < n_splits ? ml[2 * lane] : -CUDART_INF_F;
+        const float ls = lane < n_splits ? ml[2 * lane + 1] : 0.f;
+        const float mx = warp_max(m);
+        const float f = m > -CUDART_INF_F ? expf(m - mx) : 0.f;
+        const float l = warp_sum(ls * f);
+        if (lane < n_splits) w[lane] = f;
+        if (lane == 0) inv = 1.0f / l;
+    }
+    __syncthreads();
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float acc = 0.f;
-        for (int s = 0; s < n_splits; ++s)
-            if (ml[2 * s] > -CUDART_INF_F) acc += part_o[(th * n_splits + s) * hd + d] * expf(ml[2 * s] - mx);
-        out[th * hd + d] = __float2bfloat16_rn(acc / l);
+#pragma unroll 8
+        for (int s = 0; s < n_splits; ++s) acc += part_o[(th * n_splits + s) * hd + d] * w[s];
+        out[th * hd + d] = __float2bfloat16_rn(acc * inv);
     }
 }
 
 template <int HD>
 int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages, const int* page_table, int pt_stride,
-           const int* tok_pos, const int* tok_seq, const int* slots, float* part_o, float* part_ml, void* out,
-           int T, int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits, cudaStream_t stream) {
+           const int* tok_pos, const int* tok_seq, const int* slots, float* part_o, float* part_ml, int* counters,
+           void* out, int T, int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
+           cudaStream_t stream) {
     int G = H / Hkv, gtiles = (G + 15) / 16;
     dim3 grid(n_splits, Hkv * gtiles, T);
     int rc = launch_pdl(attn_decode_kernel<HD>, grid, dim3(DW * 32), 0, stream, (const __nv_bfloat16*)q, q_stride,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots,
-        part_o, part_ml, (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, n_splits);
-    if (rc != LQ_OK || n_splits == 1) return rc;
+        part_o, part_ml, counters, (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, n_splits);
+    if (rc != LQ_OK || n_splits == 1 || counters != nullptr) return rc;
     return launch_pdl(attn_merge_kernel, dim3(T * H), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml,
                       (__nv_bfloat16*)out, hd, n_splits);
 }
@@ -283,20 +332,34 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
 
 // q: rows of q_stride elements whose first H*hd hold the query heads; out [T, H*hd].
 // part_o needs T*H*n_splits*hd floats and part_ml T*H*n_splits*2 floats when n_splits > 1.
-// head_dim must be a multiple of 8 and at most 128; page_size a multiple of 16.
-LQ_EXPORT int lq_attn_decode(const void* q, int q_stride, const void* k_pages, const void* v_pages,
-                             const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
-                             const int* slots, float* part_o, float* part_ml, void* out, int T, int H, int Hkv,
-                             int hd, int page_size, float scale, int window, int n_splits, cudaStream_t stream) {
+// counters (optional): T * Hkv * ceil(H/Hkv/16) ints that are zero between calls; with them the
+// block that finishes a (token, kv head) last merges the slices itself, without them a second
+// kernel does.  head_dim must be a multiple of 8 and at most 128; page_size a multiple of 16;
+// at most 32 slices.
+LQ_EXPORT int lq_attn_decode_merged(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+                                    const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
+                                    const int* slots, float* part_o, float* part_ml, int* counters, void* out, int T,
+                                    int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
+                                    cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
     if (hd % 8 || hd > 128 || hd <= 0 || H % Hkv || page_size % TILE || n_splits < 1 || q_stride % 8) return LQ_BAD_SIZE;
+    if (n_splits > MAX_SPLITS) return LQ_BAD_SIZE;
     if (n_splits > 1 && (!part_o || !part_ml)) return LQ_BAD_SIZE;
 #define LQ_GO(HD) return launch<HD>(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, \
-                                    part_o, part_ml, out, T, H, Hkv, hd, page_size, scale, window, n_splits, stream)
+                                    part_o, part_ml, counters, out, T, H, Hkv, hd, page_size, scale, window, n_splits, stream)
     if (hd <= 32) LQ_GO(32);
     if (hd <= 64) LQ_GO(64);
     LQ_GO(128);
 #undef LQ_GO
+}
+
+// The same without counters: the slices are merged by a second kernel.
+LQ_EXPORT int lq_attn_decode(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+                             const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
+                             const int* slots, float* part_o, float* part_ml, void* out, int T, int H, int Hkv,
+                             int hd, int page_size, float scale, int window, int n_splits, cudaStream_t stream) {
+    return lq_attn_decode_merged(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, part_o,
+                                 part_ml, nullptr, out, T, H, Hkv, hd, page_size, scale, window, n_splits, stream);
 }
 
 // ------------------------------------------------------------------ the entry point that allocates nothing
@@ -339,15 +402,21 @@ LQ_EXPORT int lq_attn_decode_static(const void* q, int q_stride, const void* k_p
     if (H <= 0 || Hkv <= 0 || head_dim <= 0 || n_splits < 1) return LQ_BAD_SIZE;
     float* part_o = nullptr;
     float* part_ml = nullptr;
+    int* counters = nullptr;
     if (n_splits > 1) {
         const long long rows = (long long)T * H * n_splits;
-        if (rows * (head_dim + 2) > (long long)LQ_ATTN_STATIC_FLOATS) return LQ_STATIC_TOO_SMALL;
+        const long long n_counters = (long long)T * Hkv * ((H / Hkv + 15) / 16);
+        if (rows * (head_dim + 2) + n_counters > (long long)LQ_ATTN_STATIC_FLOATS) return LQ_STATIC_TOO_SMALL;
         int error = LQ_OK;
         float* base = static_scratch_of_current_device(&error);
         if (!base) return error;
-        part_o = base;                               // [T, H, n_splits, head_dim]
-        part_ml = base + rows * head_dim;            // [T, H, n_splits, 2]
+        part_o = base;                                        // [T, H, n_splits, head_dim]
+        part_ml = base + rows * head_dim;                     // [T, H, n_splits, 2]
+        counters = (int*)(base + rows * (head_dim + 2));      // one per (token, kv head, row tile)
+        // The counters must start at zero; whatever an earlier call left there is cleared (no allocation).
+        cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)n_counters * sizeof(int), stream);
+        if (e != cudaSuccess) return (int)e;
     }
-    return lq_attn_decode(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, part_o,
-                          part_ml, out, T, H, Hkv, head_dim, page_size, scale, window, n_splits, stream);
+    return lq_attn_decode_merged(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, part_o,
+                                 part_ml, counters, out, T, H, Hkv, head_dim, page_size, scale, window, n_splits, stream);
 }

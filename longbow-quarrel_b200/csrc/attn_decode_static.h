@@ -15,8 +15,9 @@
  *
  * The limit.  The array holds LQ_ATTN_STATIC_FLOATS floats (8 MiB).  Every GPU that loads the
  * library holds those 8 MiB from load until the process ends.  A call needs
- * T * H * n_splits * (head_dim + 2) floats and is refused with LQ_STATIC_TOO_SMALL (-4), before
- * anything is launched, when that is more; lq_attn_decode_static_floats() gives the capacity.
+ * T * H * n_splits * (head_dim + 2) floats plus one counter for each (token, kv head) and is
+ * refused with LQ_STATIC_TOO_SMALL (-4), before anything is launched, when that is more;
+ * lq_attn_decode_static_floats() gives the capacity.
  * With one slice (n_splits == 1) no scratch is used at all.
  *
  * Set-up.  The first call on a device asks the runtime for the array's device address
@@ -25,8 +26,10 @@
  * device before any stream capture begins, like any other call that may initialise a module.
  *
  * Sharing.  All calls on a device use the same array, and it keeps what the last call left in
- * it.  Nothing has to be cleared: a call writes every element that it later reads (a slice
- * without keys writes "maximum -inf, sum 0").  Two calls that overlap on the GPU -- different
+ * it.  The partial outputs need no clearing: a call writes every element that it later reads
+ * (a slice without keys writes "maximum -inf, sum 0").  The counters by which the last block of
+ * a (token, kv head) knows that it is the last must start at zero: each call clears the ones
+ * it uses with cudaMemsetAsync on its stream before the kernel.  Two calls that overlap on the GPU -- different
  * streams, or different host threads launching on different streams -- race on the array; keep
  * calls on one stream, or order them with events.
  *

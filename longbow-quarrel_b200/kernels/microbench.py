@@ -7,9 +7,10 @@
     python -m longbow_quarrel_b200.kernels.microbench step --batch 8 --context 4096 --layers 4
     python -m longbow_quarrel_b200.kernels.microbench prefill --tokens 2048 --layers 4
 
-Each kernel is timed with CUDA events over `--iters` launches after `--warmup`; operands
-are rotated through enough copies to exceed the 126 MB L2, so every launch reads from
-HBM.  One JSON line is printed: time, bytes or flops moved, achieved GB/s and TFLOP/s.
+Each kernel is timed with CUDA events over `--iters` launches after `--warmup`, captured
+into one CUDA graph so that no host time lies between the launches (`--no-graph` launches
+them from the host one by one); operands are rotated through enough copies to exceed the
+126 MB L2, so every launch reads from HBM.  One JSON line is printed: time, bytes or flops moved, achieved GB/s and TFLOP/s.
 `step` builds a model of Llama-3.1-8B layer sizes with `--layers` layers, fills the cache
 of `--batch` sequences to `--context` tokens with random keys and values (no prefill),
 and runs decode steps; with `--eager` the step's kernels are launched one by one instead
@@ -27,11 +28,29 @@ L2_BYTES = 126 * 1024 * 1024
 EPIS = {"bf16": 0, "f32": 1, "resid": 2, "swiglu": 3}
 
 
-def _time(fn, iters: int, warmup: int) -> float:
+GRAPH = True      # time kernels as one captured graph of `iters` launches: no host time between them
+
+
+def _time(fn, iters: int, warmup: int, graph: bool | None = None) -> float:
     for i in range(warmup):
         fn(i)
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
+    if GRAPH if graph is None else graph:
+        g = torch.cuda.CUDAGraph()
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream), torch.cuda.graph(g, stream=stream):
+            for i in range(iters):
+                fn(warmup + i)
+        torch.cuda.current_stream().wait_stream(stream)
+        g.replay()
+        torch.cuda.synchronize()
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / iters
     a.record()
     for i in range(iters):
         fn(warmup + i)
@@ -140,7 +159,7 @@ def bench_step(args) -> dict:
 
     def run(i):
         eng.step([(s, [int(t)]) for s, t in zip(slots, feed[i])])
-    ms = _time(run, args.iters, args.warmup)
+    ms = _time(run, args.iters, args.warmup, graph=False)
     return {"kernel": "decode step", "batch": B, "context": C, "layers": args.layers, "graph": not args.eager,
             "ms": ms, "tokens_per_s": B / ms * 1e3}
 
@@ -162,7 +181,7 @@ def bench_prefill(args) -> dict:
         slot = eng.new_sequence()
         eng.step([(slot, rng.integers(0, cfg["vocab_size"], T).tolist())])
         eng.end_sequence(slot)
-    ms = _time(run, args.iters, args.warmup)
+    ms = _time(run, args.iters, args.warmup, graph=False)
     return {"kernel": "prefill step", "tokens": T, "layers": args.layers, "ms": ms, "tokens_per_s": T / ms * 1e3}
 
 
@@ -182,9 +201,12 @@ def main(argv=None) -> int:
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--eager", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="time single kernels launch by launch from the host")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args(argv)
+    global GRAPH
+    GRAPH = not args.no_graph
     if args.what in ("gemm_skinny", "gemm_stream", "gemm_tc"):
         out = bench_gemm(args.what, args)
     elif args.what == "attn_decode":

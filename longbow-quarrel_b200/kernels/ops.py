@@ -346,10 +346,29 @@ def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq,
         part_o, part_ml = scratch
         if part_o.numel() < T * H * n_splits * hd or part_ml.numel() < T * H * n_splits * 2:
             raise KernelError("attn_decode: scratch too small")
-    fn = _fn("attn_decode", "lq_attn_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                               c_float, c_int, c_int, c_void_p])
+    counters = None
+    if n_splits > 1:
+        n_counters = T * Hkv * -(-(H // Hkv) // 16)
+        counters = _attn_counters(q.device)
+        if n_counters > counters.numel():
+            counters = None          # more (token, kv head) pairs than counters: merge with the second kernel
+    fn = _fn("attn_decode", "lq_attn_decode_merged", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                      c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
     _check(fn(_p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0), _p(tok_pos),
-              _p(tok_seq), _p(slots), _p(part_o), _p(part_ml), _p(out), T, H, Hkv, hd, page_size, float(scale),
-              int(window or 0), n_splits, _stream()), "attn_decode", 2 if n_splits > 1 else 1)
+              _p(tok_seq), _p(slots), _p(part_o), _p(part_ml), _p(counters), _p(out), T, H, Hkv, hd, page_size,
+              float(scale), int(window or 0), n_splits, _stream()), "attn_decode",
+           2 if n_splits > 1 and counters is None else 1)
     return out
+
+
+_counters: dict = {}
+
+
+def _attn_counters(device) -> torch.Tensor:
+    """The counters by which the last block of a (token, kv head) finds out that it is the last:
+    zero between calls (the kernel resets what it used), one buffer per device."""
+    key = (device.type, device.index)
+    if key not in _counters:
+        _counters[key] = torch.zeros(1 << 16, dtype=torch.int32, device=device)
+    return _counters[key]
