@@ -25,6 +25,7 @@
 #define EPI_F32 1
 #define EPI_RESID 2
 #define EPI_SWIGLU 3
+#define EPI_QKV 4       // q, k, v rows: rotate q and k, store k and v into the cache pages
 
 namespace {
 
@@ -49,6 +50,20 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// What the q/k/v epilogue needs beside the product: where each token stands and where its cache
+// page is.  W holds H query heads, then Hkv key heads, then Hkv value heads, hd rows each.
+struct QkvArgs {
+    const float* cos_t;       // [positions, hd / 2] or null (no rotation)
+    const float* sin_t;
+    const int* tok_pos;
+    const int* tok_seq;
+    const int* slots;
+    const int* page_table;
+    __nv_bfloat16* k_pages;
+    __nv_bfloat16* v_pages;
+    int pt_stride, H, Hkv, hd, page_size;
+};
+
 // Work of one warp on `UNROLL` chunks: the W rows of the block as mma A fragments, and (for
 // few tokens) the tokens' x as B fragments, all loaded before any of it is used.
 template <int MT>
@@ -60,12 +75,20 @@ struct Frags {
 template <int MT, int EPI>
 __global__ void __launch_bounds__(WARPS * 32, 2)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, void* Cout,
-                   const float* residual, int M, int N, int K) {
+                   const float* residual, int M, int N, int K, const QkvArgs qkv) {
     __shared__ float red[WARPS][ROWS][MT * 8 + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * ROWS;
-    const int r0 = n0 + g, r1 = n0 + g + 8;
+    // The block's 16 rows of W.  Normally consecutive; for q/k/v the first 8 are elements
+    // j0..j0+7 of a head and the last 8 their rotation partners j0 + hd/2 .. (same head).
+    int n0 = blockIdx.x * ROWS, n1 = n0 + 8;
+    if (EPI == EPI_QKV) {
+        const int per_head = qkv.hd / 16;             // blocks per head
+        const int head = blockIdx.x / per_head, j0 = (blockIdx.x % per_head) * 8;
+        n0 = head * qkv.hd + j0;
+        n1 = n0 + qkv.hd / 2;
+    }
+    const int r0 = n0 + g, r1 = n1 + g;
     const bool r0ok = r0 < N, r1ok = r1 < N;
     const __nv_bfloat16* w0 = W + (size_t)(r0ok ? r0 : 0) * K;
     const __nv_bfloat16* w1 = W + (size_t)(r1ok ? r1 : 0) * K;
@@ -160,7 +183,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
     }
     __syncthreads();
     // One thread per (token, row): consecutive threads write consecutive outputs of a token.
-    constexpr int OUT_ROWS = (EPI == EPI_SWIGLU) ? ROWS / 2 : ROWS;
+    constexpr int OUT_ROWS = (EPI == EPI_SWIGLU || EPI == EPI_QKV) ? ROWS / 2 : ROWS;
     auto total = [&](int r, int m) {
         float v = 0.f;
 #pragma unroll
@@ -171,7 +194,31 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
         int m = i / OUT_ROWS, r = i % OUT_ROWS;
         if (m >= M) continue;
         float s = total(r, m);
-        if (EPI == EPI_SWIGLU) {
+        if (EPI == EPI_QKV) {
+            // s and u are elements j and j + hd/2 of one head of token m.
+            float u = total(r + 8, m);
+            const int hd = qkv.hd, half = hd >> 1;
+            const int head = n0 / hd, j = n0 % hd + r;
+            const int pos = qkv.tok_pos[m];
+            if (head < qkv.H + qkv.Hkv && qkv.cos_t) {
+                float c = qkv.cos_t[(size_t)pos * half + j], sn = qkv.sin_t[(size_t)pos * half + j];
+                float y0 = s * c - u * sn, y1 = s * sn + u * c;
+                s = y0;
+                u = y1;
+            }
+            if (head < qkv.H) {
+                __nv_bfloat16* o = (__nv_bfloat16*)Cout + (size_t)m * qkv.H * hd + (size_t)head * hd + j;
+                o[0] = __float2bfloat16_rn(s);
+                o[half] = __float2bfloat16_rn(u);
+            } else {
+                const int kvh = (head - qkv.H) % qkv.Hkv;
+                __nv_bfloat16* pages = head < qkv.H + qkv.Hkv ? qkv.k_pages : qkv.v_pages;
+                const int page = qkv.page_table[(size_t)qkv.slots[qkv.tok_seq[m]] * qkv.pt_stride + pos / qkv.page_size];
+                __nv_bfloat16* o = pages + (((size_t)page * qkv.Hkv + kvh) * qkv.page_size + pos % qkv.page_size) * hd + j;
+                o[0] = __float2bfloat16_rn(s);
+                o[half] = __float2bfloat16_rn(u);
+            }
+        } else if (EPI == EPI_SWIGLU) {
             float u = total(r + 8, m);
             int f = (n0 >> 1) + r;
             if (f < (N >> 1))
@@ -189,15 +236,16 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
 
 template <int MT>
 int launch_mt(const void* X, const void* W, void* C, const float* residual, int M, int N, int K, int epi,
-              cudaStream_t stream) {
+              cudaStream_t stream, const QkvArgs qkv = QkvArgs{}) {
     dim3 grid((N + ROWS - 1) / ROWS), block(WARPS * 32);
     const __nv_bfloat16* x = (const __nv_bfloat16*)X;
     const __nv_bfloat16* w = (const __nv_bfloat16*)W;
     switch (epi) {
-        case EPI_BF16: return launch_pdl(gemm_skinny_kernel<MT, EPI_BF16>, grid, block, 0, stream, x, w, C, residual, M, N, K);
-        case EPI_F32: return launch_pdl(gemm_skinny_kernel<MT, EPI_F32>, grid, block, 0, stream, x, w, C, residual, M, N, K);
-        case EPI_RESID: return launch_pdl(gemm_skinny_kernel<MT, EPI_RESID>, grid, block, 0, stream, x, w, C, residual, M, N, K);
-        case EPI_SWIGLU: return launch_pdl(gemm_skinny_kernel<MT, EPI_SWIGLU>, grid, block, 0, stream, x, w, C, residual, M, N, K);
+        case EPI_BF16: return launch_pdl(gemm_skinny_kernel<MT, EPI_BF16>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv);
+        case EPI_F32: return launch_pdl(gemm_skinny_kernel<MT, EPI_F32>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv);
+        case EPI_RESID: return launch_pdl(gemm_skinny_kernel<MT, EPI_RESID>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv);
+        case EPI_SWIGLU: return launch_pdl(gemm_skinny_kernel<MT, EPI_SWIGLU>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv);
+        case EPI_QKV: return launch_pdl(gemm_skinny_kernel<MT, EPI_QKV>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv);
         default: return LQ_BAD_DTYPE;
     }
     return lq_launch_status();
@@ -220,4 +268,21 @@ LQ_EXPORT int lq_gemm_skinny(const void* X, const void* W, void* C, const float*
         case 3: case 4: return launch_mt<4>(X, W, C, residual, M, N, K, epi, stream);
         default: return launch_mt<8>(X, W, C, residual, M, N, K, epi, stream);
     }
+}
+
+// The q/k/v projection of decoding with its epilogue fused: X [M <= 16, K] . W^T for
+// W [(H + 2 Hkv) hd, K]; q and k are rotated by the cos/sin tables at each token's position
+// (tables null: no rotation); q goes to q_out [M, H hd], k and v go into the token's cache page.
+// hd % 16 == 0.  Replaces the product, the rotation kernel and the cache write of a decode step.
+LQ_EXPORT int lq_gemm_skinny_qkv(const void* X, const void* W, void* q_out, int M, int K, const float* cos_t,
+                                 const float* sin_t, const int* tok_pos, const int* tok_seq, const int* slots,
+                                 const int* page_table, int pt_stride, void* k_pages, void* v_pages, int H, int Hkv,
+                                 int hd, int page_size, cudaStream_t stream) {
+    if (M <= 0) return LQ_OK;
+    if (M > 16 || K % 8 != 0 || K <= 0 || hd % 16 != 0 || H <= 0 || Hkv <= 0) return LQ_BAD_SIZE;
+    QkvArgs a{cos_t, sin_t, tok_pos, tok_seq, slots, page_table, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages,
+              pt_stride, H, Hkv, hd, page_size};
+    const int N = (H + 2 * Hkv) * hd;
+    if (M <= 8) return launch_mt<1>(X, W, q_out, nullptr, M, N, K, EPI_QKV, stream, a);
+    return launch_mt<2>(X, W, q_out, nullptr, M, N, K, EPI_QKV, stream, a);
 }

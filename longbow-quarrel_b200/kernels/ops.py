@@ -227,6 +227,28 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, epi: int, residual: torch.Tens
     return out
 
 
+def gemm_skinny_qkv(a: torch.Tensor, w: torch.Tensor, cos, sin, tok_pos, tok_seq, slots, page_table, k_pages, v_pages,
+                    H: int, Hkv: int, hd: int, page_size: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """The q/k/v projection of at most 16 tokens with rotation and cache write in its epilogue:
+    returns the rotated q [M, H*hd]; the rotated k and v are stored in each token's cache page."""
+    M, K = a.shape
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
+        raise KernelError("gemm_skinny_qkv takes bfloat16 inputs and cache")
+    if tuple(w.shape) != ((H + 2 * Hkv) * hd, K):
+        raise KernelError(f"gemm_skinny_qkv: weight shape {tuple(w.shape)} is not [(H + 2 Hkv) hd, K]")
+    if M > SKINNY_BEST_ROWS or K % 8 or hd % 16:
+        raise KernelError(f"gemm_skinny_qkv: {M} rows (at most 16), width {K} (multiple of 8), head_dim {hd} (multiple of 16)")
+    if out is None:
+        out = torch.empty((M, H * hd), dtype=torch.bfloat16, device=a.device)
+    fn = _fn("gemm_skinny", "lq_gemm_skinny_qkv", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                                   c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                                   c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), M, K, _p(cos), _p(sin), _p(tok_pos), _p(tok_seq),
+              _p(slots), _p(page_table), page_table.stride(0), _p(k_pages), _p(v_pages), H, Hkv, hd, page_size,
+              _stream()), "gemm_skinny_qkv")
+    return out
+
+
 def gemm_stream(a: torch.Tensor, w: torch.Tensor, epi: int, residual: torch.Tensor | None = None,
                 out: torch.Tensor | None = None) -> torch.Tensor:
     """a [M <= 64, K] . w [N, K]^T, both bfloat16: W streamed once through all SMs by TMA in equal

@@ -63,8 +63,19 @@ class Attention(Mixer):
 
     def forward(self, h, ctx: StepContext, cache_view, residual, writes_cache: bool = True):
         store = self.own_kv and writes_cache
-        qkv = linear.linear(h, self.w_qkv, self.runtime.act_dtype)
         tables = self.position.tables() if self.position is not None else None
+        if (store and h.dtype == torch.bfloat16 and self.w_qkv.tensor.dtype == torch.bfloat16
+                and h.shape[0] <= ops.SKINNY_BEST_ROWS and self.D % 8 == 0 and cache_view.k_pages.dtype == torch.bfloat16
+                and (self.position is None or tables is not None)):
+            # Few tokens: projection, rotation and cache write are one kernel.
+            cos, sin = tables if tables is not None else (None, None)
+            q = ops.gemm_skinny_qkv(h, self.w_qkv.tensor, cos, sin, ctx.tok_pos, ctx.tok_seq, ctx.slots,
+                                    cache_view.page_table, cache_view.k_pages, cache_view.v_pages, self.H, self.Hkv,
+                                    self.hd, cache_view.page_size)
+            out = attention_kernels.attention(q, cache_view, ctx, self.H, self.Hkv, self.hd, self.scale, self.window)
+            linear.linear(out, self.w_o, self.runtime.act_dtype, residual=residual)
+            return
+        qkv = linear.linear(h, self.w_qkv, self.runtime.act_dtype)
         if self.position is not None and tables is None:
             q = qkv[:, :self.H * self.hd].unflatten(1, (self.H, self.hd))
             k = qkv[:, self.H * self.hd:(self.H + self.Hkv) * self.hd].unflatten(1, (self.Hkv, self.hd)) \

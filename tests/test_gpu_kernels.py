@@ -439,3 +439,37 @@ def test_attn_prefill_window_edge_and_far_key():
     _close(win.reshape(n, 1, hd), ref, _attn_tol(case, ref), BF16_ULP)
     assert float((win[300].float() - case.v[0][250, 0].float()).abs().max()) > 0.5     # the key outside is not seen
     assert float((win[399].float() - case.v[0][0, 0].float()).abs().max()) > 0.5
+
+
+@pytest.mark.parametrize("M", [1, 8, 13])
+@pytest.mark.parametrize("H,Hkv,hd,rotate", [(4, 2, 32, True), (6, 1, 128, True), (2, 2, 48, False)])
+def test_gemm_skinny_qkv_rotates_and_stores(M, H, Hkv, hd, rotate):
+    """The fused decode projection against product, rotation and cache write done apart."""
+    ops = _ops()
+    K = 200
+    lens = [70 + 5 * i for i in range(M)]
+    case = PagedCase(lens, Hkv, hd, torch.bfloat16, seed=11)
+    k_before, v_before = case.k_pages.clone(), case.v_pages.clone()
+    a = _rand((M, K), torch.bfloat16, 40)
+    w = _rand(((H + 2 * Hkv) * hd, K), torch.bfloat16, 41, 0.1)
+    tok_pos, tok_seq = [n - 1 for n in lens], list(range(M))
+    freqs = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)
+    ang = torch.arange(256, dtype=torch.float64)[:, None] * freqs[None]
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    q = ops.gemm_skinny_qkv(a, w, cos if rotate else None, sin if rotate else None, _ints(tok_pos), _ints(tok_seq),
+                            case.slots, case.table, case.k_pages, case.v_pages, H, Hkv, hd, 64)
+    full = (a.float().double() @ w.float().double().T).reshape(M, H + 2 * Hkv, hd)
+    c = cos[torch.tensor(tok_pos)].double().cpu().unsqueeze(1) if rotate else 1.0
+    s = sin[torch.tensor(tok_pos)].double().cpu().unsqueeze(1) if rotate else 0.0
+    x0, x1 = full.cpu()[:, :H + Hkv, :hd // 2], full.cpu()[:, :H + Hkv, hd // 2:]
+    rot = torch.cat([x0 * c - x1 * s, x0 * s + x1 * c], dim=-1)
+    _close(q.reshape(M, H, hd), rot[:, :H], _acc_tol(K), BF16_ULP)
+    touched = torch.zeros_like(case.k_pages, dtype=torch.bool)
+    for m in range(M):
+        page = int(case.table[case.slot_of[m], tok_pos[m] // 64])
+        _close(case.k_pages[page, :, tok_pos[m] % 64], rot[m, H:], _acc_tol(K), BF16_ULP)
+        _close(case.v_pages[page, :, tok_pos[m] % 64], full.cpu()[m, H + Hkv:], _acc_tol(K), BF16_ULP)
+        touched[page, :, tok_pos[m] % 64] = True
+    for pages, before in ((case.k_pages, k_before), (case.v_pages, v_before)):
+        same = (pages == before) | (pages.isnan() & before.isnan())
+        assert bool((same | touched).all())          # nothing else in the cache was written
