@@ -4,10 +4,11 @@
 // The step is bound by reading K and V once from HBM.  A block serves one token, one
 // kv head and one slice of that sequence's keys; the query heads that share the kv
 // head are the rows of the m16n8k16 tile (grouped-query attention reads each key once
-// for the whole group).  Warps take 16-key tiles in turn.  K and V go straight from
-// global memory into mma fragments with 16-byte loads -- nothing is reused, so nothing
-// is staged in shared memory: for Q.K^T the head dimension is permuted alike in Q and
-// K, for P.V the output columns are permuted and put back in place when O is written.
+// for the whole group).  The 8 warps take 16-key tiles in turn; each warp keeps a ring of
+// three tiles in shared memory, filled by cp.async two tiles ahead of the one it works on,
+// so that a block has about 128 KB of keys and values on their way at any time (with the
+// loads held in registers instead, one tile ahead was all that fitted, and the stream
+// stalled on memory latency at 3.7 TB/s).  Fragments come from the ring by ldmatrix.
 // Softmax runs online in 32-bit; the warps of a block and then the slices of a
 // sequence are merged by their running maximum and sum, in a fixed order.
 //
@@ -21,15 +22,25 @@
 
 namespace {
 
-constexpr int DW = 4;            // warps per block
+constexpr int DW = 8;            // warps per block
 constexpr int TILE = 16;         // keys per warp tile
+constexpr int RING = 3;          // tiles of a warp in shared memory: one in use, two on their way
+constexpr int PAD = 8;           // elements of padding per shared-memory row (ldmatrix without bank conflicts)
 constexpr int MAX_SPLITS = 32;   // most slices a sequence's keys are cut into
 
-__device__ __forceinline__ uint4 ldg16(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    int bytes = valid ? 16 : 0;     // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -42,23 +53,25 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
-__device__ __forceinline__ uint32_t reg_of(const uint4& v, int i) {
-    return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
-}
 
 // HD: head_dim rounded up to 32, 64 or 128; the real head_dim hd is a multiple of 8.
 template <int HD>
-__global__ void __launch_bounds__(DW * 32, 2)
+__global__ void __launch_bounds__(DW * 32, 1)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_pages,
                    const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ page_table, int pt_stride,
                    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                    __nv_bfloat16* __restrict__ out, int H, int Hkv, int hd, int page_size, float scale, int window,
                    int n_splits) {
-    constexpr int QB = HD / 32;                    // 32-wide blocks of the head dimension (Q.K^T)
-    constexpr int VC = (HD + 63) / 64;             // 64-wide column groups (P.V)
-    __shared__ float sm_o[DW][16][HD + 1];
-    __shared__ float sm_m[DW][16], sm_l[DW][16];
+    constexpr int LD = HD + PAD;                   // shared-memory row length in elements
+    constexpr int KD = HD / 16;                    // k16 steps over the head dimension
+    constexpr int STAGE = 2 * TILE * LD;           // elements of one tile: K rows, then V rows
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [DW][RING][STAGE]
+    // After the loop the same memory holds each warp's state for the merge.
+    float (*sm_o)[16][HD + 1] = reinterpret_cast<float (*)[16][HD + 1]>(smem_raw);
+    float (*sm_m)[16] = reinterpret_cast<float (*)[16]>(smem_raw + sizeof(float) * DW * 16 * (HD + 1));
+    float (*sm_l)[16] = sm_m + DW;
     __shared__ float sm_w[16][MAX_SPLITS];       // weights of the slices when this block merges them
     __shared__ float sm_inv[16];
     __shared__ int sm_last;
@@ -67,29 +80,32 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
     const int split = blockIdx.x, tok = blockIdx.z;
     const int G = H / Hkv, gtiles = (G + 15) / 16;
     const int kvh = blockIdx.y / gtiles, gt = blockIdx.y % gtiles;
-    pdl_launch_dependents();
+    // No pdl_launch_dependents() here: released early, the blocks of the product that follows moved
+    // onto the SMs this kernel leaves free and fetched weights against it (measured: the step ran
+    // 50 % slower).  The kernel after this one starts when this one ends.
     pdl_wait();
     const int pos = tok_pos[tok], len = pos + 1;
     const int start = (window > 0 && pos >= window) ? pos - window + 1 : 0;
     const int* pt = page_table + (size_t)slots[tok_seq[tok]] * pt_stride;
 
-    // Query rows of this thread: heads hq0 (row g) and hq1 (row g + 8) of the group.
+    // Query heads of the group as the rows of the mma tile (rows g and g + 8 of this thread).
     const int r0 = gt * 16 + g, r1 = r0 + 8;
     const bool r0ok = r0 < G, r1ok = r1 < G;
     const __nv_bfloat16* q0p = q + (size_t)tok * q_stride + (size_t)(kvh * G + (r0ok ? r0 : 0)) * hd;
     const __nv_bfloat16* q1p = q + (size_t)tok * q_stride + (size_t)(kvh * G + (r1ok ? r1 : 0)) * hd;
-    const uint4 zero = make_uint4(0, 0, 0, 0);
-    uint4 qa[QB], qb[QB];
+    uint32_t qf[KD][4];
 #pragma unroll
-    for (int b = 0; b < QB; ++b) {
-        int d = b * 32 + t * 8;
-        qa[b] = (r0ok && d < hd) ? ldg16(q0p + d) : zero;
-        qb[b] = (r1ok && d < hd) ? ldg16(q1p + d) : zero;
+    for (int kk = 0; kk < KD; ++kk) {
+        const int d0 = kk * 16 + 2 * t, d1 = d0 + 8;
+        qf[kk][0] = (r0ok && d0 < hd) ? *reinterpret_cast<const uint32_t*>(q0p + d0) : 0u;
+        qf[kk][1] = (r1ok && d0 < hd) ? *reinterpret_cast<const uint32_t*>(q1p + d0) : 0u;
+        qf[kk][2] = (r0ok && d1 < hd) ? *reinterpret_cast<const uint32_t*>(q0p + d1) : 0u;
+        qf[kk][3] = (r1ok && d1 < hd) ? *reinterpret_cast<const uint32_t*>(q1p + d1) : 0u;
     }
 
-    float o[VC * 8][4];
+    float o[HD / 8][4];
 #pragma unroll
-    for (int j = 0; j < VC * 8; ++j)
+    for (int j = 0; j < HD / 8; ++j)
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
     float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
@@ -100,48 +116,51 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
     const int tile_lo = first_tile + split * per_split;
     const int tile_hi = min(first_tile + n_tiles, tile_lo + per_split);
     const size_t head_off = (size_t)kvh * page_size * hd;
+    __nv_bfloat16* my_ring = ring + (size_t)warp * RING * STAGE;
 
-    // A tile's K and V as this thread's mma fragments.  K: rows kb + g and kb + 8 + g;
-    // V: rows kb + {2t, 2t+1, 2t+8, 2t+9}.
-    struct Tile { uint4 kr[2][QB]; uint4 vr[4][VC]; };
-    auto load_tile = [&](int tile, Tile& T) {
-        const int kb = tile * TILE;
-        const int page = pt[kb / page_size];
-        const size_t page_off = (size_t)page * Hkv * page_size * hd + head_off + (size_t)(kb % page_size) * hd;
-        const __nv_bfloat16* kp = k_pages + page_off;
-        const __nv_bfloat16* vp = v_pages + page_off;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            int key = kb + nt * 8 + g;
-#pragma unroll
-            for (int b = 0; b < QB; ++b) {
-                int d = b * 32 + t * 8;
-                T.kr[nt][b] = (key < len && d < hd) ? ldg16(kp + (size_t)(nt * 8 + g) * hd + d) : zero;
+    // This warp's tiles are tile_lo + warp, + DW, ...; `n` counts them.
+    auto issue = [&](int n) {
+        const int tile = tile_lo + warp + n * DW;
+        if (tile < tile_hi) {
+            const int kb = tile * TILE;
+            const int page = pt[kb / page_size];
+            const size_t off = (size_t)page * Hkv * page_size * hd + head_off + (size_t)(kb % page_size) * hd;
+            __nv_bfloat16* ks = my_ring + (size_t)(n % RING) * STAGE;
+            __nv_bfloat16* vs = ks + TILE * LD;
+            for (int i = lane; i < TILE * (HD / 8); i += 32) {
+                const int r = i / (HD / 8), c = (i % (HD / 8)) * 8;
+                const bool ok = kb + r < len && c < hd;
+                const size_t src = off + (size_t)(ok ? r : 0) * hd + (ok ? c : 0);
+                cp_async16((uint32_t)__cvta_generic_to_shared(ks + r * LD + c), k_pages + src, ok);
+                cp_async16((uint32_t)__cvta_generic_to_shared(vs + r * LD + c), v_pages + src, ok);
             }
         }
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            int row = 2 * t + (r & 1) + (r >> 1) * 8;
-#pragma unroll
-            for (int c = 0; c < VC; ++c) {
-                int d = c * 64 + g * 8;
-                T.vr[r][c] = (kb + row < len && d < hd) ? ldg16(vp + (size_t)row * hd + d) : zero;
-            }
-        }
+        cp_async_commit();          // an empty group when there is no tile: the count of groups stays in step
     };
-    auto compute_tile = [&](int tile, const Tile& T) {
-        const int kb = tile * TILE;
-        // S = Q K^T for two 8-key tiles.
+#pragma unroll
+    for (int n = 0; n < RING - 1; ++n) issue(n);
+    const int my_tiles = tile_lo + warp < tile_hi ? (tile_hi - tile_lo - warp + DW - 1) / DW : 0;
+    for (int n = 0; n < my_tiles; ++n) {
+        issue(n + RING - 1);
+        cp_async_wait<RING - 1>();
+        __syncwarp();
+        const int kb = (tile_lo + warp + n * DW) * TILE;
+        const __nv_bfloat16* ks = my_ring + (size_t)(n % RING) * STAGE;
+        const __nv_bfloat16* vs = ks + TILE * LD;
+        // S = Q K^T for the tile's two groups of 8 keys.
         float s[2][4];
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
+        for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
 #pragma unroll
-            for (int b = 0; b < QB; ++b) {
-                mma_bf16(s[nt], qa[b].x, qb[b].x, qa[b].y, qb[b].y, T.kr[nt][b].x, T.kr[nt][b].y);
-                mma_bf16(s[nt], qa[b].z, qb[b].z, qa[b].w, qb[b].w, T.kr[nt][b].z, T.kr[nt][b].w);
-            }
+        for (int kk = 0; kk < KD; ++kk) {
+            // matrices (keys 0-7, d 0-7), (keys 0-7, d 8-15), (keys 8-15, d 0-7), (keys 8-15, d 8-15)
+            const int r = (lane & 7) + (lane >> 4) * 8, c = kk * 16 + ((lane >> 3) & 1) * 8;
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4((uint32_t)__cvta_generic_to_shared(ks + r * LD + c), b0, b1, b2, b3);
+            mma_bf16(s[0], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
+            mma_bf16(s[1], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b2, b3);
         }
         float tm0 = -CUDART_INF_F, tm1 = -CUDART_INF_F;
 #pragma unroll
@@ -181,44 +200,35 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
         l0 = l0 * c0 + ps0;
         l1 = l1 * c1 + ps1;
 #pragma unroll
-        for (int c = 0; c < VC; ++c)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float (&acc)[4] = o[c * 8 + j];
-                acc[0] *= c0; acc[1] *= c0; acc[2] *= c1; acc[3] *= c1;
-                const unsigned sel = (j & 1) ? 0x7632u : 0x5410u;
-                uint32_t b0 = __byte_perm(reg_of(T.vr[0][c], j >> 1), reg_of(T.vr[1][c], j >> 1), sel);
-                uint32_t b1 = __byte_perm(reg_of(T.vr[2][c], j >> 1), reg_of(T.vr[3][c], j >> 1), sel);
-                mma_bf16(acc, pa[0], pa[1], pa[2], pa[3], b0, b1);
-            }
-    };
-    // The loads of the next tile are in flight while the current one is computed.
-    Tile ta, tb;
-    int tile = tile_lo + warp;
-    if (tile < tile_hi) load_tile(tile, ta);
-    while (tile < tile_hi) {
-        if (tile + DW < tile_hi) load_tile(tile + DW, tb);
-        compute_tile(tile, ta);
-        tile += DW;
-        if (tile >= tile_hi) break;
-        if (tile + DW < tile_hi) load_tile(tile + DW, ta);
-        compute_tile(tile, tb);
-        tile += DW;
+        for (int dp = 0; dp < HD / 16; ++dp) {
+            // V transposed on load: matrices (keys 0-7, d 0-7), (keys 8-15, d 0-7), (keys 0-7, d 8-15), (keys 8-15, d 8-15)
+            const int r = (lane & 7) + ((lane >> 3) & 1) * 8, c = dp * 16 + (lane >> 4) * 8;
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4_t((uint32_t)__cvta_generic_to_shared(vs + r * LD + c), b0, b1, b2, b3);
+            float (&oa)[4] = o[2 * dp];
+            float (&ob)[4] = o[2 * dp + 1];
+            oa[0] *= c0; oa[1] *= c0; oa[2] *= c1; oa[3] *= c1;
+            ob[0] *= c0; ob[1] *= c0; ob[2] *= c1; ob[3] *= c1;
+            mma_bf16(oa, pa[0], pa[1], pa[2], pa[3], b0, b1);
+            mma_bf16(ob, pa[0], pa[1], pa[2], pa[3], b2, b3);
+        }
+        __syncwarp();       // every lane is done with the slot before a later copy refills it
     }
+    cp_async_wait<0>();
     // Row sums: add the four threads of a row.
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    // Park each warp's state; column n of an output tile belongs to d = c*64 + n*8 + j.
+    __syncthreads();        // all rings are idle: their memory now holds the warps' states
 #pragma unroll
-    for (int c = 0; c < VC; ++c)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            int d0 = c * 64 + (2 * t) * 8 + j, d1 = d0 + 8;
-            if (d0 < HD) { sm_o[warp][g][d0] = o[c * 8 + j][0]; sm_o[warp][g + 8][d0] = o[c * 8 + j][2]; }
-            if (d1 < HD) { sm_o[warp][g][d1] = o[c * 8 + j][1]; sm_o[warp][g + 8][d1] = o[c * 8 + j][3]; }
-        }
+    for (int j = 0; j < HD / 8; ++j) {
+        const int d = j * 8 + 2 * t;
+        sm_o[warp][g][d] = o[j][0];
+        sm_o[warp][g][d + 1] = o[j][1];
+        sm_o[warp][g + 8][d] = o[j][2];
+        sm_o[warp][g + 8][d + 1] = o[j][3];
+    }
     if (t == 0) {
         sm_m[warp][g] = m0; sm_m[warp][g + 8] = m1;
         sm_l[warp][g] = l0; sm_l[warp][g + 8] = l1;
@@ -320,7 +330,16 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
            cudaStream_t stream) {
     int G = H / Hkv, gtiles = (G + 15) / 16;
     dim3 grid(n_splits, Hkv * gtiles, T);
-    int rc = launch_pdl(attn_decode_kernel<HD>, grid, dim3(DW * 32), 0, stream, (const __nv_bfloat16*)q, q_stride,
+    constexpr size_t ring = (size_t)DW * RING * 2 * TILE * (HD + PAD) * 2;
+    constexpr size_t merge = sizeof(float) * DW * 16 * (HD + 1) + sizeof(float) * 2 * DW * 16;
+    constexpr size_t smem = ring > merge ? ring : merge;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return lq_launch_status();
+        configured = true;
+    }
+    int rc = launch_pdl(attn_decode_kernel<HD>, grid, dim3(DW * 32), smem, stream, (const __nv_bfloat16*)q, q_stride,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots,
         part_o, part_ml, counters, (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, n_splits);
     if (rc != LQ_OK || n_splits == 1 || counters != nullptr) return rc;

@@ -49,8 +49,8 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 template <typename... KArgs, typename... Args>
-static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                             Args... args) {
+static inline int launch_kernel(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -62,7 +62,21 @@ static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = enabled ? 1 : 0;
+    cfg.numAttrs = (enabled && early) ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
     return e == cudaSuccess ? LQ_OK : (int)e;
+}
+
+// A kernel whose blocks may be scheduled before the kernel ahead of it has finished.
+template <typename... KArgs, typename... Args>
+static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+    return launch_kernel(true, kernel, grid, block, smem, stream, args...);
+}
+// A kernel that starts only when the kernel ahead of it has finished: for kernels whose blocks
+// fill an SM (their waiting blocks would keep the blocks of the kernel ahead off that SM).
+template <typename... KArgs, typename... Args>
+static inline int launch_after(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                               Args... args) {
+    return launch_kernel(false, kernel, grid, block, smem, stream, args...);
 }

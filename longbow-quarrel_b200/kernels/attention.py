@@ -5,7 +5,7 @@ import torch
 
 from . import ops
 
-RESIDENT_BLOCKS = 296        # two blocks of the decode kernel fit on each of the 148 SMs
+RESIDENT_BLOCKS = 148        # one block of the decode kernel (8 warps, ~200 KB of key/value rings) per SM
 MAX_SPLITS = 32
 KEYS_PER_SPLIT = 128         # a slice shorter than this is not worth a block of its own
 
