@@ -26,8 +26,10 @@ class PagedKVGroup:
         self.n_kv_heads, self.head_dim, self.window = n_kv_heads, head_dim, window
         self.page_size, self.n_pages, self.max_pages_per_seq = page_size, n_pages, max_pages_per_seq
         shape = (len(self.entries), n_pages, n_kv_heads, page_size, head_dim)
-        self.k_pages = torch.empty(shape, dtype=dtype, device=device)
-        self.v_pages = torch.empty(shape, dtype=dtype, device=device)
+        # Zero-filled: kernels that load whole pages multiply the rows beyond a sequence's length by
+        # probability zero, which needs finite values there.
+        self.k_pages = torch.zeros(shape, dtype=dtype, device=device)
+        self.v_pages = torch.zeros(shape, dtype=dtype, device=device)
         self.table = np.full((max_slots, max_pages_per_seq), NO_PAGE, dtype=np.int32)
         self.table_dev = torch.full((max_slots, max_pages_per_seq), NO_PAGE, dtype=torch.int32, device=device)
         self._free = list(range(n_pages - 1, -1, -1))

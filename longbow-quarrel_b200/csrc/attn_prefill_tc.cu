@@ -1,0 +1,346 @@
+// Causal grouped-query attention of many query tokens over the paged cache on the
+// fifth-generation tensor cores (prefill, head_dim 128, pages of 64 keys).
+//
+// A block takes 128 consecutive query tokens of one sequence and one query head and walks
+// over the keys in tiles of 128 (two cache pages).  Inside a block
+//   warp 0      one lane loads Q once and then K and V tiles by TMA into two stages of shared
+//               memory (128-byte swizzle; a page of one kv head is a [64, 128] box);
+//   warp 1      one lane issues tcgen05.mma: S = Q K^T into tensor memory, and, once the
+//               softmax warps have turned S into probabilities P in shared memory,
+//               O += P V into a second accumulator (V is the MN-major operand: its rows are
+//               keys).  S of the next tile is issued as soon as S of this one has been read,
+//               so the tensor cores work on it while the softmax of this tile runs;
+//   warps 2..9  two threads per query row (64 keys each): read the row of S from tensor
+//               memory, scale and mask it, keep the running maximum and sum in 32-bit, write
+//               bfloat16 probabilities into shared memory in the layout the tensor cores read.  The
+//               reference maximum of a row is only moved (and O rescaled in tensor memory)
+//               when the true maximum has grown by more than 2^8 since; the result is the
+//               same, as O and the sum always share one reference.
+// A row at position p sees keys max(0, p - window + 1) .. p of its own sequence.  Whole pages
+// are loaded, so rows of a page beyond a sequence's length are multiplied by probability zero:
+// the cache must hold finite values everywhere (it is zero-filled when it is made).
+// Every wait on a barrier is bounded (status word, as in gemm_tc).
+//
+// Reference counterpart: att_fused_f16 (internal/device/kernels.metal:657-813) called once per
+// row (internal/device/metal.go:1403-1424).
+#include "tcgen05.cuh"
+#include <math_constants.h>
+
+using namespace tc;
+
+namespace {
+
+constexpr int BM = 128;                 // query rows per block
+constexpr int BN = 128;                 // keys per tile
+constexpr int HD = 128;                 // head dimension
+constexpr int PAGE = 64;
+constexpr int PANEL = 128 * 128;        // bytes of a [128 rows, 64 elements] panel
+constexpr int N_THREADS = 320;         // TMA warp, MMA warp, 8 softmax warps
+constexpr float RESCALE_STEP = 8.0f;    // log2 units the maximum may run ahead of the reference
+
+__device__ int g_status = 0;
+
+struct Smem {
+    alignas(1024) uint8_t q[2][PANEL];          // [d half][128 rows x 128 B]
+    alignas(1024) uint8_t k[2][2][PANEL];       // [stage][d half][128 keys x 128 B]
+    alignas(1024) uint8_t v[2][2][PANEL];       // [stage][d half][128 keys x 128 B]
+    alignas(1024) uint8_t p[2][PANEL];          // [key half][128 rows x 128 B]
+    alignas(8) uint64_t q_full;
+    uint64_t k_full[2], v_full[2], kv_empty[2];
+    uint64_t s_full, s_empty, p_full, pv_done;
+    uint32_t tmem_base;
+    float row_max[2][2][BM];                    // [tile parity][column half][row]: the halves' maxima of a row
+    float row_sum[2][BM];                       // [column half][row]: the halves' sums at the end
+};
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+// 2^x by the special-function unit (relative error about 2^-22; -inf gives 0).
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+#define LQ_WAIT(bar, parity, code) \
+    if (!mbar_wait(smem_u32(&(bar)), (parity))) { atomicExch(&g_status, (code)); ok = false; }
+
+__global__ void __launch_bounds__(N_THREADS, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table, int pt_stride,
+                       const int* __restrict__ slots, const int* __restrict__ kv_len, const int* __restrict__ qb_seq,
+                       const int* __restrict__ qb_row, const int* __restrict__ qb_rows, const int* __restrict__ qb_pos,
+                       __nv_bfloat16* __restrict__ out, int H, int Hkv, int oob_row, float scale_log2, int window) {
+    extern __shared__ uint8_t smem_raw[];
+    Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr uint32_t TMEM_COLS = 256;          // S in columns 0..127, O in 128..255
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&sm.q_full), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&sm.k_full[s]), 1);
+            mbar_init(smem_u32(&sm.v_full[s]), 1);
+            mbar_init(smem_u32(&sm.kv_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&sm.s_full), 1);
+        mbar_init(smem_u32(&sm.s_empty), 256);
+        mbar_init(smem_u32(&sm.p_full), 256);
+        mbar_init(smem_u32(&sm.pv_done), 1);
+        mbar_fence_init();
+        prefetch_map(&map_q);
+        prefetch_map(&map_k);
+        prefetch_map(&map_v);
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&sm.tmem_base), TMEM_COLS);
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem_s = sm.tmem_base, tmem_o = sm.tmem_base + BN;
+    pdl_wait();
+
+    const int blk = blockIdx.x, h = blockIdx.y;
+    const int seq = qb_seq[blk], row0 = qb_row[blk], n_rows = qb_rows[blk], pos0 = qb_pos[blk];
+    const int kvh = h / (H / Hkv);
+    const int len = kv_len[seq];
+    const int* pt = page_table + (size_t)slots[seq] * pt_stride;
+    const int pos_last = pos0 + n_rows - 1;
+    const int key_first = (window > 0 && pos0 >= window) ? pos0 - window + 1 : 0;
+    const int tile_lo = key_first / BN, n_tiles = pos_last / BN - tile_lo + 1;
+    const int last_page = (len - 1) / PAGE;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            bool ok = true;
+            mbar_expect_tx(smem_u32(&sm.q_full), 2 * PANEL);
+            for (int half = 0; half < 2; ++half)
+                tma_load_2d(smem_u32(sm.q[half]), &map_q, h * HD + half * 64, row0, smem_u32(&sm.q_full));
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j & 1;
+                LQ_WAIT(sm.kv_empty[s], ((j >> 1) & 1) ^ 1, 1);
+                if (!ok) break;
+                int rows[2];
+                for (int i = 0; i < 2; ++i) {
+                    const int pg = (tile_lo + j) * 2 + i;
+                    const int page = pg <= last_page ? pt[pg] : -1;
+                    rows[i] = page >= 0 ? (page * Hkv + kvh) * PAGE : oob_row;   // out of range: TMA fills zeros
+                }
+                mbar_expect_tx(smem_u32(&sm.k_full[s]), 2 * PANEL);
+                for (int half = 0; half < 2; ++half)
+                    for (int i = 0; i < 2; ++i)
+                        tma_load_2d(smem_u32(sm.k[s][half]) + i * (PANEL / 2), &map_k, half * 64, rows[i], smem_u32(&sm.k_full[s]));
+                mbar_expect_tx(smem_u32(&sm.v_full[s]), 2 * PANEL);
+                for (int half = 0; half < 2; ++half)
+                    for (int i = 0; i < 2; ++i)
+                        tma_load_2d(smem_u32(sm.v[s][half]) + i * (PANEL / 2), &map_v, half * 64, rows[i], smem_u32(&sm.v_full[s]));
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = idesc_bf16(BM, BN, false);
+            constexpr uint32_t idesc_pv = idesc_bf16(BM, HD, true);
+            bool ok = true;
+            auto issue_s = [&](int s) {
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint64_t a = desc_k_major(smem_u32(sm.q[kk >> 2]) + (kk & 3) * 32);
+                    const uint64_t b = desc_k_major(smem_u32(sm.k[s][kk >> 2]) + (kk & 3) * 32);
+                    mma_f16(tmem_s, a, b, idesc_s, kk > 0 ? 1u : 0u);
+                }
+                commit(smem_u32(&sm.s_full));
+            };
+            LQ_WAIT(sm.q_full, 0, 2);
+            if (ok) LQ_WAIT(sm.k_full[0], 0, 3);
+            if (ok) { fence_after(); issue_s(0); }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j & 1;
+                if (j + 1 < n_tiles) {
+                    LQ_WAIT(sm.k_full[s ^ 1], ((j + 1) >> 1) & 1, 3);
+                    if (ok) LQ_WAIT(sm.s_empty, j & 1, 4);
+                    if (!ok) break;
+                    fence_after();
+                    issue_s(s ^ 1);
+                }
+                LQ_WAIT(sm.p_full, j & 1, 5);
+                if (ok) LQ_WAIT(sm.v_full[s], (j >> 1) & 1, 6);
+                if (!ok) break;
+                fence_after();
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint64_t a = desc_k_major(smem_u32(sm.p[kk >> 2]) + (kk & 3) * 32);
+                    const uint64_t b = desc_mn_major(smem_u32(sm.v[s][0]) + kk * 2048, PANEL);
+                    mma_f16(tmem_o, a, b, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                commit(smem_u32(&sm.kv_empty[s]));
+                commit(smem_u32(&sm.pv_done));
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------------------------------------------------------- softmax: two threads per query row,
+        // each with 64 of the tile's 128 keys (and, at the end, 64 of the 128 output columns)
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const int pos_r = pos0 + r;
+        const bool row_ok = r < n_rows;
+        constexpr int NC = BN / 2;                        // columns of this thread
+        float m_ref = -CUDART_INF_F, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            LQ_WAIT(sm.s_full, j & 1, 7);
+            if (!ok) break;
+            fence_after();
+            float t[NC];
+#pragma unroll
+            for (int c = 0; c < NC / 32; ++c)
+                ld32(tmem_s + lane_base + half * NC + c * 32, reinterpret_cast<uint32_t*>(t) + c * 32);
+            wait_ld();
+            fence_before();
+            mbar_arrive(smem_u32(&sm.s_empty));          // S may be overwritten by the next tile's product
+            const int kb = (tile_lo + j) * BN + half * NC;
+            // Tiles that lie wholly inside every row's range (most of them) need no mask.
+            const bool whole = n_rows == BM && (tile_lo + j) * BN + BN - 1 <= pos0 && (tile_lo + j) * BN + BN <= len &&
+                               (window <= 0 || (tile_lo + j) * BN > pos_last - window);
+            float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+            if (whole) {
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+                    t[c] *= scale_log2;
+                    mx[c & 3] = fmaxf(mx[c & 3], t[c]);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+                    const int key = kb + c;
+                    const bool vis = row_ok && key <= pos_r && key < len && (window <= 0 || key > pos_r - window);
+                    t[c] = vis ? t[c] * scale_log2 : -CUDART_INF_F;
+                    mx[c & 3] = fmaxf(mx[c & 3], t[c]);
+                }
+            }
+            // The row's maximum over both halves.
+            const float m_mine = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            sm.row_max[j & 1][half][r] = m_mine;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const float m_tile = fmaxf(m_mine, sm.row_max[j & 1][half ^ 1][r]);
+            // Move the reference only when the maximum has run ahead of it by more than the step.
+            const bool need = m_tile > m_ref + RESCALE_STEP;      // also true for the first visible key (m_ref = -inf)
+            const float corr = need ? ex2(m_ref - m_tile) : 1.0f;     // m_ref = -inf gives 0
+            if (need) { m_ref = m_tile; l *= corr; }
+            if (j > 0 && __any_sync(0xffffffffu, need)) {
+                LQ_WAIT(sm.pv_done, (j - 1) & 1, 8);              // O holds everything up to the last tile
+                if (!ok) break;
+                fence_after();
+#pragma unroll 1
+                for (int c = 0; c < NC / 32; ++c) {               // this thread's half of the row of O
+                    uint32_t o[32];
+                    ld32(tmem_o + lane_base + half * NC + c * 32, o);
+                    wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                    st32(tmem_o + lane_base + half * NC + c * 32, o);
+                }
+                wait_st();
+            }
+            const float base = m_ref == -CUDART_INF_F ? 0.f : m_ref;
+            if (j > 0) {
+                LQ_WAIT(sm.pv_done, (j - 1) & 1, 8);              // the last product has read P
+                if (!ok) break;
+            }
+            // Row r of this half's panel of P: 8 pieces of 8 keys; piece c lies at piece (c ^ (r % 8)) of the row.
+            // The sum runs over the probabilities as the product will see them (rounded to bfloat16).
+            float sums[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < NC / 8; ++c) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float p0 = round_bf16(ex2(t[8 * c + 2 * i] - base));
+                    const float p1 = round_bf16(ex2(t[8 * c + 2 * i + 1] - base));
+                    sums[i] += p0 + p1;
+                    pk[i] = pack2(p0, p1);
+                }
+                uint8_t* dst = sm.p[half] + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
+                *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+            l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
+            fence_async_shared();
+            fence_before();
+            mbar_arrive(smem_u32(&sm.p_full));
+        }
+        if (ok) {
+            LQ_WAIT(sm.pv_done, (n_tiles - 1) & 1, 9);
+        }
+        if (ok) {
+            fence_after();
+            sm.row_sum[half][r] = l;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const float inv = 1.0f / (sm.row_sum[0][r] + sm.row_sum[1][r]);
+            __nv_bfloat16* orow = out + ((size_t)(row0 + r) * H + h) * HD + half * NC;
+#pragma unroll 1
+            for (int c = 0; c < NC / 32; ++c) {
+                uint32_t o[32];
+                ld32(tmem_o + lane_base + half * NC + c * 32, o);
+                wait_ld();
+                if (row_ok) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        reinterpret_cast<uint4*>(orow + c * 32)[i] =
+                            make_uint4(pack2(__uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv),
+                                       pack2(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv),
+                                       pack2(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv),
+                                       pack2(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv));
+                }
+            }
+        }
+    }
+    fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        fence_after();
+        tmem_dealloc(sm.tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace
+
+// q: [T, q_stride] bfloat16 rows whose first H*128 elements hold the query heads; out [T, H*128].
+// k_pages, v_pages: [n_pages, Hkv, 64, 128] bfloat16 of one cache entry, finite everywhere.
+// qb_*: the work list, n_blocks entries: sequence, first packed row, rows (<= 128), position of the first row.
+LQ_EXPORT int lq_attn_prefill_tc(const void* q, int q_stride, int T, const void* k_pages, const void* v_pages,
+                                 int n_pages, const int* page_table, int pt_stride, const int* slots, const int* kv_len,
+                                 const int* qb_seq, const int* qb_row, const int* qb_rows, const int* qb_pos, void* out,
+                                 int n_blocks, int H, int Hkv, int hd, int page_size, float scale, int window,
+                                 cudaStream_t stream) {
+    if (n_blocks <= 0) return LQ_OK;
+    if (hd != HD || page_size != PAGE || H % Hkv || q_stride % 8 || ((uintptr_t)q & 15)) return LQ_BAD_SIZE;
+    CUtensorMap mq, mk, mv;
+    const long kv_rows = (long)n_pages * Hkv * PAGE;
+    int rc = make_map_bf16(&mq, q, T, q_stride, q_stride, BM);
+    if (rc == LQ_OK) rc = make_map_bf16(&mk, k_pages, kv_rows, HD, HD, PAGE);
+    if (rc == LQ_OK) rc = make_map_bf16(&mv, v_pages, kv_rows, HD, HD, PAGE);
+    if (rc != LQ_OK) return rc;
+    constexpr size_t smem = sizeof(Smem) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return lq_launch_status();
+        configured = true;
+    }
+    return launch_pdl(attn_prefill_tc_kernel, dim3(n_blocks, H), dim3(N_THREADS), smem, stream, mq, mk, mv, page_table,
+                      pt_stride, slots, kv_len, qb_seq, qb_row, qb_rows, qb_pos, (__nv_bfloat16*)out, H, Hkv,
+                      (int)kv_rows, scale * 1.4426950408889634f, window);
+}
+
+LQ_EXPORT int lq_attn_prefill_tc_status() {
+    int v = 0, zero = 0;
+    cudaMemcpyFromSymbol(&v, g_status, sizeof(int));
+    if (v) cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+    return v;
+}

@@ -67,13 +67,15 @@ def pack_step(entries, want, past: list[int]) -> tuple[np.ndarray, dict]:
     else:
         rows = np.asarray([cu[b] + int(w) for b, ws in enumerate(want) for w in ws], dtype=np.int64)
     # Work list of the prefill attention: blocks of at most 64 consecutive rows of one sequence.
-    qb = [(b, int(cu[b]) + r, min(QUERY_BLOCK, n - r), p + r)
-          for b, (p, n) in enumerate(zip(past, new)) for r in range(0, n, QUERY_BLOCK)]
-    qb.sort(key=lambda e: -e[3])          # blocks with the most keys first
-    qb = np.asarray(qb, dtype=np.int64).reshape(-1, 4)
+    def blocks(size):
+        qb = [(b, int(cu[b]) + r, min(size, n - r), p + r)
+              for b, (p, n) in enumerate(zip(past, new)) for r in range(0, n, size)]
+        qb.sort(key=lambda e: -e[3])          # blocks with the most keys first
+        return np.asarray(qb, dtype=np.int64).reshape(-1, 4)
+    qb, qc = blocks(QUERY_BLOCK), blocks(2 * QUERY_BLOCK)
     parts = {"tokens": tokens, "tok_seq": tok_seq, "tok_pos": tok_pos, "slots": slots, "kv_len": kv_len,
              "cu_rows": cu, "want_rows": rows, "qb_seq": qb[:, 0], "qb_row": qb[:, 1], "qb_rows": qb[:, 2],
-             "qb_pos": qb[:, 3]}
+             "qb_pos": qb[:, 3], "qc_seq": qc[:, 0], "qc_row": qc[:, 1], "qc_rows": qc[:, 2], "qc_pos": qc[:, 3]}
     layout, offset = {}, 0
     for name, arr in parts.items():
         layout[name] = (offset, len(arr))
@@ -96,6 +98,7 @@ def make_context(flat_dev: torch.Tensor, info: dict, h_slots: list[int]) -> Step
                        tok_pos=part("tok_pos"), slots=part("slots"), kv_len=part("kv_len"), cu_rows=part("cu_rows"),
                        want_rows=want if want.numel() else None,
                        query_blocks=(part("qb_seq"), part("qb_row"), part("qb_rows"), part("qb_pos")),
+                       query_blocks128=(part("qc_seq"), part("qc_row"), part("qc_rows"), part("qc_pos")),
                        h_slots=h_slots, h_new=info["new"],
                        h_past=info["past"], max_new=info["max_new"], max_kv=info["max_kv"])
 

@@ -126,11 +126,20 @@ def bench_attn_prefill(args) -> dict:
     slots = torch.zeros(1, dtype=torch.int32, device=dev)
     kv_len = torch.full((1,), T, dtype=torch.int32, device=dev)
 
+    nb2 = -(-T // 128)
+    starts2 = torch.arange(nb2 - 1, -1, -1, dtype=torch.int32, device=dev) * 128
+    blocks128 = (torch.zeros(nb2, dtype=torch.int32, device=dev), starts2.contiguous(),
+                 torch.minimum(torch.full_like(starts2, 128), T - starts2).contiguous(), starts2.clone())
+    tc = args.what == "attn_prefill_tc"
+
     def run(i):
-        ops.attn_prefill(q, k, v, table, slots, kv_len, blocks, H, Hkv, hd, 64, hd ** -0.5, None)
+        if tc:
+            ops.attn_prefill_tc(q, k, v, table, slots, kv_len, blocks128, H, Hkv, hd, 64, hd ** -0.5, None)
+        else:
+            ops.attn_prefill(q, k, v, table, slots, kv_len, blocks, H, Hkv, hd, 64, hd ** -0.5, None)
     ms = _time(run, args.iters, args.warmup)
     flops = 4.0 * H * hd * T * (T + 1) / 2.0
-    return {"kernel": "attn_prefill", "tokens": T, "heads": H, "kv_heads": Hkv, "head_dim": hd, "ms": ms,
+    return {"kernel": args.what, "tokens": T, "heads": H, "kv_heads": Hkv, "head_dim": hd, "ms": ms,
             "tflops": flops / ms / 1e9}
 
 
@@ -187,7 +196,8 @@ def bench_prefill(args) -> dict:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("what", choices=["gemm_skinny", "gemm_stream", "gemm_tc", "attn_decode", "attn_prefill", "step", "prefill"])
+    ap.add_argument("what", choices=["gemm_skinny", "gemm_stream", "gemm_tc", "attn_decode", "attn_prefill", "attn_prefill_tc", "step",
+                                     "prefill"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -211,7 +221,7 @@ def main(argv=None) -> int:
         out = bench_gemm(args.what, args)
     elif args.what == "attn_decode":
         out = bench_attn_decode(args)
-    elif args.what == "attn_prefill":
+    elif args.what in ("attn_prefill", "attn_prefill_tc"):
         out = bench_attn_prefill(args)
     elif args.what == "prefill":
         out = bench_prefill(args)

@@ -87,7 +87,7 @@ def _contig(t: torch.Tensor, what: str) -> torch.Tensor:
 def prepare(dtype: torch.dtype, verbose: bool = True) -> None:
     """Build and load the libraries a model of this dtype uses, before the first step."""
     from concurrent.futures import ThreadPoolExecutor
-    names = ["plain_kernels"] + (["gemm_skinny", "gemm_stream", "gemm_tc", "attn_decode", "attn_prefill"]
+    names = ["plain_kernels"] + (["gemm_skinny", "gemm_stream", "gemm_tc", "attn_decode", "attn_prefill", "attn_prefill_tc"]
                                              if dtype == torch.bfloat16 else [])
     with ThreadPoolExecutor(max_workers=len(names)) as pool:
         list(pool.map(build.build, names))
@@ -346,6 +346,34 @@ def attn_prefill(q: torch.Tensor, k_pages, v_pages, page_table, slots, kv_len, q
               _p(qb_seq), _p(qb_row), _p(qb_rows), _p(qb_pos), _p(out), qb_seq.numel(), H, Hkv, hd, page_size,
               float(scale), int(window or 0), _stream()), "attn_prefill")
     return out
+
+
+def attn_prefill_tc(q: torch.Tensor, k_pages, v_pages, page_table, slots, kv_len, query_blocks128, H: int, Hkv: int,
+                    hd: int, page_size: int, scale: float, window: int | None,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """attn_prefill on the tcgen05 tensor cores (TMA-fed, S and O in tensor memory): blocks of at
+    most 128 query rows, head_dim 128, pages of 64 keys, a cache that is finite everywhere."""
+    T = q.shape[0]
+    if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
+        raise KernelError("attn_prefill_tc takes bfloat16 queries and cache")
+    if hd != 128 or page_size != 64:
+        raise KernelError(f"attn_prefill_tc: head_dim {hd} (128) and page size {page_size} (64)")
+    if out is None:
+        out = torch.empty((T, H * hd), dtype=torch.bfloat16, device=q.device)
+    qb_seq, qb_row, qb_rows, qb_pos = query_blocks128
+    fn = _fn("attn_prefill_tc", "lq_attn_prefill_tc", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                       c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _check(fn(_p(q), q.stride(0), T, _p(_contig(k_pages, "k_pages")), _p(_contig(v_pages, "v_pages")), k_pages.shape[0],
+              _p(page_table), page_table.stride(0), _p(slots), _p(kv_len), _p(qb_seq), _p(qb_row), _p(qb_rows), _p(qb_pos),
+              _p(out), qb_seq.numel(), H, Hkv, hd, page_size, float(scale), int(window or 0), _stream()), "attn_prefill_tc")
+    return out
+
+
+def attn_prefill_tc_status() -> int:
+    fn = build.load("attn_prefill_tc").lq_attn_prefill_tc_status
+    fn.restype = c_int
+    return int(fn())
 
 
 def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq, slots, H: int, Hkv: int, hd: int,

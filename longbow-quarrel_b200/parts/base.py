@@ -44,6 +44,7 @@ class StepContext:
     cu_rows: torch.Tensor
     want_rows: torch.Tensor | None
     query_blocks: tuple | None      # (sequence, first row, rows, first position) of each 64-row block, int32
+    query_blocks128: tuple | None   # the same for blocks of 128 rows
     h_slots: list[int]
     h_new: list[int]
     h_past: list[int]

@@ -109,7 +109,7 @@ def test_swiglu(dtype, block):
 class PagedCase:
     """Random K/V for sequences of given lengths, scattered over shuffled pages."""
 
-    def __init__(self, lens, Hkv, hd, dtype, seed, page_size=64, extra_pages=3):
+    def __init__(self, lens, Hkv, hd, dtype, seed, page_size=64, extra_pages=3, poison=float("nan")):
         rng = np.random.default_rng(seed)
         self.lens, self.Hkv, self.hd, self.page_size = lens, Hkv, hd, page_size
         n_seq = len(lens)
@@ -119,8 +119,8 @@ class PagedCase:
         self.k = [_rand((n, Hkv, hd), dtype, seed * 100 + i) for i, n in enumerate(lens)]
         self.v = [_rand((n, Hkv, hd), dtype, seed * 100 + 50 + i) for i, n in enumerate(lens)]
         # Unused memory is poisoned so that a read outside a sequence's keys shows.
-        self.k_pages = torch.full((n_pages, Hkv, page_size, hd), float("nan"), dtype=dtype, device=DEV)
-        self.v_pages = torch.full((n_pages, Hkv, page_size, hd), float("nan"), dtype=dtype, device=DEV)
+        self.k_pages = torch.full((n_pages, Hkv, page_size, hd), poison, dtype=dtype, device=DEV)
+        self.v_pages = torch.full((n_pages, Hkv, page_size, hd), poison, dtype=dtype, device=DEV)
         self.n_slots = n_seq + 2
         self.slot_of = [int(s) for s in rng.permutation(self.n_slots)[:n_seq]]
         table = np.full((self.n_slots, max(pages_per) + 1), -1, dtype=np.int32)
@@ -473,3 +473,66 @@ def test_gemm_skinny_qkv_rotates_and_stores(M, H, Hkv, hd, rotate):
     for pages, before in ((case.k_pages, k_before), (case.v_pages, v_before)):
         same = (pages == before) | (pages.isnan() & before.isnan())
         assert bool((same | touched).all())          # nothing else in the cache was written
+
+
+def _query_blocks128(new, past):
+    out, row = [], 0
+    for b, (n, p) in enumerate(zip(new, past)):
+        for r in range(0, n, 128):
+            out.append((b, row + r, min(128, n - r), p + r))
+        row += n
+    arr = np.asarray(out, dtype=np.int32)
+    return tuple(torch.from_numpy(np.ascontiguousarray(arr[:, i])).to(DEV) for i in range(4))
+
+
+@pytest.mark.parametrize("H,Hkv,window", [(8, 2, None), (4, 4, 100), (2, 1, 300)])
+def test_attn_prefill_tc(H, Hkv, window):
+    """The tcgen05 prefill attention: three sequences in one call (whole from position 0; one
+    token; one continuing after 70 cached tokens), unused cache rows poisoned with huge finite
+    values, so that a key read beyond a sequence shows."""
+    ops = _ops()
+    hd = 128
+    lens, new, past = [700, 1, 330], [700, 1, 260], [0, 0, 70]
+    case = PagedCase(lens, Hkv, hd, torch.bfloat16, seed=12, poison=3.0e38)
+    tok_seq = [b for b, n in enumerate(new) for _ in range(n)]
+    tok_pos = [p + i for n, p in zip(new, past) for i in range(n)]
+    q = _rand((sum(new), (H + 2 * Hkv) * hd), torch.bfloat16, 83)
+    scale = hd ** -0.5
+    out = ops.attn_prefill_tc(q, case.k_pages, case.v_pages, case.table, case.slots, _ints(lens),
+                              _query_blocks128(new, past), H, Hkv, hd, 64, scale, window)
+    torch.cuda.synchronize()
+    assert ops.attn_prefill_tc_status() == 0
+    ref = case.reference(q[:, :H * hd].reshape(-1, H, hd).float(), tok_seq, tok_pos, H, scale, window)
+    _close(out.reshape(-1, H, hd), ref, _attn_tol(case, ref), BF16_ULP)
+
+
+def test_attn_prefill_tc_far_key_and_growing_maximum():
+    """Scores that grow along the keys (the reference maximum has to move and O be rescaled
+    several times), and a key made to stand out at position 0 of a long sequence."""
+    ops = _ops()
+    H = Hkv = 1
+    hd, n = 128, 900
+    case = PagedCase([n], Hkv, hd, torch.bfloat16, seed=13, poison=3.0e38)
+    q = _rand((n, hd), torch.bfloat16, 84)
+    slot = case.slot_of[0]
+    # keys aligned with a fixed direction and growing in length: scores rise steadily with the key index
+    direction = torch.nn.functional.normalize(_rand((hd,), torch.float32, 85), dim=0)
+    q[:, :] = (direction * 6.0).to(torch.bfloat16)
+    for pos in range(n):
+        key = (direction * (pos / 15.0)).to(torch.bfloat16)
+        case.k_pages[int(case.table[slot, pos // 64]), 0, pos % 64] = key
+        case.k[0][pos, 0] = key
+    blocks = _query_blocks128([n], [0])
+    out = ops.attn_prefill_tc(q, case.k_pages, case.v_pages, case.table, case.slots, _ints([n]), blocks, 1, 1, hd, 64,
+                              1.0, None)
+    ref = case.reference(q.reshape(n, 1, hd).float(), [0] * n, list(range(n)), 1, 1.0, None)
+    _close(out.reshape(n, 1, hd), ref, _attn_tol(case, ref), BF16_ULP)
+    # a far key: position 0 dominates row 899
+    far = (direction * 200.0).to(torch.bfloat16)
+    case.k_pages[int(case.table[slot, 0]), 0, 0] = far
+    case.k[0][0, 0] = far
+    out = ops.attn_prefill_tc(q, case.k_pages, case.v_pages, case.table, case.slots, _ints([n]), blocks, 1, 1, hd, 64,
+                              1.0, None)
+    _close(out[899], case.v[0][0, 0], 2e-2)
+    torch.cuda.synchronize()
+    assert ops.attn_prefill_tc_status() == 0
