@@ -65,7 +65,9 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
     __nv_bfloat16* sv = sk + 2 * BLOCK_N * LD;                                    // [2][64][LD]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int blk = blockIdx.x, h = blockIdx.y;
+    // Heads vary fastest: the work list has the blocks with the most keys first, so the launch order is
+    // longest-first over all heads and the short blocks fill the tail.
+    const int blk = blockIdx.x / H, h = blockIdx.x % H;
     pdl_launch_dependents();
     pdl_wait();
     const int seq = qb_seq[blk], row0 = qb_row[blk], n_rows = qb_rows[blk], pos0 = qb_pos[blk];
@@ -238,7 +240,7 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
             return lq_launch_status();
         configured = true;
     }
-    dim3 grid(n_blocks, H);
+    dim3 grid(n_blocks * H);
     return launch_pdl(attn_prefill_kernel<HD>, grid, dim3(NT), smem, stream, (const __nv_bfloat16*)q, q_stride,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, slots, kv_len, qb_seq, qb_row,
         qb_rows, qb_pos, (__nv_bfloat16*)out, H, Hkv, hd, scale * 1.4426950408889634f, window);

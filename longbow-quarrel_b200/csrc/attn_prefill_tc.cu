@@ -102,7 +102,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t tmem_s = sm.tmem_base, tmem_o = sm.tmem_base + BN;
     pdl_wait();
 
-    const int blk = blockIdx.x, h = blockIdx.y;
+    // Heads vary fastest: the work list has the blocks with the most keys first, so the launch order is
+    // longest-first over all heads and the short blocks fill the tail.
+    const int blk = blockIdx.x / H, h = blockIdx.x % H;
     const int seq = qb_seq[blk], row0 = qb_row[blk], n_rows = qb_rows[blk], pos0 = qb_pos[blk];
     const int kvh = h / (H / Hkv);
     const int len = kv_len[seq];
@@ -333,7 +335,7 @@ LQ_EXPORT int lq_attn_prefill_tc(const void* q, int q_stride, int T, const void*
             return lq_launch_status();
         configured = true;
     }
-    return launch_pdl(attn_prefill_tc_kernel, dim3(n_blocks, H), dim3(N_THREADS), smem, stream, mq, mk, mv, page_table,
+    return launch_pdl(attn_prefill_tc_kernel, dim3(n_blocks * H), dim3(N_THREADS), smem, stream, mq, mk, mv, page_table,
                       pt_stride, slots, kv_len, qb_seq, qb_row, qb_rows, qb_pos, (__nv_bfloat16*)out, H, Hkv,
                       (int)kv_rows, scale * 1.4426950408889634f, window);
 }

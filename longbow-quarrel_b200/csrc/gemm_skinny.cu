@@ -17,6 +17,12 @@
 // SwiGLU over weight rows interleaved in blocks of 8 (8 gate rows, then their 8 up
 // rows), writing up * silu(gate).
 //
+// RMS norm around the product, without a kernel of its own: the residual epilogue can also
+// write what the next norm makes of the new residual r, split in two -- r * gain rounded to
+// bfloat16, and for every row the sum of r^2 over the block's 16 columns.  A product that reads
+// such rows multiplies its result by 1 / sqrt(sum / width + eps), summed over the blocks in a
+// fixed order: (x * gain * s) . w = s * ((x * gain) . w).
+//
 // Reference counterpart: the mat-vec kernels linear_f16 / linear_f16_f32
 // (internal/device/kernels.metal:105-132,1084-1106), one output row per SIMD group.
 #include "common.cuh"
@@ -64,6 +70,16 @@ struct QkvArgs {
     int pt_stride, H, Hkv, hd, page_size;
 };
 
+// RMS norm folded into the products on either side of it (null pointers: not used).
+struct NormArgs {
+    const float* in_sums;     // [rows of x, in_blocks]: sums of squares of the rows that x was made from
+    int in_blocks;
+    float in_inv_width, in_eps;
+    const float* out_gain;    // [N] gain of the norm that reads the residual next (EPI_RESID only)
+    __nv_bfloat16* out_x;     // [M, N] residual * gain
+    float* out_sums;          // [M, blocks of this launch]
+};
+
 // Work of one warp on `UNROLL` chunks: the W rows of the block as mma A fragments, and (for
 // few tokens) the tokens' x as B fragments, all loaded before any of it is used.
 template <int MT>
@@ -75,8 +91,9 @@ struct Frags {
 template <int MT, int EPI>
 __global__ void __launch_bounds__(WARPS * 32, 2)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, void* Cout,
-                   const float* residual, int M, int N, int K, const QkvArgs qkv) {
+                   const float* residual, int M, int N, int K, const QkvArgs qkv, const NormArgs norm) {
     __shared__ float red[WARPS][ROWS][MT * 8 + 1];
+    __shared__ float row_scale[MT * 8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     // The block's 16 rows of W.  Normally consecutive; for q/k/v the first 8 are elements
@@ -174,6 +191,16 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
             compute(c0, fa);
         }
     }
+    if (norm.in_sums) {
+        // 1 / rms of every row of x, from the sums its producer left: lanes stride over the blocks,
+        // then a butterfly -- the same order whatever the batch.
+        for (int m = warp; m < M; m += WARPS) {
+            float ss = 0.f;
+            for (int b = lane; b < norm.in_blocks; b += 32) ss += norm.in_sums[(size_t)m * norm.in_blocks + b];
+            ss = warp_sum(ss);
+            if (lane == 0) row_scale[m] = rsqrtf(ss * norm.in_inv_width + norm.in_eps);
+        }
+    }
 #pragma unroll
     for (int j = 0; j < MT; ++j) {
         red[warp][g][j * 8 + 2 * t] = acc[j][0];
@@ -192,11 +219,30 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
     };
     for (int i = threadIdx.x; i < MT * 8 * OUT_ROWS; i += WARPS * 32) {
         int m = i / OUT_ROWS, r = i % OUT_ROWS;
+        if (EPI == EPI_RESID && norm.out_x) {
+            // New residual, what the next norm makes of it, and the row's sum of squares over the
+            // block's columns: 16 consecutive lanes hold one row.
+            const int n = n0 + r;
+            const bool ok = m < M && n < N;
+            const size_t o = (size_t)m * N + n;
+            float v = 0.f;
+            if (ok) {
+                v = residual[o] + total(r, m) * (norm.in_sums ? row_scale[m] : 1.f);
+                ((float*)Cout)[o] = v;
+                norm.out_x[o] = __float2bfloat16_rn(v * norm.out_gain[n]);
+            }
+            float ss = v * v;
+#pragma unroll
+            for (int d = 8; d >= 1; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+            if (r == 0 && m < M) norm.out_sums[(size_t)m * gridDim.x + blockIdx.x] = ss;
+            continue;
+        }
         if (m >= M) continue;
-        float s = total(r, m);
+        const float sc = norm.in_sums ? row_scale[m] : 1.f;
+        float s = total(r, m) * sc;
         if (EPI == EPI_QKV) {
             // s and u are elements j and j + hd/2 of one head of token m.
-            float u = total(r + 8, m);
+            float u = total(r + 8, m) * sc;
             const int hd = qkv.hd, half = hd >> 1;
             const int head = n0 / hd, j = n0 % hd + r;
             const int pos = qkv.tok_pos[m];
@@ -219,7 +265,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
                 o[half] = __float2bfloat16_rn(u);
             }
         } else if (EPI == EPI_SWIGLU) {
-            float u = total(r + 8, m);
+            float u = total(r + 8, m) * sc;
             int f = (n0 >> 1) + r;
             if (f < (N >> 1))
                 ((__nv_bfloat16*)Cout)[(size_t)m * (N >> 1) + f] = __float2bfloat16_rn(u * (s / (1.0f + expf(-s))));
@@ -236,16 +282,16 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
 
 template <int MT>
 int launch_mt(const void* X, const void* W, void* C, const float* residual, int M, int N, int K, int epi,
-              cudaStream_t stream, const QkvArgs qkv = QkvArgs{}) {
+              cudaStream_t stream, const NormArgs norm, const QkvArgs qkv = QkvArgs{}) {
     dim3 grid((N + ROWS - 1) / ROWS), block(WARPS * 32);
     const __nv_bfloat16* x = (const __nv_bfloat16*)X;
     const __nv_bfloat16* w = (const __nv_bfloat16*)W;
     switch (epi) {
-        case EPI_BF16: return launch_pdl(gemm_skinny_kernel<MT, EPI_BF16>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv);
-        case EPI_F32: return launch_pdl(gemm_skinny_kernel<MT, EPI_F32>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv);
-        case EPI_RESID: return launch_pdl(gemm_skinny_kernel<MT, EPI_RESID>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv);
-        case EPI_SWIGLU: return launch_pdl(gemm_skinny_kernel<MT, EPI_SWIGLU>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv);
-        case EPI_QKV: return launch_pdl(gemm_skinny_kernel<MT, EPI_QKV>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv);
+        case EPI_BF16: return launch_pdl(gemm_skinny_kernel<MT, EPI_BF16>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv, norm);
+        case EPI_F32: return launch_pdl(gemm_skinny_kernel<MT, EPI_F32>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv, norm);
+        case EPI_RESID: return launch_pdl(gemm_skinny_kernel<MT, EPI_RESID>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv, norm);
+        case EPI_SWIGLU: return launch_pdl(gemm_skinny_kernel<MT, EPI_SWIGLU>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv, norm);
+        case EPI_QKV: return launch_pdl(gemm_skinny_kernel<MT, EPI_QKV>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv, norm);
         default: return LQ_BAD_DTYPE;
     }
     return lq_launch_status();
@@ -255,34 +301,50 @@ int launch_mt(const void* X, const void* W, void* C, const float* residual, int 
 
 // X [M, K] bf16, W [N, K] bf16; M <= 64, K % 8 == 0.  For EPI_SWIGLU, N counts the
 // interleaved gate and up rows (N % 16 == 0) and C is [M, N / 2].
+// in_sums (or null): x is (rows * gain) of an RMS norm whose 1 / rms is still to be applied;
+// in_sums [M, in_blocks] holds the rows' sums of squares, in_inv_width = 1 / width, in_eps the norm's eps.
+// out_gain, out_x, out_sums (EPI_RESID only, or null): also write (new residual * out_gain) as
+// bfloat16 [M, N] and the sums of squares [M, lq_gemm_skinny_blocks(N)] for the product that follows.
 LQ_EXPORT int lq_gemm_skinny(const void* X, const void* W, void* C, const float* residual, int M, int N, int K,
-                             int epi, cudaStream_t stream) {
+                             int epi, const float* in_sums, int in_blocks, float in_inv_width, float in_eps,
+                             const float* out_gain, void* out_x, float* out_sums, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return LQ_OK;
     if (M > 64 || K % 8 != 0 || K <= 0) return LQ_BAD_SIZE;
     if (epi == EPI_SWIGLU && N % 16 != 0) return LQ_BAD_SIZE;
     if (epi == EPI_RESID && residual == nullptr) return LQ_BAD_SIZE;
+    if (in_sums && in_blocks <= 0) return LQ_BAD_SIZE;
+    if (out_x && (epi != EPI_RESID || !out_gain || !out_sums)) return LQ_BAD_SIZE;
+    const NormArgs norm{in_sums, in_blocks, in_inv_width, in_eps, out_x ? out_gain : nullptr,
+                        (__nv_bfloat16*)out_x, out_x ? out_sums : nullptr};
     int mt = (M + 7) / 8;
     switch (mt) {
-        case 1: return launch_mt<1>(X, W, C, residual, M, N, K, epi, stream);
-        case 2: return launch_mt<2>(X, W, C, residual, M, N, K, epi, stream);
-        case 3: case 4: return launch_mt<4>(X, W, C, residual, M, N, K, epi, stream);
-        default: return launch_mt<8>(X, W, C, residual, M, N, K, epi, stream);
+        case 1: return launch_mt<1>(X, W, C, residual, M, N, K, epi, stream, norm);
+        case 2: return launch_mt<2>(X, W, C, residual, M, N, K, epi, stream, norm);
+        case 3: case 4: return launch_mt<4>(X, W, C, residual, M, N, K, epi, stream, norm);
+        default: return launch_mt<8>(X, W, C, residual, M, N, K, epi, stream, norm);
     }
 }
+
+// Blocks of a product with N output columns: the second size of out_sums.
+LQ_EXPORT int lq_gemm_skinny_blocks(int N) { return (N + ROWS - 1) / ROWS; }
 
 // The q/k/v projection of decoding with its epilogue fused: X [M <= 16, K] . W^T for
 // W [(H + 2 Hkv) hd, K]; q and k are rotated by the cos/sin tables at each token's position
 // (tables null: no rotation); q goes to q_out [M, H hd], k and v go into the token's cache page.
 // hd % 16 == 0.  Replaces the product, the rotation kernel and the cache write of a decode step.
+// in_sums ...: as for lq_gemm_skinny.
 LQ_EXPORT int lq_gemm_skinny_qkv(const void* X, const void* W, void* q_out, int M, int K, const float* cos_t,
                                  const float* sin_t, const int* tok_pos, const int* tok_seq, const int* slots,
                                  const int* page_table, int pt_stride, void* k_pages, void* v_pages, int H, int Hkv,
-                                 int hd, int page_size, cudaStream_t stream) {
+                                 int hd, int page_size, const float* in_sums, int in_blocks, float in_inv_width,
+                                 float in_eps, cudaStream_t stream) {
     if (M <= 0) return LQ_OK;
     if (M > 16 || K % 8 != 0 || K <= 0 || hd % 16 != 0 || H <= 0 || Hkv <= 0) return LQ_BAD_SIZE;
+    if (in_sums && in_blocks <= 0) return LQ_BAD_SIZE;
     QkvArgs a{cos_t, sin_t, tok_pos, tok_seq, slots, page_table, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages,
               pt_stride, H, Hkv, hd, page_size};
+    const NormArgs norm{in_sums, in_blocks, in_inv_width, in_eps, nullptr, nullptr, nullptr};
     const int N = (H + 2 * Hkv) * hd;
-    if (M <= 8) return launch_mt<1>(X, W, q_out, nullptr, M, N, K, EPI_QKV, stream, a);
-    return launch_mt<2>(X, W, q_out, nullptr, M, N, K, EPI_QKV, stream, a);
+    if (M <= 8) return launch_mt<1>(X, W, q_out, nullptr, M, N, K, EPI_QKV, stream, norm, a);
+    return launch_mt<2>(X, W, q_out, nullptr, M, N, K, EPI_QKV, stream, norm, a);
 }

@@ -84,8 +84,17 @@ class Model:
         """Run this step's rows through every scheduled layer; logits [wanted, vocab]
         (float32) at ctx.want_rows, or None when nothing is wanted."""
         x = self.embedding.forward(ctx.tokens)
-        for entry in self.spec.schedule:
-            self.blocks[entry.layer].forward(x, ctx, cache.view(entry.cache), entry.writes_cache)
+        schedule = self.spec.schedule
+        normed = None           # rows of the next layer's first norm, when this layer's last product made them
+        for i, entry in enumerate(schedule):
+            block = self.blocks[entry.layer]
+            if not getattr(block, "folds_norm", False):
+                block.forward(x, ctx, cache.view(entry.cache), entry.writes_cache)
+                normed = None
+                continue
+            after = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+            emit = after.input_norm(x.shape[0]) if getattr(after, "folds_norm", False) else None
+            normed = block.forward(x, ctx, cache.view(entry.cache), entry.writes_cache, normed=normed, emit=emit)
         if ctx.want_rows is None or ctx.want_rows.numel() == 0:
             return None
         h = self.final_norm.forward(x, rows=ctx.want_rows)

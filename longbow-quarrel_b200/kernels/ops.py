@@ -201,12 +201,49 @@ SKINNY_MAX_ROWS = 64          # most rows the two decode products take
 SKINNY_BEST_ROWS = 16         # up to here streaming W through registers beats the TMA stream
 
 
-def gemm_skinny(a: torch.Tensor, w: torch.Tensor, epi: int, residual: torch.Tensor | None = None,
-                out: torch.Tensor | None = None) -> torch.Tensor:
+class NormedRows:
+    """Rows of an RMS norm whose 1 / rms is still to be applied, as the residual epilogue of
+    gemm_skinny leaves them: `data` = residual * gain in bfloat16 [M, width]; `sums` float32
+    [M, blocks], each row's sum of squares cut into column blocks; `eps` of the norm.  A product
+    that reads them multiplies its result by 1 / sqrt(sum(sums) / width + eps)."""
+
+    __slots__ = ("data", "sums", "eps")
+
+    def __init__(self, data: torch.Tensor, sums: torch.Tensor, eps: float):
+        self.data, self.sums, self.eps = data, sums, float(eps)
+
+    @property
+    def shape(self):
+        return self.data.shape
+
+    @property
+    def dtype(self):
+        return self.data.dtype
+
+    def finish(self) -> torch.Tensor:
+        """The normalised rows themselves (for an operation that cannot take them unfinished)."""
+        scale = torch.rsqrt(self.sums.sum(dim=1, keepdim=True) / self.data.shape[1] + self.eps)
+        return (self.data.to(torch.float32) * scale).to(self.data.dtype)
+
+
+def _norm_in(a):
+    """(tensor, sums pointer, blocks, 1 / width, eps) of plain or unfinished rows."""
+    if isinstance(a, NormedRows):
+        if a.sums.dtype != torch.float32 or a.sums.shape[0] != a.data.shape[0] or not a.sums.is_contiguous():
+            raise KernelError("unfinished rows: sums must be contiguous float32 [rows, blocks]")
+        return a.data, _p(a.sums), a.sums.shape[1], 1.0 / a.data.shape[1], a.eps
+    return a, None, 0, 0.0, 0.0
+
+
+def gemm_skinny(a, w: torch.Tensor, epi: int, residual: torch.Tensor | None = None,
+                out: torch.Tensor | None = None, emit: tuple | None = None):
     """a [M <= 64, K] . w [N, K]^T, both bfloat16, streaming w once from memory.
     epi: EPI_BF16 / EPI_F32 store; EPI_RESID adds into the float32 `residual` in place;
     EPI_SWIGLU reads w as alternating blocks of 8 gate and 8 up rows and stores
-    up * silu(gate) [M, N / 2]."""
+    up * silu(gate) [M, N / 2].
+    `a` may be NormedRows.  emit = (gain [N] float32, eps), with EPI_RESID only: also returns what the
+    RMS norm with that gain makes of the new residual, as NormedRows: (residual, rows)."""
+    a, in_sums, in_blocks, in_inv, in_eps = _norm_in(a)
     M, K = a.shape
     N = w.shape[0]
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
@@ -222,15 +259,27 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, epi: int, residual: torch.Tens
     elif out is None:
         shape = (M, N // 2) if epi == EPI_SWIGLU else (M, N)
         out = torch.empty(shape, dtype=torch.float32 if epi == EPI_F32 else torch.bfloat16, device=a.device)
-    fn = _fn("gemm_skinny", "lq_gemm_skinny", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), _p(residual), M, N, K, epi, _stream()), "gemm_skinny")
-    return out
+    rows = None
+    gain = None
+    if emit is not None:
+        gain, eps = emit
+        if epi != EPI_RESID or gain.dtype != torch.float32 or gain.numel() != N:
+            raise KernelError("gemm_skinny: rows for the next norm come with EPI_RESID and a float32 gain [N]")
+        rows = NormedRows(torch.empty((M, N), dtype=torch.bfloat16, device=a.device),
+                          torch.empty((M, -(-N // 16)), dtype=torch.float32, device=a.device), eps)
+    fn = _fn("gemm_skinny", "lq_gemm_skinny", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                               c_void_p, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), _p(residual), M, N, K, epi, in_sums, in_blocks, in_inv,
+              in_eps, _p(gain), _p(rows.data) if rows else None, _p(rows.sums) if rows else None, _stream()), "gemm_skinny")
+    return (out, rows) if emit is not None else out
 
 
-def gemm_skinny_qkv(a: torch.Tensor, w: torch.Tensor, cos, sin, tok_pos, tok_seq, slots, page_table, k_pages, v_pages,
+def gemm_skinny_qkv(a, w: torch.Tensor, cos, sin, tok_pos, tok_seq, slots, page_table, k_pages, v_pages,
                     H: int, Hkv: int, hd: int, page_size: int, out: torch.Tensor | None = None) -> torch.Tensor:
     """The q/k/v projection of at most 16 tokens with rotation and cache write in its epilogue:
-    returns the rotated q [M, H*hd]; the rotated k and v are stored in each token's cache page."""
+    returns the rotated q [M, H*hd]; the rotated k and v are stored in each token's cache page.
+    `a` may be NormedRows."""
+    a, in_sums, in_blocks, in_inv, in_eps = _norm_in(a)
     M, K = a.shape
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
         raise KernelError("gemm_skinny_qkv takes bfloat16 inputs and cache")
@@ -242,10 +291,10 @@ def gemm_skinny_qkv(a: torch.Tensor, w: torch.Tensor, cos, sin, tok_pos, tok_seq
         out = torch.empty((M, H * hd), dtype=torch.bfloat16, device=a.device)
     fn = _fn("gemm_skinny", "lq_gemm_skinny_qkv", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                                    c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
-                                                   c_int, c_int, c_void_p])
+                                                   c_int, c_int, c_void_p, c_int, c_float, c_float, c_void_p])
     _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), M, K, _p(cos), _p(sin), _p(tok_pos), _p(tok_seq),
               _p(slots), _p(page_table), page_table.stride(0), _p(k_pages), _p(v_pages), H, Hkv, hd, page_size,
-              _stream()), "gemm_skinny_qkv")
+              in_sums, in_blocks, in_inv, in_eps, _stream()), "gemm_skinny_qkv")
     return out
 
 

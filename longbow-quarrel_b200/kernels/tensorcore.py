@@ -16,13 +16,23 @@ def _decode_kernel(M: int):
     return ops.gemm_skinny if M <= ops.SKINNY_BEST_ROWS else ops.gemm_stream
 
 
-def linear_bf16(a, weight, out_dtype, residual):
+def _rows_for(fn, a):
+    """Unfinished rows of a norm go to the kernel that finishes them; every other kernel gets plain rows."""
+    return a if fn is ops.gemm_skinny or not isinstance(a, ops.NormedRows) else a.finish()
+
+
+def linear_bf16(a, weight, out_dtype, residual, emit=None):
     """a [M, K] bf16 . W^T; returns None when no tensor-core kernel takes this product."""
     M, K = a.shape
     if K % 8:
         return None
     fn = _decode_kernel(M) if M <= ops.SKINNY_MAX_ROWS else ops.gemm_tc
+    a = _rows_for(fn, a)
     if residual is not None:
+        if emit is not None:
+            if fn is ops.gemm_skinny:
+                return fn(a, weight.tensor, ops.EPI_RESID, residual, emit=emit)
+            return fn(a, weight.tensor, ops.EPI_RESID, residual), None
         return fn(a, weight.tensor, ops.EPI_RESID, residual)
     return fn(a, weight.tensor, ops.EPI_F32 if out_dtype == torch.float32 else ops.EPI_BF16)
 
@@ -33,4 +43,4 @@ def linear_swiglu_bf16(a, weight):
     if K % 8:
         return None
     fn = _decode_kernel(M) if M <= ops.SKINNY_MAX_ROWS else ops.gemm_tc
-    return fn(a, weight.tensor, ops.EPI_SWIGLU)
+    return fn(_rows_for(fn, a), weight.tensor, ops.EPI_SWIGLU)

@@ -28,6 +28,7 @@ DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight
 @register_part("mixer", "attention")
 class Attention(Mixer):
     graph_safe = True
+    folds_norm = True
 
     def __init__(self, runtime: Runtime, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  scale: float, position: PartSpec | None = None, window: int | None = None,
@@ -61,7 +62,7 @@ class Attention(Mixer):
         self.w_qkv = linear.LinearWeight(torch.cat(rows, dim=0))
         self.w_o = linear.LinearWeight(tensors[n["o"]])
 
-    def forward(self, h, ctx: StepContext, cache_view, residual, writes_cache: bool = True):
+    def forward(self, h, ctx: StepContext, cache_view, residual, writes_cache: bool = True, emit=None):
         store = self.own_kv and writes_cache
         tables = self.position.tables() if self.position is not None else None
         if (store and h.dtype == torch.bfloat16 and self.w_qkv.tensor.dtype == torch.bfloat16
@@ -73,8 +74,7 @@ class Attention(Mixer):
                                     cache_view.page_table, cache_view.k_pages, cache_view.v_pages, self.H, self.Hkv,
                                     self.hd, cache_view.page_size)
             out = attention_kernels.attention(q, cache_view, ctx, self.H, self.Hkv, self.hd, self.scale, self.window)
-            linear.linear(out, self.w_o, self.runtime.act_dtype, residual=residual)
-            return
+            return self._project(out, residual, emit)
         qkv = linear.linear(h, self.w_qkv, self.runtime.act_dtype)
         if self.position is not None and tables is None:
             q = qkv[:, :self.H * self.hd].unflatten(1, (self.H, self.hd))
@@ -91,4 +91,11 @@ class Attention(Mixer):
             ops.rope_kv_write(qkv, cos, sin, ctx.tok_pos, ctx.tok_seq, ctx.slots, cache_view.page_table,
                               cache_view.k_pages, cache_view.v_pages, self.H, self.Hkv, self.hd, cache_view.page_size)
         out = attention_kernels.attention(qkv, cache_view, ctx, self.H, self.Hkv, self.hd, self.scale, self.window)
-        linear.linear(out, self.w_o, self.runtime.act_dtype, residual=residual)
+        return self._project(out, residual, emit)
+
+    def _project(self, out, residual, emit):
+        """Output projection added into the residual; with `emit`, the next norm's rows (or None)."""
+        if emit is None:
+            linear.linear(out, self.w_o, self.runtime.act_dtype, residual=residual)
+            return None
+        return linear.linear(out, self.w_o, self.runtime.act_dtype, residual=residual, emit=emit)[1]

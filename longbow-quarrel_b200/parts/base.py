@@ -90,6 +90,12 @@ class StateNeed:
 
 
 class Mixer(Part):
+    # A part that sets this takes unfinished rows of a norm (kernels.ops.NormedRows) as `h` and takes
+    # the keyword `emit`: (gain, eps) of the RMS norm that reads the residual next.  With `emit` it
+    # returns that norm's rows, made in the epilogue of its last product, or None where it cannot.
+    # A part that leaves it False is always given finished rows and its return value is not read.
+    folds_norm = False
+
     def cache_need(self) -> KVNeed | StateNeed | None:
         return None
 
@@ -100,6 +106,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    folds_norm = False        # as for Mixer
+
     def forward(self, h: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
         """Read the normed rows h [T, D]; add the output to residual [T, D] (float32)."""
         raise NotImplementedError
@@ -109,6 +117,11 @@ class Norm(Part):
     def forward(self, x: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
         """Normalise rows of the float32 stream; returns the activation dtype."""
         raise NotImplementedError
+
+    def foldable(self, n_rows: int) -> tuple | None:
+        """(gain, eps) when this norm is x / rms(x) * gain and the products on either side of it can
+        do its work for `n_rows` rows (see Mixer.folds_norm); None otherwise."""
+        return None
 
 
 class PositionEncoding(Part):

@@ -39,8 +39,24 @@ class PreNormBlock(Part):
         for part in self.parts():
             part.load({n: tensors[n] for n in part.weights()})
 
-    def forward(self, x, ctx: StepContext, cache_view, writes_cache: bool = True):
-        h = self.norm1.forward(x)
-        self.mixer.forward(h, ctx, cache_view, x, writes_cache)
-        h = self.norm2.forward(x)
+    folds_norm = True
+
+    def input_norm(self, n_rows: int):
+        """(gain, eps) when the layer ahead of this one may leave this layer's first norm to the
+        products on either side of it; None otherwise."""
+        return self.norm1.foldable(n_rows) if self.mixer.folds_norm else None
+
+    def forward(self, x, ctx: StepContext, cache_view, writes_cache: bool = True, normed=None, emit=None):
+        """`normed`: the rows of norm1, when the layer ahead made them (see input_norm).  `emit`: the
+        input_norm() of the layer that follows.  Returns that layer's rows, or None."""
+        n_rows = x.shape[0]
+        h = normed if normed is not None else self.norm1.forward(x)
+        fold2 = self.norm2.foldable(n_rows) if (self.mixer.folds_norm and self.ffn.folds_norm) else None
+        h = self.mixer.forward(h, ctx, cache_view, x, writes_cache, emit=fold2) if fold2 is not None \
+            else self.mixer.forward(h, ctx, cache_view, x, writes_cache)
+        if fold2 is None or h is None:
+            h = self.norm2.forward(x)
+        if emit is not None and self.ffn.folds_norm:
+            return self.ffn.forward(h, ctx, x, emit=emit)
         self.ffn.forward(h, ctx, x)
+        return None

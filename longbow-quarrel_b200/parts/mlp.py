@@ -16,6 +16,7 @@ DEFAULT_NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "do
 @register_part("ffn", "gated_mlp")
 class GatedMLP(FeedForward):
     graph_safe = True
+    folds_norm = True
 
     def __init__(self, runtime: Runtime, hidden_size: int, intermediate_size: int, activation: str = "silu",
                  names: dict | None = None):
@@ -44,6 +45,9 @@ class GatedMLP(FeedForward):
         self.w_gu = linear.LinearWeight(stacked)
         self.w_down = linear.LinearWeight(tensors[n["down"]])
 
-    def forward(self, h, ctx: StepContext, residual):
+    def forward(self, h, ctx: StepContext, residual, emit=None):
         act = linear.linear_swiglu(h, self.w_gu, self.block)
-        linear.linear(act, self.w_down, self.runtime.act_dtype, residual=residual)
+        if emit is None:
+            linear.linear(act, self.w_down, self.runtime.act_dtype, residual=residual)
+            return None
+        return linear.linear(act, self.w_down, self.runtime.act_dtype, residual=residual, emit=emit)[1]

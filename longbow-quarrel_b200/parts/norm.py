@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels import ops
+from ..kernels import linear, ops
 from ..weights.spec import WeightSpec
 from .base import Norm, Runtime
 from .registry import register_part
@@ -27,3 +27,8 @@ class RMSNorm(Norm):
 
     def forward(self, x, rows=None):
         return ops.rmsnorm(x, self.gain, self.eps, self.runtime.act_dtype, rows)
+
+    def foldable(self, n_rows):
+        if self.gain is None or not linear.can_defer_norm(n_rows, self.size, self.runtime.act_dtype):
+            return None
+        return self.gain, self.eps

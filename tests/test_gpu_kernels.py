@@ -251,6 +251,73 @@ def test_gemm_skinny_is_independent_of_other_rows():
         assert torch.equal(ops.gemm_skinny(a[r:r + 1].contiguous(), w, ops.EPI_F32)[0], full[r])
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (7, 104, 200), (16, 4104, 328), (8, 4096, 4096)])
+def test_gemm_skinny_folds_the_norm_that_follows(M, N, K):
+    """The residual epilogue also leaves the next RMS norm's rows (residual * gain, sums of
+    squares); a product that reads them finishes the norm.  Against norm and products done apart."""
+    ops = _ops()
+    from longbow_quarrel_b200.kernels.linear import interleave_gate_up
+    a, w = _rand((M, K), torch.bfloat16, 50), _rand((N, K), torch.bfloat16, 51, 0.2)
+    res = _rand((M, N), torch.float32, 52, 3.0)
+    res[-1] *= 40.0                                        # rows of very different size
+    gain = 1 + 0.1 * _rand((N,), torch.float32, 53)
+    eps = 1e-5
+    expect = res.double().cpu() + a.float().double().cpu() @ w.float().double().cpu().T
+    out, rows = ops.gemm_skinny(a, w, ops.EPI_RESID, residual=res, emit=(gain, eps))
+    assert out.data_ptr() == res.data_ptr()
+    _close(out, expect, _acc_tol(K))
+    new = out.double().cpu()
+    _close(rows.data, new * gain.double().cpu(), 1e-6, BF16_ULP)
+    assert rows.sums.shape == (M, -(-N // 16))
+    sums = rows.sums.double().cpu().sum(1)
+    assert float(((sums - new.pow(2).sum(1)).abs() / new.pow(2).sum(1)).max()) < 1e-5
+    # the rows as a norm kernel would have left them, from the same bfloat16 values
+    rstd = torch.rsqrt(new.pow(2).mean(1, keepdim=True) + eps)
+    normed = rows.data.float().double().cpu() * rstd
+    _close(rows.finish(), normed, 1e-6, BF16_ULP)
+    N2 = 176
+    w2 = _rand((N2, N), torch.bfloat16, 54, 0.2)
+    ref2 = normed @ w2.float().double().cpu().T
+    _close(ops.gemm_skinny(rows, w2, ops.EPI_F32), ref2, _acc_tol(N) + 1e-6)
+    _close(ops.gemm_skinny(rows, w2, ops.EPI_BF16), ref2, _acc_tol(N) + 1e-6, BF16_ULP)
+    res2 = _rand((M, N2), torch.float32, 55)
+    expect2 = res2.double().cpu() + ref2
+    _close(ops.gemm_skinny(rows, w2, ops.EPI_RESID, residual=res2), expect2, _acc_tol(N) + 1e-6)
+    wg, wu = _rand((N2, N), torch.bfloat16, 56, 0.1), _rand((N2, N), torch.bfloat16, 57, 0.1)
+    g, u = normed @ wg.float().double().cpu().T, normed @ wu.float().double().cpu().T
+    _close(ops.gemm_skinny(rows, interleave_gate_up(wg, wu), ops.EPI_SWIGLU), u * (g / (1 + torch.exp(-g))), 1e-4, BF16_ULP)
+    # a row's result does not depend on the other rows
+    one = ops.NormedRows(rows.data[-1:].contiguous(), rows.sums[-1:].contiguous(), eps)
+    assert torch.equal(ops.gemm_skinny(one, w2, ops.EPI_F32)[0], ops.gemm_skinny(rows, w2, ops.EPI_F32)[-1])
+
+
+def test_gemm_skinny_qkv_finishes_a_folded_norm():
+    ops = _ops()
+    M, H, Hkv, hd, K = 5, 4, 2, 32, 200
+    lens = [70 + 5 * i for i in range(M)]
+    a = _rand((M, K), torch.bfloat16, 60)
+    sums = (_rand((M, 13), torch.float32, 61).abs() * 50 + 1).contiguous()
+    eps = 1e-6
+    w = _rand(((H + 2 * Hkv) * hd, K), torch.bfloat16, 62, 0.1)
+    tok_pos, tok_seq = [n - 1 for n in lens], list(range(M))
+    outs = []
+    for rows in (ops.NormedRows(a, sums, eps), ops.NormedRows(a, sums, eps).finish()):
+        case = PagedCase(lens, Hkv, hd, torch.bfloat16, seed=11)
+        q = ops.gemm_skinny_qkv(rows, w, None, None, _ints(tok_pos), _ints(tok_seq), case.slots, case.table,
+                                case.k_pages, case.v_pages, H, Hkv, hd, 64)
+        outs.append((q, case))
+    rstd = torch.rsqrt(sums.double().cpu().sum(1, keepdim=True) / K + eps)
+    full = ((a.float().double().cpu() * rstd) @ w.float().double().cpu().T).reshape(M, H + 2 * Hkv, hd)
+    q, case = outs[0]
+    _close(q.reshape(M, H, hd), full[:, :H], _acc_tol(K) + 1e-6, BF16_ULP)
+    for m in range(M):
+        page = int(case.table[case.slot_of[m], tok_pos[m] // 64])
+        _close(case.k_pages[page, :, tok_pos[m] % 64], full[m, H:H + Hkv], _acc_tol(K) + 1e-6, BF16_ULP)
+        _close(case.v_pages[page, :, tok_pos[m] % 64], full[m, H + Hkv:], _acc_tol(K) + 1e-6, BF16_ULP)
+    # finishing the rows first rounds them once more: close, not equal
+    _close(outs[1][0], outs[0][0], 3 * BF16_ULP, BF16_ULP)
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 16, 17, 33, 64])
 @pytest.mark.parametrize("N,K", [(16, 64), (100, 200), (4104, 4096), (250, 80), (1000, 14336), (33000, 512)])
 def test_gemm_stream(M, N, K):
