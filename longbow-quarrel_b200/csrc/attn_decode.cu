@@ -62,7 +62,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
                    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                    __nv_bfloat16* __restrict__ out, int H, int Hkv, int hd, int page_size, float scale, int window,
-                   int n_splits) {
+                   int n_splits, const char* next_w, unsigned next_piece) {
     constexpr int LD = HD + PAD;                   // shared-memory row length in elements
     constexpr int KD = HD / 16;                    // k16 steps over the head dimension
     constexpr int STAGE = 2 * TILE * LD;           // elements of one tile: K rows, then V rows
@@ -215,6 +215,12 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
         __syncwarp();       // every lane is done with the slot before a later copy refills it
     }
     cp_async_wait<0>();
+    if (next_w && threadIdx.x == 0) {
+        // The weights that the stream reads after this kernel: each block asks for one piece of their
+        // first bytes to be brought into L2 now that its own keys and values have arrived.
+        const size_t b = ((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(next_w + b * next_piece), "r"(next_piece) : "memory");
+    }
     // Row sums: add the four threads of a row.
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -327,9 +333,13 @@ template <int HD>
 int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages, const int* page_table, int pt_stride,
            const int* tok_pos, const int* tok_seq, const int* slots, float* part_o, float* part_ml, int* counters,
            void* out, int T, int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
-           cudaStream_t stream) {
+           const void* next_w, long next_bytes, cudaStream_t stream) {
     int G = H / Hkv, gtiles = (G + 15) / 16;
     dim3 grid(n_splits, Hkv * gtiles, T);
+    const long n_blocks = (long)grid.x * grid.y * grid.z;
+    long piece = (next_w && !((uintptr_t)next_w & 15)) ? next_bytes / n_blocks / 16 * 16 : 0;
+    if (piece > (1 << 20)) piece = 1 << 20;
+    if (piece <= 0) next_w = nullptr;
     constexpr size_t ring = (size_t)DW * RING * 2 * TILE * (HD + PAD) * 2;
     constexpr size_t merge = sizeof(float) * DW * 16 * (HD + 1) + sizeof(float) * 2 * DW * 16;
     constexpr size_t smem = ring > merge ? ring : merge;
@@ -341,7 +351,8 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
     }
     int rc = launch_pdl(attn_decode_kernel<HD>, grid, dim3(DW * 32), smem, stream, (const __nv_bfloat16*)q, q_stride,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots,
-        part_o, part_ml, counters, (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, n_splits);
+        part_o, part_ml, counters, (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, n_splits,
+        (const char*)next_w, (unsigned)piece);
     if (rc != LQ_OK || n_splits == 1 || counters != nullptr) return rc;
     return launch_pdl(attn_merge_kernel, dim3(T * H), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml,
                       (__nv_bfloat16*)out, hd, n_splits);
@@ -355,21 +366,33 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
 // block that finishes a (token, kv head) last merges the slices itself, without them a second
 // kernel does.  head_dim must be a multiple of 8 and at most 128; page_size a multiple of 16;
 // at most 32 slices.
-LQ_EXPORT int lq_attn_decode_merged(const void* q, int q_stride, const void* k_pages, const void* v_pages,
-                                    const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
-                                    const int* slots, float* part_o, float* part_ml, int* counters, void* out, int T,
-                                    int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
-                                    cudaStream_t stream) {
+// next_w, next_bytes (or null): weights that are read next on this stream; their first next_bytes
+// are asked into L2 as the blocks finish.
+LQ_EXPORT int lq_attn_decode_next(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+                                  const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
+                                  const int* slots, float* part_o, float* part_ml, int* counters, void* out, int T,
+                                  int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
+                                  const void* next_w, long next_bytes, cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
     if (hd % 8 || hd > 128 || hd <= 0 || H % Hkv || page_size % TILE || n_splits < 1 || q_stride % 8) return LQ_BAD_SIZE;
     if (n_splits > MAX_SPLITS) return LQ_BAD_SIZE;
     if (n_splits > 1 && (!part_o || !part_ml)) return LQ_BAD_SIZE;
 #define LQ_GO(HD) return launch<HD>(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, \
-                                    part_o, part_ml, counters, out, T, H, Hkv, hd, page_size, scale, window, n_splits, stream)
+                                    part_o, part_ml, counters, out, T, H, Hkv, hd, page_size, scale, window, n_splits, \
+                                    next_w, next_bytes, stream)
     if (hd <= 32) LQ_GO(32);
     if (hd <= 64) LQ_GO(64);
     LQ_GO(128);
 #undef LQ_GO
+}
+
+LQ_EXPORT int lq_attn_decode_merged(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+                                    const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
+                                    const int* slots, float* part_o, float* part_ml, int* counters, void* out, int T,
+                                    int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
+                                    cudaStream_t stream) {
+    return lq_attn_decode_next(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, part_o,
+                               part_ml, counters, out, T, H, Hkv, hd, page_size, scale, window, n_splits, nullptr, 0, stream);
 }
 
 // The same without counters: the slices are merged by a second kernel.

@@ -80,6 +80,15 @@ struct NormArgs {
     float* out_sums;          // [M, blocks of this launch]
 };
 
+// The weights that the stream reads next (of the product that follows this one): the last blocks of
+// this launch ask for their first bytes to be brought into L2, so that HBM stays busy while this
+// launch runs out and the next one starts from L2.  ptr null: nothing is asked for.
+struct NextWeights {
+    const char* ptr;
+    unsigned bytes_per_block;   // a multiple of 16
+    int first_block;            // blocks from this one on ask for one piece each
+};
+
 // Work of one warp on `UNROLL` chunks: the W rows of the block as mma A fragments, and (for
 // few tokens) the tokens' x as B fragments, all loaded before any of it is used.
 template <int MT>
@@ -91,7 +100,8 @@ struct Frags {
 template <int MT, int EPI>
 __global__ void __launch_bounds__(WARPS * 32, 2)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, void* Cout,
-                   const float* residual, int M, int N, int K, const QkvArgs qkv, const NormArgs norm) {
+                   const float* residual, int M, int N, int K, const QkvArgs qkv, const NormArgs norm,
+                   const NextWeights next) {
     __shared__ float red[WARPS][ROWS][MT * 8 + 1];
     __shared__ float row_scale[MT * 8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -144,6 +154,10 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
     // Weights are written by no kernel, so the first round of them is loaded before the kernel
     // ahead of this one is known to have finished; x and the output wait for pdl_wait().
     pdl_launch_dependents();
+    if (next.ptr && (int)blockIdx.x >= next.first_block && threadIdx.x == 0) {
+        const char* piece = next.ptr + (size_t)((int)blockIdx.x - next.first_block) * next.bytes_per_block;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(piece), "r"(next.bytes_per_block) : "memory");
+    }
     auto compute = [&](int c0, const Frags<MT>& f) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
@@ -280,18 +294,36 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
     }
 }
 
+int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    }
+    return n;
+}
+
 template <int MT>
 int launch_mt(const void* X, const void* W, void* C, const float* residual, int M, int N, int K, int epi,
-              cudaStream_t stream, const NormArgs norm, const QkvArgs qkv = QkvArgs{}) {
+              cudaStream_t stream, const NormArgs norm, const void* next_w, long next_bytes,
+              const QkvArgs qkv = QkvArgs{}) {
     dim3 grid((N + ROWS - 1) / ROWS), block(WARPS * 32);
+    // The blocks of the last wave (two a SM) share the bytes asked for.
+    NextWeights next{nullptr, 0u, 0};
+    if (next_w && next_bytes >= 16 && !((uintptr_t)next_w & 15)) {
+        const int askers = (int)grid.x < 2 * sm_count() ? (int)grid.x : 2 * sm_count();
+        const long piece = next_bytes / askers / 16 * 16;
+        if (piece > 0) next = NextWeights{(const char*)next_w, (unsigned)piece, (int)grid.x - askers};
+    }
     const __nv_bfloat16* x = (const __nv_bfloat16*)X;
     const __nv_bfloat16* w = (const __nv_bfloat16*)W;
     switch (epi) {
-        case EPI_BF16: return launch_pdl(gemm_skinny_kernel<MT, EPI_BF16>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv, norm);
-        case EPI_F32: return launch_pdl(gemm_skinny_kernel<MT, EPI_F32>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv, norm);
-        case EPI_RESID: return launch_pdl(gemm_skinny_kernel<MT, EPI_RESID>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv, norm);
-        case EPI_SWIGLU: return launch_pdl(gemm_skinny_kernel<MT, EPI_SWIGLU>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv, norm);
-        case EPI_QKV: return launch_pdl(gemm_skinny_kernel<MT, EPI_QKV>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv, norm);
+        case EPI_BF16: return launch_pdl(gemm_skinny_kernel<MT, EPI_BF16>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv, norm, next);
+        case EPI_F32: return launch_pdl(gemm_skinny_kernel<MT, EPI_F32>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv, norm, next);
+        case EPI_RESID: return launch_pdl(gemm_skinny_kernel<MT, EPI_RESID>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv, norm, next);
+        case EPI_SWIGLU: return launch_pdl(gemm_skinny_kernel<MT, EPI_SWIGLU>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv, norm, next);
+        case EPI_QKV: return launch_pdl(gemm_skinny_kernel<MT, EPI_QKV>, grid, block, 0, stream, x, w, C, residual, M, N, K, qkv, norm, next);
         default: return LQ_BAD_DTYPE;
     }
     return lq_launch_status();
@@ -303,11 +335,14 @@ int launch_mt(const void* X, const void* W, void* C, const float* residual, int 
 // interleaved gate and up rows (N % 16 == 0) and C is [M, N / 2].
 // in_sums (or null): x is (rows * gain) of an RMS norm whose 1 / rms is still to be applied;
 // in_sums [M, in_blocks] holds the rows' sums of squares, in_inv_width = 1 / width, in_eps the norm's eps.
+// next_w, next_bytes (or null): weights that are read next on this stream; their first next_bytes
+// are asked into L2 while this product runs out.
 // out_gain, out_x, out_sums (EPI_RESID only, or null): also write (new residual * out_gain) as
 // bfloat16 [M, N] and the sums of squares [M, lq_gemm_skinny_blocks(N)] for the product that follows.
 LQ_EXPORT int lq_gemm_skinny(const void* X, const void* W, void* C, const float* residual, int M, int N, int K,
                              int epi, const float* in_sums, int in_blocks, float in_inv_width, float in_eps,
-                             const float* out_gain, void* out_x, float* out_sums, cudaStream_t stream) {
+                             const float* out_gain, void* out_x, float* out_sums, const void* next_w, long next_bytes,
+                             cudaStream_t stream) {
     if (M <= 0 || N <= 0) return LQ_OK;
     if (M > 64 || K % 8 != 0 || K <= 0) return LQ_BAD_SIZE;
     if (epi == EPI_SWIGLU && N % 16 != 0) return LQ_BAD_SIZE;
@@ -318,10 +353,10 @@ LQ_EXPORT int lq_gemm_skinny(const void* X, const void* W, void* C, const float*
                         (__nv_bfloat16*)out_x, out_x ? out_sums : nullptr};
     int mt = (M + 7) / 8;
     switch (mt) {
-        case 1: return launch_mt<1>(X, W, C, residual, M, N, K, epi, stream, norm);
-        case 2: return launch_mt<2>(X, W, C, residual, M, N, K, epi, stream, norm);
-        case 3: case 4: return launch_mt<4>(X, W, C, residual, M, N, K, epi, stream, norm);
-        default: return launch_mt<8>(X, W, C, residual, M, N, K, epi, stream, norm);
+        case 1: return launch_mt<1>(X, W, C, residual, M, N, K, epi, stream, norm, next_w, next_bytes);
+        case 2: return launch_mt<2>(X, W, C, residual, M, N, K, epi, stream, norm, next_w, next_bytes);
+        case 3: case 4: return launch_mt<4>(X, W, C, residual, M, N, K, epi, stream, norm, next_w, next_bytes);
+        default: return launch_mt<8>(X, W, C, residual, M, N, K, epi, stream, norm, next_w, next_bytes);
     }
 }
 
@@ -337,7 +372,7 @@ LQ_EXPORT int lq_gemm_skinny_qkv(const void* X, const void* W, void* q_out, int 
                                  const float* sin_t, const int* tok_pos, const int* tok_seq, const int* slots,
                                  const int* page_table, int pt_stride, void* k_pages, void* v_pages, int H, int Hkv,
                                  int hd, int page_size, const float* in_sums, int in_blocks, float in_inv_width,
-                                 float in_eps, cudaStream_t stream) {
+                                 float in_eps, const void* next_w, long next_bytes, cudaStream_t stream) {
     if (M <= 0) return LQ_OK;
     if (M > 16 || K % 8 != 0 || K <= 0 || hd % 16 != 0 || H <= 0 || Hkv <= 0) return LQ_BAD_SIZE;
     if (in_sums && in_blocks <= 0) return LQ_BAD_SIZE;
@@ -345,6 +380,6 @@ LQ_EXPORT int lq_gemm_skinny_qkv(const void* X, const void* W, void* q_out, int 
               pt_stride, H, Hkv, hd, page_size};
     const NormArgs norm{in_sums, in_blocks, in_inv_width, in_eps, nullptr, nullptr, nullptr};
     const int N = (H + 2 * Hkv) * hd;
-    if (M <= 8) return launch_mt<1>(X, W, q_out, nullptr, M, N, K, EPI_QKV, stream, norm, a);
-    return launch_mt<2>(X, W, q_out, nullptr, M, N, K, EPI_QKV, stream, norm, a);
+    if (M <= 8) return launch_mt<1>(X, W, q_out, nullptr, M, N, K, EPI_QKV, stream, norm, next_w, next_bytes, a);
+    return launch_mt<2>(X, W, q_out, nullptr, M, N, K, EPI_QKV, stream, norm, next_w, next_bytes, a);
 }

@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import torch
 
+from ..kernels import linear
 from ..parts.base import Runtime, StepContext
 from ..parts.registry import make_part
 from ..parts.spec import ModelSpec, PartSpec
@@ -17,6 +18,7 @@ class Model:
         self.blocks = [make_part("block", PartSpec(layer.arrangement), runtime, layer=layer) for layer in spec.layers]
         self.final_norm = make_part("norm", spec.final_norm, runtime)
         self.head = make_part("head", spec.head, runtime)
+        self._order_known = False
         for n, entry in enumerate(spec.schedule):
             if not 0 <= entry.layer < len(self.blocks):
                 raise ValueError(f"schedule entry {n} names layer {entry.layer}; the model has {len(self.blocks)}")
@@ -83,6 +85,11 @@ class Model:
     def forward(self, ctx: StepContext, cache) -> torch.Tensor | None:
         """Run this step's rows through every scheduled layer; logits [wanted, vocab]
         (float32) at ctx.want_rows, or None when nothing is wanted."""
+        if not self._order_known:
+            # The first step also notes in which order the weights are read (it is the same in every step).
+            self._order_known = True
+            with linear.recording():
+                return self.forward(ctx, cache)
         x = self.embedding.forward(ctx.tokens)
         schedule = self.spec.schedule
         normed = None           # rows of the next layer's first norm, when this layer's last product made them

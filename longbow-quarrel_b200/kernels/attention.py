@@ -17,8 +17,9 @@ def decode_splits(n_tokens: int, Hkv: int, group_tiles: int, max_kv: int) -> int
     return max(1, min(RESIDENT_BLOCKS // blocks, MAX_SPLITS, -(-max_kv // KEYS_PER_SPLIT)))
 
 
-def attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window):
-    """Rows of qkv hold q in their left H*hd columns.  Returns [T, H*hd]."""
+def attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w=None):
+    """Rows of qkv hold q in their left H*hd columns.  Returns [T, H*hd].  next_w: the weights the
+    stream reads after the attention (the decode kernel asks for their first bytes as it ends)."""
     fast = qkv.dtype == torch.bfloat16 and hd <= 128 and hd % 8 == 0 and qkv.stride(0) % 8 == 0
     if (fast and not ctx.decode and hd == 128 and cache_view.page_size == 64 and USE_TC_PREFILL
             and getattr(ctx, "query_blocks128", None) is not None):
@@ -30,6 +31,7 @@ def attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window):
     if fast and ctx.decode:
         n_splits = decode_splits(ctx.T, Hkv, -(-(H // Hkv) // 16), ctx.max_kv)
         return ops.attn_decode(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.tok_pos,
-                               ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window, n_splits)
+                               ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window, n_splits,
+                               next_w=next_w)
     return ops.attention_plain(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.tok_pos,
                                ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window)

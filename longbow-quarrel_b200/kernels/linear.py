@@ -23,6 +23,40 @@ class LinearWeight:
         self.tensor = tensor.contiguous()
         self.N, self.K = self.tensor.shape
         self.prepared: dict = {}
+        # The weight that the same stream reads after this one in a step (see `recording`): the
+        # kernels for few rows ask for its first bytes while they run out.
+        self.next: LinearWeight | None = None
+
+    @property
+    def next_tensor(self):
+        return self.next.tensor if self.next is not None else None
+
+
+_log: list | None = None
+
+
+class recording:
+    """While active, the products note their weights in the order of use; at the end every weight
+    learns which one follows it (the last one is followed by the first: the next step)."""
+
+    def __enter__(self):
+        global _log
+        _log = []
+        return self
+
+    def __exit__(self, *exc):
+        global _log
+        log, _log = _log, None
+        if exc[0] is None and len(log) > 1:
+            for w, after in zip(log, log[1:] + log[:1]):
+                if after is not w:
+                    w.next = after
+        return False
+
+
+def note(weight: "LinearWeight") -> None:
+    if _log is not None:
+        _log.append(weight)
 
 
 FOLD_NORMS = os.environ.get("LQ_FOLD_NORMS", "1") != "0"      # 0: every norm runs as a kernel of its own
@@ -48,6 +82,7 @@ def linear(a, weight: LinearWeight, out_dtype: torch.dtype, residual: torch.Tens
     `a` may be ops.NormedRows.  With emit = (gain, eps) of the RMS norm that reads the residual
     next, returns (residual, rows) where rows are that norm's ops.NormedRows, or None when the
     kernel for this shape does not make them."""
+    note(weight)
     if a.dtype == torch.bfloat16 and weight.tensor.dtype == torch.bfloat16:
         from . import tensorcore
         out = tensorcore.linear_bf16(a, weight, out_dtype, residual, emit)
@@ -76,6 +111,7 @@ def linear_swiglu(a: torch.Tensor, weight: LinearWeight, block: int) -> torch.Te
         from . import tensorcore
         out = tensorcore.linear_swiglu_bf16(a, weight)
         if out is not None:
+            note(weight)
             return out
     gu = linear(a, weight, a.dtype)
     return ops.swiglu(gu, block)

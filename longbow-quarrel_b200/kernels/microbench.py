@@ -84,6 +84,31 @@ def bench_gemm(kind: str, args) -> dict:
             "gbs": nbytes / ms / 1e6, "tflops": flops / ms / 1e9, "weight_copies": n}
 
 
+def bench_chain(args) -> dict:
+    """The four products of a decoder layer one after another (no attention between them), over
+    several layers' weights, each product naming the weights that follow it."""
+    from . import ops
+    from .linear import interleave_gate_up
+    M, D, F, dev = args.m, 4096, 14336, "cuda"
+    L = max(2, args.layers)
+    mk = lambda n, k: torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.02
+    layers = [dict(qkv=mk(6144, D), o=mk(D, D), gu=interleave_gate_up(mk(F, D), mk(F, D)), down=mk(D, F)) for _ in range(L)]
+    x = torch.randn(M, D, device=dev, dtype=torch.bfloat16)
+    res = torch.zeros(M, D, device=dev, dtype=torch.float32)
+
+    def run(i):
+        for j, w in enumerate(layers):
+            nxt = layers[(j + 1) % L]
+            q = ops.gemm_skinny(x, w["qkv"], ops.EPI_BF16, next_w=w["o"])
+            ops.gemm_skinny(q[:, :D].contiguous() if False else x, w["o"], ops.EPI_RESID, res, next_w=w["gu"])
+            act = ops.gemm_skinny(x, w["gu"], ops.EPI_SWIGLU, next_w=w["down"])
+            ops.gemm_skinny(act, w["down"], ops.EPI_RESID, res, next_w=nxt["qkv"])
+    ms = _time(run, args.iters, args.warmup)
+    nbytes = L * (6144 * D + D * D + 2 * F * D + D * F) * 2
+    return {"kernel": "chain of a layer's products", "M": M, "layers": L, "ms_per_layer": ms / L, "gbs": nbytes / ms / 1e6,
+            "prefetch_bytes": ops.PREFETCH_BYTES}
+
+
 def _paged(batch: int, context: int, Hkv: int, hd: int, dev):
     pages_per = -(-context // 64)
     n_pages = batch * pages_per
@@ -196,7 +221,7 @@ def bench_prefill(args) -> dict:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("what", choices=["gemm_skinny", "gemm_stream", "gemm_tc", "attn_decode", "attn_prefill", "attn_prefill_tc", "step",
+    ap.add_argument("what", choices=["gemm_skinny", "gemm_stream", "gemm_tc", "attn_decode", "attn_prefill", "attn_prefill_tc", "chain", "step",
                                      "prefill"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
@@ -219,6 +244,8 @@ def main(argv=None) -> int:
     GRAPH = not args.no_graph
     if args.what in ("gemm_skinny", "gemm_stream", "gemm_tc"):
         out = bench_gemm(args.what, args)
+    elif args.what == "chain":
+        out = bench_chain(args)
     elif args.what == "attn_decode":
         out = bench_attn_decode(args)
     elif args.what in ("attn_prefill", "attn_prefill_tc"):

@@ -7,7 +7,8 @@ fallback: a tensor on the CPU, or a library that cannot be built, is an error.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_float, c_int, c_void_p
+import os
+from ctypes import c_float, c_int, c_long, c_void_p
 
 import torch
 
@@ -235,14 +236,25 @@ def _norm_in(a):
     return a, None, 0, 0.0, 0.0
 
 
+PREFETCH_BYTES = int(float(os.environ.get("LQ_PREFETCH_MB", "8")) * (1 << 20))   # of the weights read next; 0: none
+
+
+def _next(next_w):
+    """(pointer, bytes) of the piece of the next weights to ask into L2."""
+    if next_w is None or PREFETCH_BYTES <= 0:
+        return None, 0
+    return _p(next_w), min(PREFETCH_BYTES, next_w.numel() * next_w.element_size())
+
+
 def gemm_skinny(a, w: torch.Tensor, epi: int, residual: torch.Tensor | None = None,
-                out: torch.Tensor | None = None, emit: tuple | None = None):
+                out: torch.Tensor | None = None, emit: tuple | None = None, next_w: torch.Tensor | None = None):
     """a [M <= 64, K] . w [N, K]^T, both bfloat16, streaming w once from memory.
     epi: EPI_BF16 / EPI_F32 store; EPI_RESID adds into the float32 `residual` in place;
     EPI_SWIGLU reads w as alternating blocks of 8 gate and 8 up rows and stores
     up * silu(gate) [M, N / 2].
     `a` may be NormedRows.  emit = (gain [N] float32, eps), with EPI_RESID only: also returns what the
-    RMS norm with that gain makes of the new residual, as NormedRows: (residual, rows)."""
+    RMS norm with that gain makes of the new residual, as NormedRows: (residual, rows).
+    next_w: the weights that the stream reads after these; their first bytes are asked into L2."""
     a, in_sums, in_blocks, in_inv, in_eps = _norm_in(a)
     M, K = a.shape
     N = w.shape[0]
@@ -268,14 +280,18 @@ def gemm_skinny(a, w: torch.Tensor, epi: int, residual: torch.Tensor | None = No
         rows = NormedRows(torch.empty((M, N), dtype=torch.bfloat16, device=a.device),
                           torch.empty((M, -(-N // 16)), dtype=torch.float32, device=a.device), eps)
     fn = _fn("gemm_skinny", "lq_gemm_skinny", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                               c_void_p, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p])
+                                               c_void_p, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+                                               c_long, c_void_p])
+    next_p, next_n = _next(next_w)
     _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), _p(residual), M, N, K, epi, in_sums, in_blocks, in_inv,
-              in_eps, _p(gain), _p(rows.data) if rows else None, _p(rows.sums) if rows else None, _stream()), "gemm_skinny")
+              in_eps, _p(gain), _p(rows.data) if rows else None, _p(rows.sums) if rows else None, next_p, next_n,
+              _stream()), "gemm_skinny")
     return (out, rows) if emit is not None else out
 
 
 def gemm_skinny_qkv(a, w: torch.Tensor, cos, sin, tok_pos, tok_seq, slots, page_table, k_pages, v_pages,
-                    H: int, Hkv: int, hd: int, page_size: int, out: torch.Tensor | None = None) -> torch.Tensor:
+                    H: int, Hkv: int, hd: int, page_size: int, out: torch.Tensor | None = None,
+                    next_w: torch.Tensor | None = None) -> torch.Tensor:
     """The q/k/v projection of at most 16 tokens with rotation and cache write in its epilogue:
     returns the rotated q [M, H*hd]; the rotated k and v are stored in each token's cache page.
     `a` may be NormedRows."""
@@ -291,10 +307,12 @@ def gemm_skinny_qkv(a, w: torch.Tensor, cos, sin, tok_pos, tok_seq, slots, page_
         out = torch.empty((M, H * hd), dtype=torch.bfloat16, device=a.device)
     fn = _fn("gemm_skinny", "lq_gemm_skinny_qkv", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                                    c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
-                                                   c_int, c_int, c_void_p, c_int, c_float, c_float, c_void_p])
+                                                   c_int, c_int, c_void_p, c_int, c_float, c_float, c_void_p, c_long,
+                                                   c_void_p])
+    next_p, next_n = _next(next_w)
     _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), M, K, _p(cos), _p(sin), _p(tok_pos), _p(tok_seq),
               _p(slots), _p(page_table), page_table.stride(0), _p(k_pages), _p(v_pages), H, Hkv, hd, page_size,
-              in_sums, in_blocks, in_inv, in_eps, _stream()), "gemm_skinny_qkv")
+              in_sums, in_blocks, in_inv, in_eps, next_p, next_n, _stream()), "gemm_skinny_qkv")
     return out
 
 
@@ -427,9 +445,11 @@ def attn_prefill_tc_status() -> int:
 
 def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq, slots, H: int, Hkv: int, hd: int,
                 page_size: int, scale: float, window: int | None, n_splits: int,
-                out: torch.Tensor | None = None, scratch: tuple | None = None) -> torch.Tensor:
+                out: torch.Tensor | None = None, scratch: tuple | None = None,
+                next_w: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of single query rows over the paged bfloat16 cache, the keys of each
-    sequence cut into n_splits slices that are merged afterwards."""
+    sequence cut into n_splits slices that are merged afterwards.  next_w: the weights that the
+    stream reads after this; their first bytes are asked into L2 as the blocks finish."""
     T = q.shape[0]
     if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
         raise KernelError("attn_decode takes bfloat16 queries and cache")
@@ -451,12 +471,14 @@ def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq,
         counters = _attn_counters(q.device)
         if n_counters > counters.numel():
             counters = None          # more (token, kv head) pairs than counters: merge with the second kernel
-    fn = _fn("attn_decode", "lq_attn_decode_merged", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                                      c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
+    fn = _fn("attn_decode", "lq_attn_decode_next", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                    c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_long,
+                                                    c_void_p])
+    next_p, next_n = _next(next_w)
     _check(fn(_p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0), _p(tok_pos),
               _p(tok_seq), _p(slots), _p(part_o), _p(part_ml), _p(counters), _p(out), T, H, Hkv, hd, page_size,
-              float(scale), int(window or 0), n_splits, _stream()), "attn_decode",
+              float(scale), int(window or 0), n_splits, next_p, next_n, _stream()), "attn_decode",
            2 if n_splits > 1 and counters is None else 1)
     return out
 

@@ -28,13 +28,14 @@ def linear_bf16(a, weight, out_dtype, residual, emit=None):
         return None
     fn = _decode_kernel(M) if M <= ops.SKINNY_MAX_ROWS else ops.gemm_tc
     a = _rows_for(fn, a)
+    more = {"next_w": weight.next_tensor} if fn is ops.gemm_skinny else {}
     if residual is not None:
         if emit is not None:
             if fn is ops.gemm_skinny:
-                return fn(a, weight.tensor, ops.EPI_RESID, residual, emit=emit)
+                return fn(a, weight.tensor, ops.EPI_RESID, residual, emit=emit, **more)
             return fn(a, weight.tensor, ops.EPI_RESID, residual), None
-        return fn(a, weight.tensor, ops.EPI_RESID, residual)
-    return fn(a, weight.tensor, ops.EPI_F32 if out_dtype == torch.float32 else ops.EPI_BF16)
+        return fn(a, weight.tensor, ops.EPI_RESID, residual, **more)
+    return fn(a, weight.tensor, ops.EPI_F32 if out_dtype == torch.float32 else ops.EPI_BF16, **more)
 
 
 def linear_swiglu_bf16(a, weight):
@@ -43,4 +44,5 @@ def linear_swiglu_bf16(a, weight):
     if K % 8:
         return None
     fn = _decode_kernel(M) if M <= ops.SKINNY_MAX_ROWS else ops.gemm_tc
-    return fn(_rows_for(fn, a), weight.tensor, ops.EPI_SWIGLU)
+    more = {"next_w": weight.next_tensor} if fn is ops.gemm_skinny else {}
+    return fn(_rows_for(fn, a), weight.tensor, ops.EPI_SWIGLU, **more)

@@ -70,10 +70,12 @@ class Attention(Mixer):
                 and (self.position is None or tables is not None)):
             # Few tokens: projection, rotation and cache write are one kernel.
             cos, sin = tables if tables is not None else (None, None)
+            linear.note(self.w_qkv)
             q = ops.gemm_skinny_qkv(h, self.w_qkv.tensor, cos, sin, ctx.tok_pos, ctx.tok_seq, ctx.slots,
                                     cache_view.page_table, cache_view.k_pages, cache_view.v_pages, self.H, self.Hkv,
                                     self.hd, cache_view.page_size)
-            out = attention_kernels.attention(q, cache_view, ctx, self.H, self.Hkv, self.hd, self.scale, self.window)
+            out = attention_kernels.attention(q, cache_view, ctx, self.H, self.Hkv, self.hd, self.scale, self.window,
+                                              next_w=self.w_o.tensor)
             return self._project(out, residual, emit)
         qkv = linear.linear(h, self.w_qkv, self.runtime.act_dtype)
         if self.position is not None and tables is None:
@@ -90,7 +92,8 @@ class Attention(Mixer):
                 raise ValueError("attention: a layer with its own k and v must write its cache entry")
             ops.rope_kv_write(qkv, cos, sin, ctx.tok_pos, ctx.tok_seq, ctx.slots, cache_view.page_table,
                               cache_view.k_pages, cache_view.v_pages, self.H, self.Hkv, self.hd, cache_view.page_size)
-        out = attention_kernels.attention(qkv, cache_view, ctx, self.H, self.Hkv, self.hd, self.scale, self.window)
+        out = attention_kernels.attention(qkv, cache_view, ctx, self.H, self.Hkv, self.hd, self.scale, self.window,
+                                          next_w=self.w_o.tensor)
         return self._project(out, residual, emit)
 
     def _project(self, out, residual, emit):
