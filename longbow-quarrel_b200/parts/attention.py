@@ -54,6 +54,8 @@ class Attention(Mixer):
         if self.own_kv:
             out[n["k"]] = WeightSpec((self.Hkv * self.hd, self.D))
             out[n["v"]] = WeightSpec((self.Hkv * self.hd, self.D))
+        if self.position is not None:
+            out.update(self.position.weights())        # a position encoding may have tensors of its own
         return out
 
     def load(self, tensors):
@@ -61,6 +63,8 @@ class Attention(Mixer):
         rows = [tensors[n["q"]]] + ([tensors[n["k"]], tensors[n["v"]]] if self.own_kv else [])
         self.w_qkv = linear.LinearWeight(torch.cat(rows, dim=0))
         self.w_o = linear.LinearWeight(tensors[n["o"]])
+        if self.position is not None and self.position.weights():
+            self.position.load({name: tensors[name] for name in self.position.weights()})
 
     def forward(self, h, ctx: StepContext, cache_view, residual, writes_cache: bool = True, emit=None):
         store = self.own_kv and writes_cache

@@ -231,6 +231,149 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     assert not np.allclose(whole[1], whole[0])
 
 
+# ------------------------------------------------------------------ other kinds of parts, defined here
+def test_a_routed_feed_forward_and_a_learned_position_encoding_from_a_test():
+    """A feed-forward that routes each token to one of three small experts (router in 32-bit) and a
+    position encoding with a tensor of its own that shifts q and k in place (no cos/sin tables, so the
+    attention takes its unfused path) are defined here, registered and put into a model whose two
+    layers differ; whole prompts, token-by-token decoding and a batch agree with each other and with
+    the same computation spelled out with the plain functions."""
+    from dataclasses import dataclass
+
+    from longbow_quarrel_b200.config import register_architecture
+    from longbow_quarrel_b200.engine import Engine
+    from longbow_quarrel_b200.parts import (FeedForward, LayerSpec, ModelSpec, PartSpec, PositionEncoding,
+                                            ScheduleEntry, register_part)
+    from longbow_quarrel_b200.weights import WeightSpec
+
+    D, H, Hkv, hd, F, V, E, P = 48, 3, 1, 16, 40, 90, 3, 64
+
+    @register_part("ffn", "toy_routed")
+    class Routed(FeedForward):
+        """y = gate-free expert e(x) = relu(x We1^T) We2^T for the one expert with the largest router logit."""
+
+        def __init__(self, runtime, hidden_size, inner, experts):
+            self.runtime, self.D, self.F, self.E = runtime, hidden_size, inner, experts
+
+        def weights(self):
+            out = {"router": WeightSpec((self.E, self.D))}
+            for e in range(self.E):
+                out[f"e{e}.w1"] = WeightSpec((self.F, self.D))
+                out[f"e{e}.w2"] = WeightSpec((self.D, self.F))
+            return out
+
+        def load(self, tensors):
+            self.t = {k: v.float() for k, v in tensors.items()}
+
+        def forward(self, h, ctx, residual):
+            x = h.float()
+            choice = (x @ self.t["router"].T).argmax(dim=-1)
+            for e in range(self.E):
+                rows = (choice == e).nonzero().squeeze(1)
+                if rows.numel():
+                    y = torch.relu(x[rows] @ self.t[f"e{e}.w1"].T) @ self.t[f"e{e}.w2"].T
+                    residual.index_add_(0, rows, y)
+
+    @register_part("position", "toy_learned_shift")
+    class LearnedShift(PositionEncoding):
+        """q and k of position p get table[p] added (one vector per position, shared by the heads)."""
+
+        def __init__(self, runtime, head_dim, positions):
+            self.runtime, self.hd, self.P, self.table = runtime, head_dim, positions, None
+
+        def weights(self):
+            return {"pos_table": WeightSpec((self.P, self.hd))}
+
+        def load(self, tensors):
+            self.table = tensors["pos_table"]
+
+        def apply(self, q, k, positions):
+            shift = self.table[positions.long()].to(q.dtype).unsqueeze(1)
+            q += shift
+            if k is not None:
+                k += shift
+
+    @dataclass(frozen=True)
+    class Cfg:
+        architectures: tuple = ("ToyRoutedLM",)
+
+    def describe(cfg):
+        norm = lambda name: PartSpec("rms_norm", {"size": D, "eps": 1e-5, "name": name})  # noqa: E731
+        attn = lambda position: PartSpec("attention", {"hidden_size": D, "n_heads": H, "n_kv_heads": Hkv,  # noqa: E731
+                                                       "head_dim": hd, "scale": hd ** -0.5, "position": position})
+        layers = (LayerSpec("l0.", attn(PartSpec("toy_learned_shift", {"head_dim": hd, "positions": P})),
+                            PartSpec("toy_routed", {"hidden_size": D, "inner": F, "experts": E}), norm("n1"), norm("n2")),
+                  LayerSpec("l1.", attn(PartSpec("rope", {"head_dim": hd, "theta": 1e4})),
+                            PartSpec("gated_mlp", {"hidden_size": D, "intermediate_size": 64}), norm("n1"), norm("n2")))
+        return ModelSpec(name="ToyRoutedLM", hidden_size=D, vocab_size=V,
+                         embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": D, "name": "emb"}),
+                         layers=layers, schedule=(ScheduleEntry(0, 0), ScheduleEntry(1, 1)), final_norm=norm("fn"),
+                         head=PartSpec("linear_head", {"vocab_size": V, "hidden_size": D, "name": "head",
+                                                       "tied_to": "emb", "tied": True}),
+                         max_positions=P)
+
+    register_architecture("ToyRoutedLM", lambda d: Cfg(), describe)
+    eng = Engine.from_config({"architectures": ["ToyRoutedLM"]}, seed=9, dtype="float32", max_tokens=512, gain_std=0.1)
+    table = eng.model.weight_table()
+    assert "l0.pos_table" in table and "l0.router" in table and "l0.e2.w2" in table and "l1.gate_proj.weight" in table
+    toks = [[int(t) for t in np.random.default_rng(i).integers(0, V, n)] for i, n in enumerate((23, 9))]
+
+    # the same computation with the plain functions
+    b0, b1 = eng.model.blocks
+    dd = lambda t: t.double().cpu()  # noqa: E731
+    emb = dd(eng.model.embedding.table)
+
+    def plain(tokens):
+        T = len(tokens)
+        pos = np.arange(T)
+        x = emb[tokens]
+        for blk in (b0, b1):
+            m = blk.mixer
+            w = dd(m.w_qkv.tensor)
+            n = pl.rms_norm(x, dd(blk.norm1.gain), 1e-5)
+            q = pl.linear(n, w[:H * hd]).reshape(T, H, hd)
+            k = pl.linear(n, w[H * hd:(H + Hkv) * hd]).reshape(T, Hkv, hd)
+            v = pl.linear(n, w[(H + Hkv) * hd:]).reshape(T, Hkv, hd)
+            if blk is b0:
+                shift = dd(m.position.table)[pos][:, None, :]
+                q, k = q + shift, k + shift
+            else:
+                f = pl.rope_frequencies(hd, 1e4, None)
+                q, k = pl.rope(q, pos, f), pl.rope(k, pos, f)
+            x = x + pl.linear(pl.attention(q, k, v, hd ** -0.5, None).reshape(T, H * hd), dd(m.w_o.tensor))
+            n = pl.rms_norm(x, dd(blk.norm2.gain), 1e-5)
+            if blk is b0:
+                t = {kk: dd(vv) for kk, vv in blk.ffn.t.items()}
+                choice = (n @ t["router"].T).argmax(-1)
+                y = torch.zeros_like(x)
+                for r in range(T):
+                    e = int(choice[r])
+                    y[r] = torch.relu(n[r] @ t[f"e{e}.w1"].T) @ t[f"e{e}.w2"].T
+                x = x + y
+                assert len(set(choice.tolist())) > 1          # the router does route
+            else:
+                gu = dd(blk.ffn.w_gu.tensor)
+                Fi = gu.shape[0] // 2
+                x = x + pl.linear(pl.swiglu(pl.linear(n, gu[:Fi]), pl.linear(n, gu[Fi:])), dd(blk.ffn.w_down.tensor))
+        return pl.linear(pl.rms_norm(x, dd(eng.model.final_norm.gain), 1e-5), emb).numpy()
+
+    want = [plain(t) for t in toks]
+    s = [eng.new_sequence() for _ in toks]
+    whole = eng.step([(s[0], toks[0]), (s[1], toks[1])], want=[list(range(23)), list(range(9))]).cpu().numpy()
+    assert rel_err(whole[:23], want[0]) < 1e-4 and rel_err(whole[23:], want[1]) < 1e-4
+    for slot in s:
+        eng.end_sequence(slot)
+    # prompts cut short, the rest token by token, the shorter request ending earlier
+    s = [eng.new_sequence() for _ in toks]
+    eng.step([(s[0], toks[0][:15]), (s[1], toks[1][:4])], want=[[], []])
+    for i in range(8):
+        entries = [(s[0], [toks[0][15 + i]])] + ([(s[1], [toks[1][4 + i]])] if i < 5 else [])
+        out = eng.step(entries).cpu().numpy()
+        assert rel_err(out[0], want[0][15 + i]) < 1e-4
+        if i < 5:
+            assert rel_err(out[1], want[1][4 + i]) < 1e-4
+
+
 # ------------------------------------------------------------------ the order of layers is data
 def test_a_layer_run_twice_and_a_layer_that_reads_anothers_cache():
     """Schedule: layer 0 (cache entry 0), layer 1 reading entry 0 without keys and values of its
