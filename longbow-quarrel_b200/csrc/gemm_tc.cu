@@ -15,6 +15,11 @@
 // Epilogues: bfloat16 store; float32 store; float32 residual add in place; SwiGLU over
 // weight rows interleaved in blocks of 8 (8 gate rows, then their 8 up rows).
 //
+// Few rows and a narrow weight give fewer tiles than SMs, and the product is then bound by
+// reading W: the contraction is cut into `splits` ranges, a block's piece of work is (tile, range),
+// the pieces' float32 results go to scratch memory and a second kernel adds them in the order of K
+// and applies the epilogue.  With W as the N side, one tcgen05.mma consumes 8 KB of W.
+//
 // Reference counterpart: the per-row linear_f16 kernels and the library GEMM of
 // internal/device/metal.go:886-964; its CUDA path calls cublasSgemmEx (internal/device/cuda.go:293-318).
 #include "common.cuh"
@@ -194,13 +199,15 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], void* Cout,
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(N_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               void* Cout, const float* residual, int M, int N, int K) {
+               void* Cout, const float* residual, int M, int N, int K, int splits) {
     extern __shared__ uint8_t smem_raw[];
     using S = Smem<BN, STAGES>;
     S& sm = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
-    const int total = m_tiles * n_tiles;
+    // A piece of work is (tile, range of K): piece = tile * splits + range.  With splits > 1 the kernel
+    // is the float32-store one and Cout the scratch [splits, M, N].
+    const int total = m_tiles * n_tiles * splits;
     const int n_kb = (K + BK - 1) / BK;
     constexpr uint32_t STAGE_BYTES = (BM + BN) * BK * 2;
     constexpr uint32_t TMEM_COLS = 2 * BN;             // two accumulators of BN float32 columns
@@ -228,9 +235,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+            for (int piece = blockIdx.x; piece < total && ok; piece += gridDim.x) {
+                const int tile = piece / splits, range = piece % splits;
                 const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
-                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                const int kb_lo = (int)((long)n_kb * range / splits), kb_hi = (int)((long)n_kb * (range + 1) / splits);
+                for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(smem_u32(&sm.empty[s]), ((it / STAGES) & 1) ^ 1)) { atomicExch(&g_status, 1); ok = false; break; }
                     const uint32_t full = smem_u32(&sm.full[s]);
@@ -254,19 +263,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             constexpr uint32_t idesc = instr_desc(BN);
             uint32_t it = 0, t = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++t) {
+            for (int piece = blockIdx.x; piece < total && ok; piece += gridDim.x, ++t) {
+                const int range = piece % splits;
+                const int kb_lo = (int)((long)n_kb * range / splits), kb_hi = (int)((long)n_kb * (range + 1) / splits);
                 const uint32_t acc = t & 1;
                 if (!mbar_wait(smem_u32(&sm.acc_empty[acc]), ((t >> 1) & 1) ^ 1)) { atomicExch(&g_status, 2); ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(smem_u32(&sm.full[s]), (it / STAGES) & 1)) { atomicExch(&g_status, 3); ok = false; break; }
                     tc_fence_after();
                     const uint64_t da = smem_desc(smem_u32(sm.a[s])), db = smem_desc(smem_u32(sm.b[s]));
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)   // 32 bytes further along K: 2 units of 16 bytes
-                        tc_mma(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        tc_mma(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > kb_lo || k > 0) ? 1u : 0u);
                     tc_commit(smem_u32(&sm.empty[s]));      // the stage is free once these products have read it
                 }
                 if (ok) tc_commit(smem_u32(&sm.acc_full[acc]));
@@ -278,8 +289,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int quarter = warp & 3;                     // the 32 lanes of tensor memory this warp may read
         uint32_t t = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++t) {
+        for (int piece = blockIdx.x; piece < total && ok; piece += gridDim.x, ++t) {
+            const int tile = piece / splits, range = piece % splits;
             const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+            void* dst = splits > 1 ? (void*)((float*)Cout + (size_t)range * M * N) : Cout;
             const uint32_t acc = t & 1;
             if (!mbar_wait(smem_u32(&sm.acc_full[acc]), (t >> 1) & 1)) { atomicExch(&g_status, 4); ok = false; break; }
             tc_fence_after();
@@ -290,7 +303,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint32_t r[32];
                 tc_ld32(taddr + c * 32, r);
                 tc_wait_ld();
-                store_chunk<EPI>(r, Cout, residual, m, n0 + c * 32, M, N);
+                store_chunk<EPI>(r, dst, residual, m, n0 + c * 32, M, N);
             }
             tc_fence_before();
             __syncwarp();
@@ -303,6 +316,68 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
+}
+
+// ------------------------------------------------------------------ adding the ranges of K
+// part [splits, M, N] float32 -> the epilogue of their sum, the ranges added in their order.
+// One thread makes four neighbouring outputs.
+template <int EPI>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int splits, void* Cout,
+                                                            const float* residual, int M, int N) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int NO = EPI == EPI_SWIGLU ? N >> 1 : N;          // output columns
+    const int groups = (NO + 3) >> 2;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)M * groups) return;
+    const int m = (int)(idx / groups), c = (int)(idx % groups) * 4;
+    const size_t plane = (size_t)M * N;
+    auto sum4 = [&](int col, float (&v)[4]) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = 0.f;
+        const float* p = part + (size_t)m * N + col;
+        if (col + 4 <= N && (N & 3) == 0) {
+            for (int s = 0; s < splits; ++s) {
+                float4 q = __ldcg(reinterpret_cast<const float4*>(p + s * plane));
+                v[0] += q.x; v[1] += q.y; v[2] += q.z; v[3] += q.w;
+            }
+        } else {
+            for (int s = 0; s < splits; ++s)
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (col + i < N) v[i] += __ldcg(p + s * plane + i);
+        }
+    };
+    float v[4];
+    if (EPI == EPI_SWIGLU) {
+        // outputs c..c+3 lie in one block of 8: their gate columns and, 8 further, their up columns
+        const int gcol = (c >> 3) * 16 + (c & 7);
+        float u[4];
+        sum4(gcol, v);
+        sum4(gcol + 8, u);
+        __nv_bfloat16* dst = (__nv_bfloat16*)Cout + (size_t)m * NO + c;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (c + i < NO) dst[i] = __float2bfloat16_rn(u[i] * (v[i] / (1.0f + __expf(-v[i]))));
+        return;
+    }
+    sum4(c, v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (c + i >= N) break;
+        const size_t o = (size_t)m * N + c + i;
+        if (EPI == EPI_BF16) ((__nv_bfloat16*)Cout)[o] = __float2bfloat16_rn(v[i]);
+        else if (EPI == EPI_F32) ((float*)Cout)[o] = v[i];
+        else ((float*)Cout)[o] = residual[o] + v[i];
+    }
+}
+
+template <int EPI>
+int launch_reduce(const float* part, int splits, void* C, const float* residual, int M, int N, cudaStream_t stream) {
+    const int NO = EPI == EPI_SWIGLU ? N >> 1 : N;
+    const long threads = (long)M * ((NO + 3) >> 2);
+    return launch_pdl(splitk_reduce_kernel<EPI>, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, stream, part, splits,
+                      C, residual, M, N);
 }
 
 // ------------------------------------------------------------------ host side
@@ -338,7 +413,7 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) 
 
 template <int BN, int STAGES, int EPI>
 int launch_epi(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const float* residual, int M, int N, int K,
-               int n_sms, cudaStream_t stream) {
+               int n_sms, int splits, cudaStream_t stream) {
     constexpr size_t smem = sizeof(Smem<BN, STAGES>) + 1024;
     static bool configured = false;
     if (!configured) {
@@ -346,49 +421,91 @@ int launch_epi(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const floa
             return lq_launch_status();
         configured = true;
     }
-    int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * splits;
     int grid = tiles < n_sms ? tiles : n_sms;
-    return launch_pdl(gemm_tc_kernel<BN, STAGES, EPI>, dim3(grid), dim3(N_THREADS), smem, stream, ma, mb, C, residual, M, N, K);
+    return launch_pdl(gemm_tc_kernel<BN, STAGES, EPI>, dim3(grid), dim3(N_THREADS), smem, stream, ma, mb, C, residual, M, N, K,
+                      splits);
 }
 
 template <int BN, int STAGES>
 int launch_bn(const void* A, const void* W, void* C, const float* residual, int M, int N, int K, int epi, int n_sms,
-              cudaStream_t stream) {
+              int splits, float* scratch, cudaStream_t stream) {
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, M, K, BM);
     if (rc != LQ_OK) return rc;
     rc = make_map(&mb, W, N, K, BN);
     if (rc != LQ_OK) return rc;
+    if (splits > 1) {
+        rc = launch_epi<BN, STAGES, EPI_F32>(ma, mb, scratch, nullptr, M, N, K, n_sms, splits, stream);
+        if (rc != LQ_OK) return rc;
+        switch (epi) {
+            case EPI_BF16: return launch_reduce<EPI_BF16>(scratch, splits, C, residual, M, N, stream);
+            case EPI_F32: return launch_reduce<EPI_F32>(scratch, splits, C, residual, M, N, stream);
+            case EPI_RESID: return launch_reduce<EPI_RESID>(scratch, splits, C, residual, M, N, stream);
+            case EPI_SWIGLU: return launch_reduce<EPI_SWIGLU>(scratch, splits, C, residual, M, N, stream);
+        }
+        return LQ_BAD_DTYPE;
+    }
     switch (epi) {
-        case EPI_BF16: return launch_epi<BN, STAGES, EPI_BF16>(ma, mb, C, residual, M, N, K, n_sms, stream);
-        case EPI_F32: return launch_epi<BN, STAGES, EPI_F32>(ma, mb, C, residual, M, N, K, n_sms, stream);
-        case EPI_RESID: return launch_epi<BN, STAGES, EPI_RESID>(ma, mb, C, residual, M, N, K, n_sms, stream);
-        case EPI_SWIGLU: return launch_epi<BN, STAGES, EPI_SWIGLU>(ma, mb, C, residual, M, N, K, n_sms, stream);
+        case EPI_BF16: return launch_epi<BN, STAGES, EPI_BF16>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
+        case EPI_F32: return launch_epi<BN, STAGES, EPI_F32>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
+        case EPI_RESID: return launch_epi<BN, STAGES, EPI_RESID>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
+        case EPI_SWIGLU: return launch_epi<BN, STAGES, EPI_SWIGLU>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
     }
     return LQ_BAD_DTYPE;
 }
 
-}  // namespace
-
-// A [M, K] and W [N, K] bfloat16, row-major, 16-byte aligned, K % 8 == 0.
-// For EPI_SWIGLU, N counts the interleaved gate and up rows (N % 16 == 0) and C is [M, N / 2].
-LQ_EXPORT int lq_gemm_tc(const void* A, const void* W, void* C, const float* residual, int M, int N, int K, int epi,
-                         cudaStream_t stream) {
-    if (M <= 0 || N <= 0) return LQ_OK;
-    if (K <= 0 || K % 8 != 0) return LQ_BAD_SIZE;
-    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return LQ_BAD_SIZE;
-    if (epi == EPI_SWIGLU && N % 16 != 0) return LQ_BAD_SIZE;
-    if (epi == EPI_RESID && residual == nullptr) return LQ_BAD_SIZE;
+int sm_count() {
     static int n_sms = 0;
     if (!n_sms) {
         int dev = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
     }
+    return n_sms;
+}
+
+// Into how many ranges the contraction is cut: only when 128 x 256 tiles alone leave most SMs idle
+// (few rows, narrow weight); then as many as fill the SMs once, each at least MIN_KB steps of 64 long.
+constexpr int MIN_KB = 6;
+constexpr int MAX_SPLITS = 16;
+int plan_splits(int M, int N, int K) {
+    const long tiles = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
+    const int n_kb = (K + BK - 1) / BK;
+    if (tiles * 3 > sm_count() * 2) return 1;
+    long s = sm_count() / tiles;
+    if (s > n_kb / MIN_KB) s = n_kb / MIN_KB;
+    if (s > MAX_SPLITS) s = MAX_SPLITS;
+    return s < 1 ? 1 : (int)s;
+}
+
+}  // namespace
+
+// A [M, K] and W [N, K] bfloat16, row-major, 16-byte aligned, K % 8 == 0.
+// For EPI_SWIGLU, N counts the interleaved gate and up rows (N % 16 == 0) and C is [M, N / 2].
+// scratch: lq_gemm_tc_splits(M, N, K) * M * N floats when that number is above 1 (else unused).
+LQ_EXPORT int lq_gemm_tc(const void* A, const void* W, void* C, const float* residual, int M, int N, int K, int epi,
+                         float* scratch, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return LQ_OK;
+    if (K <= 0 || K % 8 != 0) return LQ_BAD_SIZE;
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return LQ_BAD_SIZE;
+    if (epi == EPI_SWIGLU && N % 16 != 0) return LQ_BAD_SIZE;
+    if (epi == EPI_RESID && residual == nullptr) return LQ_BAD_SIZE;
+    const int n_sms = sm_count();
+    const int splits = plan_splits(M, N, K);
+    if (splits > 1) {
+        if (!scratch || ((uintptr_t)scratch & 15)) return LQ_BAD_SIZE;
+        return launch_bn<256, 4>(A, W, C, residual, M, N, K, epi, n_sms, splits, scratch, stream);
+    }
     // Wide tiles when they still fill the GPU, narrower ones otherwise.
     long tiles256 = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
-    if (tiles256 >= n_sms) return launch_bn<256, 4>(A, W, C, residual, M, N, K, epi, n_sms, stream);
-    return launch_bn<128, 6>(A, W, C, residual, M, N, K, epi, n_sms, stream);
+    if (tiles256 >= n_sms) return launch_bn<256, 4>(A, W, C, residual, M, N, K, epi, n_sms, 1, nullptr, stream);
+    return launch_bn<128, 6>(A, W, C, residual, M, N, K, epi, n_sms, 1, nullptr, stream);
+}
+
+LQ_EXPORT int lq_gemm_tc_splits(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 1;
+    return plan_splits(M, N, K);
 }
 
 // The status word of the bounded waits: 0, or the code of the first wait that gave up

@@ -1,6 +1,6 @@
 """Timing single kernels and single steps, for roofline work and for profilers.
 
-    python -m longbow_quarrel_b200.kernels.microbench gemm_stream --m 8 --n 28672 --k 4096 --epi swiglu
+    python -m longbow_quarrel_b200.kernels.microbench gemm_tc --m 64 --n 28672 --k 4096 --epi swiglu
     python -m longbow_quarrel_b200.kernels.microbench gemm_tc --m 2048 --n 6144 --k 4096
     python -m longbow_quarrel_b200.kernels.microbench attn_decode --batch 8 --context 4096
     python -m longbow_quarrel_b200.kernels.microbench attn_prefill --tokens 2048
@@ -71,7 +71,7 @@ def bench_gemm(kind: str, args) -> dict:
     ws = [torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(n)]
     xs = [torch.randn(M, K, device=dev, dtype=torch.bfloat16) for _ in range(n)]
     res = torch.zeros(M, N, device=dev, dtype=torch.float32) if args.epi == "resid" else None
-    fn = {"gemm_skinny": ops.gemm_skinny, "gemm_stream": ops.gemm_stream, "gemm_tc": ops.gemm_tc}[kind]
+    fn = {"gemm_skinny": ops.gemm_skinny, "gemm_tc": ops.gemm_tc}[kind]
     outs = {}
 
     def run(i):
@@ -221,7 +221,7 @@ def bench_prefill(args) -> dict:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("what", choices=["gemm_skinny", "gemm_stream", "gemm_tc", "attn_decode", "attn_prefill", "attn_prefill_tc", "chain", "step",
+    ap.add_argument("what", choices=["gemm_skinny", "gemm_tc", "attn_decode", "attn_prefill", "attn_prefill_tc", "chain", "step",
                                      "prefill"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
@@ -242,7 +242,7 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
     global GRAPH
     GRAPH = not args.no_graph
-    if args.what in ("gemm_skinny", "gemm_stream", "gemm_tc"):
+    if args.what in ("gemm_skinny", "gemm_tc"):
         out = bench_gemm(args.what, args)
     elif args.what == "chain":
         out = bench_chain(args)

@@ -88,7 +88,7 @@ def _contig(t: torch.Tensor, what: str) -> torch.Tensor:
 def prepare(dtype: torch.dtype, verbose: bool = True) -> None:
     """Build and load the libraries a model of this dtype uses, before the first step."""
     from concurrent.futures import ThreadPoolExecutor
-    names = ["plain_kernels"] + (["gemm_skinny", "gemm_stream", "gemm_tc", "attn_decode", "attn_prefill", "attn_prefill_tc"]
+    names = ["plain_kernels"] + (["gemm_skinny", "gemm_tc", "attn_decode", "attn_prefill", "attn_prefill_tc"]
                                              if dtype == torch.bfloat16 else [])
     with ThreadPoolExecutor(max_workers=len(names)) as pool:
         list(pool.map(build.build, names))
@@ -198,8 +198,8 @@ def swiglu(gu: torch.Tensor, block: int = 0, out: torch.Tensor | None = None) ->
 
 # ------------------------------------------------------------------ bfloat16 tensor-core kernels
 EPI_BF16, EPI_F32, EPI_RESID, EPI_SWIGLU = 0, 1, 2, 3
-SKINNY_MAX_ROWS = 64          # most rows the two decode products take
-SKINNY_BEST_ROWS = 16         # up to here streaming W through registers beats the TMA stream
+SKINNY_MAX_ROWS = 64          # most rows gemm_skinny takes
+SKINNY_BEST_ROWS = 16         # up to here streaming W through registers beats the TMA-fed tcgen05 kernel
 
 
 class NormedRows:
@@ -316,56 +316,11 @@ def gemm_skinny_qkv(a, w: torch.Tensor, cos, sin, tok_pos, tok_seq, slots, page_
     return out
 
 
-def gemm_stream(a: torch.Tensor, w: torch.Tensor, epi: int, residual: torch.Tensor | None = None,
-                out: torch.Tensor | None = None) -> torch.Tensor:
-    """a [M <= 64, K] . w [N, K]^T, both bfloat16: W streamed once through all SMs by TMA in equal
-    shares, multiplied by tcgen05 with the tokens as the narrow side.  Epilogues as gemm_skinny."""
-    M, K = a.shape
-    N = w.shape[0]
-    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
-        raise KernelError("gemm_stream takes bfloat16 inputs")
-    if w.shape[1] != K:
-        raise KernelError(f"linear: input width {K} does not match weight width {w.shape[1]}")
-    if M > SKINNY_MAX_ROWS or K % 8:
-        raise KernelError(f"gemm_stream: {M} rows (at most {SKINNY_MAX_ROWS}) and width {K} (a multiple of 8)")
-    if epi == EPI_RESID:
-        if residual is None or residual.dtype != torch.float32 or tuple(residual.shape) != (M, N):
-            raise KernelError("linear: residual must be float32 [M, N]")
-        out = residual
-    elif out is None:
-        shape = (M, N // 2) if epi == EPI_SWIGLU else (M, N)
-        out = torch.empty(shape, dtype=torch.float32 if epi == EPI_F32 else torch.bfloat16, device=a.device)
-    fn = _fn("gemm_stream", "lq_gemm_stream", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                               c_void_p, c_void_p])
-    _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), _p(residual), M, N, K, epi,
-              _p(_lib_scratch("gemm_stream", "lq_gemm_stream_scratch_bytes", a.device)), _stream()), "gemm_stream")
-    return out
-
-
-def gemm_stream_status() -> int:
-    fn = build.load("gemm_stream").lq_gemm_stream_status
-    fn.restype = c_int
-    return int(fn())
-
-
-_scratch: dict = {}
-
-
-def _lib_scratch(lib: str, size_fn: str, device) -> torch.Tensor:
-    """Zeroed scratch of a kernel library, one buffer per device, made at first use.  Kernels
-    on one stream follow one another, so they can share it."""
-    key = (lib, device.type, device.index)
-    if key not in _scratch:
-        size = getattr(build.load(lib), size_fn)
-        size.restype = ctypes.c_long
-        _scratch[key] = torch.zeros(int(size()), dtype=torch.uint8, device=device)
-    return _scratch[key]
-
-
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, epi: int, residual: torch.Tensor | None = None,
             out: torch.Tensor | None = None) -> torch.Tensor:
     """a [M, K] . w [N, K]^T on the tcgen05 tensor cores (TMA-fed, float32 accumulation in
-    tensor memory), with the epilogues of gemm_skinny.  For many rows."""
+    tensor memory), with the epilogues of gemm_skinny.  For many rows; with few tiles (few rows
+    and a narrow weight) the contraction is cut into ranges that a second kernel adds."""
     M, K = a.shape
     N = w.shape[0]
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
@@ -381,8 +336,13 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, epi: int, residual: torch.Tensor |
     elif out is None:
         shape = (M, N // 2) if epi == EPI_SWIGLU else (M, N)
         out = torch.empty(shape, dtype=torch.float32 if epi == EPI_F32 else torch.bfloat16, device=a.device)
-    fn = _fn("gemm_tc", "lq_gemm_tc", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), _p(residual), M, N, K, epi, _stream()), "gemm_tc")
+    # Few tiles (few rows, narrow weight): the kernel cuts the contraction into ranges and adds them afterwards.
+    splits = int(_fn("gemm_tc", "lq_gemm_tc_splits", [c_int, c_int, c_int])(M, N, K))
+    scratch = torch.empty(splits * M * N, dtype=torch.float32, device=a.device) if splits > 1 else None
+    fn = _fn("gemm_tc", "lq_gemm_tc", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                       c_void_p])
+    _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), _p(residual), M, N, K, epi, _p(scratch), _stream()),
+           "gemm_tc", 2 if splits > 1 else 1)
     return out
 
 

@@ -1,11 +1,13 @@
 """Tensor-core paths of the bfloat16 matrix products: which kernel takes which shape.
 
-rows <= 16   gemm_skinny: W streamed through registers into mma.sync (fastest measured stream
-             of W: the loads of all warps keep more bytes in flight than one TMA unit does)
-rows <= 64   gemm_stream: W streamed by TMA in equal shares over all SMs into tcgen05 -- or
-             gemm_skinny where the weight is small enough that gemm_stream's fixed cost (filling
-             its ring, adding parked pieces: about 15 us) outweighs its better rate per row
-more rows    gemm_tc: 128 x 256 tiles, TMA ring, tcgen05 with two accumulators in tensor memory
+rows <= 16   gemm_skinny: W streamed through registers into mma.sync (the fastest stream of W
+             measured: 6.4-6.9 TB/s on the LM head)
+more rows    gemm_tc: 128 x 256 tiles, TMA ring, tcgen05 with two accumulators in tensor memory;
+             with few tiles (few rows, narrow weight) it cuts the contraction into ranges so that
+             every SM streams a share of W
+
+Measured on B200 at 64 rows, weights of 34 / 50 / 117 / 235 MB (us): gemm_tc 15 / 19 / 30 / 53,
+gemm_skinny 24 / 63 / 74 / 193; at 17 rows gemm_tc 13 / 15 / 26 / 52, gemm_skinny 11 / 19 / 31 / 64.
 """
 from __future__ import annotations
 
@@ -14,17 +16,8 @@ import torch
 from . import ops
 
 
-# Measured on B200 (us, gemm_skinny / gemm_stream), weights of 34, 50, 117 and 235 MB:
-#   32 rows: 12 / 23, 21 / 22, 33 / 40, 71 / 59        64 rows: 24 / 36, 63 / 31, 74 / 53, 193 / 73
-# Inside a decode step of 8 layers: 32 rows 2.15 ms with gemm_skinny for the three smaller weights against
-# 2.26 ms without; 64 rows 3.43 ms with it for the smallest against 3.38 ms without.
-SKINNY_BYTES_32 = 128 << 20     # up to 32 rows gemm_skinny takes weights up to this size
-
-
 def _decode_kernel(M: int, N: int, K: int):
-    if M <= ops.SKINNY_BEST_ROWS:
-        return ops.gemm_skinny
-    return ops.gemm_skinny if M <= 32 and 2 * N * K <= SKINNY_BYTES_32 else ops.gemm_stream
+    return ops.gemm_skinny if M <= ops.SKINNY_BEST_ROWS else ops.gemm_tc
 
 
 def _rows_for(fn, a):
@@ -37,7 +30,7 @@ def linear_bf16(a, weight, out_dtype, residual, emit=None):
     M, K = a.shape
     if K % 8:
         return None
-    fn = _decode_kernel(M, weight.N, K) if M <= ops.SKINNY_MAX_ROWS else ops.gemm_tc
+    fn = _decode_kernel(M, weight.N, K)
     a = _rows_for(fn, a)
     more = {"next_w": weight.next_tensor} if fn is ops.gemm_skinny else {}
     if residual is not None:
@@ -54,6 +47,6 @@ def linear_swiglu_bf16(a, weight):
     M, K = a.shape
     if K % 8:
         return None
-    fn = _decode_kernel(M, weight.N, K) if M <= ops.SKINNY_MAX_ROWS else ops.gemm_tc
+    fn = _decode_kernel(M, weight.N, K)
     more = {"next_w": weight.next_tensor} if fn is ops.gemm_skinny else {}
     return fn(_rows_for(fn, a), weight.tensor, ops.EPI_SWIGLU, **more)

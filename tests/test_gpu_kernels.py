@@ -318,48 +318,6 @@ def test_gemm_skinny_qkv_finishes_a_folded_norm():
     _close(outs[1][0], outs[0][0], 3 * BF16_ULP, BF16_ULP)
 
 
-@pytest.mark.parametrize("M", [1, 3, 8, 16, 17, 33, 64])
-@pytest.mark.parametrize("N,K", [(16, 64), (100, 200), (4104, 4096), (250, 80), (1000, 14336), (33000, 512)])
-def test_gemm_stream(M, N, K):
-    """Shapes whose units divide among the blocks in every way: fewer units than blocks, row
-    tiles split between blocks, blocks that hold several whole tiles."""
-    ops = _ops()
-    a, w = _rand((M, K), torch.bfloat16, 30), _rand((N, K), torch.bfloat16, 31)
-    ref = a.float().double() @ w.float().double().T
-    _close(ops.gemm_stream(a, w, ops.EPI_F32), ref, _acc_tol(K))
-    _close(ops.gemm_stream(a, w, ops.EPI_BF16), ref, _acc_tol(K), BF16_ULP)
-    res = _rand((M, N), torch.float32, 32)
-    expect = res.double() + ref
-    _close(ops.gemm_stream(a, w, ops.EPI_RESID, residual=res), expect, _acc_tol(K))
-    torch.cuda.synchronize()
-    assert ops.gemm_stream_status() == 0
-
-
-@pytest.mark.parametrize("M,F,K", [(1, 8, 64), (5, 176, 64), (64, 1000, 328), (8, 14336, 1024)])
-def test_gemm_stream_swiglu(M, F, K):
-    ops = _ops()
-    from longbow_quarrel_b200.kernels.linear import interleave_gate_up
-    a = _rand((M, K), torch.bfloat16, 33)
-    wg, wu = _rand((F, K), torch.bfloat16, 34, 0.2), _rand((F, K), torch.bfloat16, 35, 0.2)
-    g = a.float().double() @ wg.float().double().T
-    u = a.float().double() @ wu.float().double().T
-    ref = u * (g / (1 + torch.exp(-g)))
-    out = ops.gemm_stream(a, interleave_gate_up(wg, wu), ops.EPI_SWIGLU)
-    assert out.shape == (M, F)
-    _close(out, ref, 1e-4, BF16_ULP)
-    torch.cuda.synchronize()
-    assert ops.gemm_stream_status() == 0
-
-
-def test_gemm_stream_is_independent_of_other_rows_and_repeatable():
-    ops = _ops()
-    a, w = _rand((37, 4096), torch.bfloat16, 36), _rand((4096, 4096), torch.bfloat16, 37)
-    full = ops.gemm_stream(a, w, ops.EPI_F32)
-    assert torch.equal(ops.gemm_stream(a, w, ops.EPI_F32), full)          # parked pieces are added in a fixed order
-    for r in (0, 11, 36):
-        assert torch.equal(ops.gemm_stream(a[r:r + 1].contiguous(), w, ops.EPI_F32)[0], full[r])
-
-
 @pytest.mark.parametrize("M", [65, 128, 300, 1111])
 @pytest.mark.parametrize("N,K", [(16, 64), (250, 80), (1000, 200), (4104, 1024), (520, 4096)])
 def test_gemm_tc(M, N, K):
@@ -387,6 +345,33 @@ def test_gemm_tc_swiglu(M, F, K):
     out = ops.gemm_tc(a, interleave_gate_up(wg, wu), ops.EPI_SWIGLU)
     assert out.shape == (M, F)
     _close(out, ref, 1e-4, BF16_ULP)
+    torch.cuda.synchronize()
+    assert ops.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("M", [17, 64, 100, 300])
+@pytest.mark.parametrize("N,K", [(520, 4096), (4104, 1024), (250, 14336), (1000, 392)])
+def test_gemm_tc_cuts_the_contraction_when_tiles_are_few(M, N, K):
+    """Few rows and a narrow weight: pieces of work are (tile, range of K), added by a second kernel."""
+    ops = _ops()
+    from longbow_quarrel_b200.kernels.linear import interleave_gate_up
+    a, w = _rand((M, K), torch.bfloat16, 70), _rand((N, K), torch.bfloat16, 71, 0.3)
+    ref = a.float().double() @ w.float().double().T
+    _close(ops.gemm_tc(a, w, ops.EPI_F32), ref, _acc_tol(K))
+    _close(ops.gemm_tc(a, w, ops.EPI_BF16), ref, _acc_tol(K), BF16_ULP)
+    res = _rand((M, N), torch.float32, 72)
+    expect = res.double() + ref
+    _close(ops.gemm_tc(a, w, ops.EPI_RESID, residual=res), expect, _acc_tol(K))
+    F = N // 16 * 8
+    if F:
+        wg, wu = w[:F].contiguous() * 0.3, w[F:2 * F].contiguous() * 0.3
+        g, u = a.float().double() @ wg.float().double().T, a.float().double() @ wu.float().double().T
+        out = ops.gemm_tc(a, interleave_gate_up(wg, wu), ops.EPI_SWIGLU)
+        assert out.shape == (M, F)
+        _close(out, u * (g / (1 + torch.exp(-g))), 1e-4, BF16_ULP)
+    full = ops.gemm_tc(a, w, ops.EPI_F32)
+    assert torch.equal(ops.gemm_tc(a, w, ops.EPI_F32), full)                               # repeatable
+    assert torch.equal(ops.gemm_tc(a[3:4].contiguous(), w, ops.EPI_F32)[0], full[3])       # a row alone
     torch.cuda.synchronize()
     assert ops.gemm_tc_status() == 0
 
