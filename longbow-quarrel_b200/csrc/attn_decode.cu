@@ -13,7 +13,8 @@
 // sequence are merged by their running maximum and sum, in a fixed order.
 //
 // Slices write unnormalised partial outputs [token, head, slice, head_dim] with
-// (max, sum) to scratch memory; lq_attn_decode's second kernel merges them.
+// (max, sum) to scratch memory; the block that parks its slice last for a (token, kv head)
+// merges them (a counter per pair; without counters a second kernel merges).
 //
 // Reference counterpart: att_fused_f16 (internal/device/kernels.metal:657-813), one
 // threadgroup per query head, scores in threadgroup memory.
