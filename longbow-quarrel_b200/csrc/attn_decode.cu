@@ -63,7 +63,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
                    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                    __nv_bfloat16* __restrict__ out, int H, int Hkv, int hd, int page_size, float scale, int window,
-                   int n_splits, const char* next_w, unsigned next_piece) {
+                   int n_splits, const char* next_w, unsigned next_piece, int early_loads) {
     constexpr int LD = HD + PAD;                   // shared-memory row length in elements
     constexpr int KD = HD / 16;                    // k16 steps over the head dimension
     constexpr int STAGE = 2 * TILE * LD;           // elements of one tile: K rows, then V rows
@@ -84,32 +84,11 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
     // No pdl_launch_dependents() here: released early, the blocks of the product that follows moved
     // onto the SMs this kernel leaves free and fetched weights against it (measured: the step ran
     // 50 % slower).  The kernel after this one starts when this one ends.
-    pdl_wait();
+    // Positions, slots and page table are written before the step starts, never by a kernel of the
+    // step, so they may be read before the kernel ahead is known to have finished.
     const int pos = tok_pos[tok], len = pos + 1;
     const int start = (window > 0 && pos >= window) ? pos - window + 1 : 0;
     const int* pt = page_table + (size_t)slots[tok_seq[tok]] * pt_stride;
-
-    // Query heads of the group as the rows of the mma tile (rows g and g + 8 of this thread).
-    const int r0 = gt * 16 + g, r1 = r0 + 8;
-    const bool r0ok = r0 < G, r1ok = r1 < G;
-    const __nv_bfloat16* q0p = q + (size_t)tok * q_stride + (size_t)(kvh * G + (r0ok ? r0 : 0)) * hd;
-    const __nv_bfloat16* q1p = q + (size_t)tok * q_stride + (size_t)(kvh * G + (r1ok ? r1 : 0)) * hd;
-    uint32_t qf[KD][4];
-#pragma unroll
-    for (int kk = 0; kk < KD; ++kk) {
-        const int d0 = kk * 16 + 2 * t, d1 = d0 + 8;
-        qf[kk][0] = (r0ok && d0 < hd) ? *reinterpret_cast<const uint32_t*>(q0p + d0) : 0u;
-        qf[kk][1] = (r1ok && d0 < hd) ? *reinterpret_cast<const uint32_t*>(q1p + d0) : 0u;
-        qf[kk][2] = (r0ok && d1 < hd) ? *reinterpret_cast<const uint32_t*>(q0p + d1) : 0u;
-        qf[kk][3] = (r1ok && d1 < hd) ? *reinterpret_cast<const uint32_t*>(q1p + d1) : 0u;
-    }
-
-    float o[HD / 8][4];
-#pragma unroll
-    for (int j = 0; j < HD / 8; ++j)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
-    float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
 
     const int first_tile = start / TILE;
     const int n_tiles = (len + TILE - 1) / TILE - first_tile;
@@ -138,8 +117,44 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
         }
         cp_async_commit();          // an empty group when there is no tile: the count of groups stays in step
     };
+    // The keys and values of earlier positions were stored by earlier steps: a warp whose first tiles
+    // do not hold the token's own position (which the kernel ahead is writing) asks for them at once.
+    const int own_tile = pos / TILE;
+    bool early = early_loads != 0;
 #pragma unroll
-    for (int n = 0; n < RING - 1; ++n) issue(n);
+    for (int n = 0; n < RING - 1; ++n) early = early && (tile_lo + warp + n * DW != own_tile);
+    if (early) {
+#pragma unroll
+        for (int n = 0; n < RING - 1; ++n) issue(n);
+    }
+    pdl_wait();
+    if (!early) {
+#pragma unroll
+        for (int n = 0; n < RING - 1; ++n) issue(n);
+    }
+    // Query heads of the group as the rows of the mma tile (rows g and g + 8 of this thread).
+    const int r0 = gt * 16 + g, r1 = r0 + 8;
+    const bool r0ok = r0 < G, r1ok = r1 < G;
+    const __nv_bfloat16* q0p = q + (size_t)tok * q_stride + (size_t)(kvh * G + (r0ok ? r0 : 0)) * hd;
+    const __nv_bfloat16* q1p = q + (size_t)tok * q_stride + (size_t)(kvh * G + (r1ok ? r1 : 0)) * hd;
+    uint32_t qf[KD][4];
+#pragma unroll
+    for (int kk = 0; kk < KD; ++kk) {
+        const int d0 = kk * 16 + 2 * t, d1 = d0 + 8;
+        qf[kk][0] = (r0ok && d0 < hd) ? *reinterpret_cast<const uint32_t*>(q0p + d0) : 0u;
+        qf[kk][1] = (r1ok && d0 < hd) ? *reinterpret_cast<const uint32_t*>(q1p + d0) : 0u;
+        qf[kk][2] = (r0ok && d1 < hd) ? *reinterpret_cast<const uint32_t*>(q0p + d1) : 0u;
+        qf[kk][3] = (r1ok && d1 < hd) ? *reinterpret_cast<const uint32_t*>(q1p + d1) : 0u;
+    }
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
+    float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+
+
     const int my_tiles = tile_lo + warp < tile_hi ? (tile_hi - tile_lo - warp + DW - 1) / DW : 0;
     for (int n = 0; n < my_tiles; ++n) {
         issue(n + RING - 1);
@@ -334,7 +349,7 @@ template <int HD>
 int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages, const int* page_table, int pt_stride,
            const int* tok_pos, const int* tok_seq, const int* slots, float* part_o, float* part_ml, int* counters,
            void* out, int T, int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
-           const void* next_w, long next_bytes, cudaStream_t stream) {
+           const void* next_w, long next_bytes, int early_loads, cudaStream_t stream) {
     int G = H / Hkv, gtiles = (G + 15) / 16;
     dim3 grid(n_splits, Hkv * gtiles, T);
     const long n_blocks = (long)grid.x * grid.y * grid.z;
@@ -353,7 +368,7 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
     int rc = launch_pdl(attn_decode_kernel<HD>, grid, dim3(DW * 32), smem, stream, (const __nv_bfloat16*)q, q_stride,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots,
         part_o, part_ml, counters, (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, n_splits,
-        (const char*)next_w, (unsigned)piece);
+        (const char*)next_w, (unsigned)piece, early_loads);
     if (rc != LQ_OK || n_splits == 1 || counters != nullptr) return rc;
     return launch_pdl(attn_merge_kernel, dim3(T * H), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml,
                       (__nv_bfloat16*)out, hd, n_splits);
@@ -369,18 +384,21 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
 // at most 32 slices.
 // next_w, next_bytes (or null): weights that are read next on this stream; their first next_bytes
 // are asked into L2 as the blocks finish.
+// early_loads: non-zero when, of all keys and values that a token reads, only those at its own
+// position can have been written by the kernel ahead on the stream (one new token per sequence):
+// the others are then requested before that kernel is known to have finished.
 LQ_EXPORT int lq_attn_decode_next(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                                   const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
                                   const int* slots, float* part_o, float* part_ml, int* counters, void* out, int T,
                                   int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
-                                  const void* next_w, long next_bytes, cudaStream_t stream) {
+                                  const void* next_w, long next_bytes, int early_loads, cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
     if (hd % 8 || hd > 128 || hd <= 0 || H % Hkv || page_size % TILE || n_splits < 1 || q_stride % 8) return LQ_BAD_SIZE;
     if (n_splits > MAX_SPLITS) return LQ_BAD_SIZE;
     if (n_splits > 1 && (!part_o || !part_ml)) return LQ_BAD_SIZE;
 #define LQ_GO(HD) return launch<HD>(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, \
                                     part_o, part_ml, counters, out, T, H, Hkv, hd, page_size, scale, window, n_splits, \
-                                    next_w, next_bytes, stream)
+                                    next_w, next_bytes, early_loads, stream)
     if (hd <= 32) LQ_GO(32);
     if (hd <= 64) LQ_GO(64);
     LQ_GO(128);
@@ -393,7 +411,7 @@ LQ_EXPORT int lq_attn_decode_merged(const void* q, int q_stride, const void* k_p
                                     int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
                                     cudaStream_t stream) {
     return lq_attn_decode_next(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, part_o,
-                               part_ml, counters, out, T, H, Hkv, hd, page_size, scale, window, n_splits, nullptr, 0, stream);
+                               part_ml, counters, out, T, H, Hkv, hd, page_size, scale, window, n_splits, nullptr, 0, 0, stream);
 }
 
 // The same without counters: the slices are merged by a second kernel.

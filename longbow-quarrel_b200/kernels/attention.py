@@ -32,6 +32,6 @@ def attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w=None):
         n_splits = decode_splits(ctx.T, Hkv, -(-(H // Hkv) // 16), ctx.max_kv)
         return ops.attn_decode(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.tok_pos,
                                ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window, n_splits,
-                               next_w=next_w)
+                               next_w=next_w, early_loads=True)      # a decode step: one new token per sequence
     return ops.attention_plain(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.tok_pos,
                                ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window)

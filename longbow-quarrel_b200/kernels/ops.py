@@ -406,10 +406,13 @@ def attn_prefill_tc_status() -> int:
 def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq, slots, H: int, Hkv: int, hd: int,
                 page_size: int, scale: float, window: int | None, n_splits: int,
                 out: torch.Tensor | None = None, scratch: tuple | None = None,
-                next_w: torch.Tensor | None = None) -> torch.Tensor:
+                next_w: torch.Tensor | None = None, early_loads: bool = False) -> torch.Tensor:
     """Attention of single query rows over the paged bfloat16 cache, the keys of each
     sequence cut into n_splits slices that are merged afterwards.  next_w: the weights that the
-    stream reads after this; their first bytes are asked into L2 as the blocks finish."""
+    stream reads after this; their first bytes are asked into L2 as the blocks finish.
+    early_loads: of the keys and values a row reads, only those at its own position can have been
+    written by the kernel ahead on the stream (a decode step: one new token per sequence); the kernel
+    then requests the others without waiting for that kernel."""
     T = q.shape[0]
     if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
         raise KernelError("attn_decode takes bfloat16 queries and cache")
@@ -434,11 +437,11 @@ def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq,
     fn = _fn("attn_decode", "lq_attn_decode_next", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                     c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_long,
-                                                    c_void_p])
+                                                    c_int, c_void_p])
     next_p, next_n = _next(next_w)
     _check(fn(_p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0), _p(tok_pos),
               _p(tok_seq), _p(slots), _p(part_o), _p(part_ml), _p(counters), _p(out), T, H, Hkv, hd, page_size,
-              float(scale), int(window or 0), n_splits, next_p, next_n, _stream()), "attn_decode",
+              float(scale), int(window or 0), n_splits, next_p, next_n, int(early_loads), _stream()), "attn_decode",
            2 if n_splits > 1 and counters is None else 1)
     return out
 

@@ -398,10 +398,11 @@ def test_attn_decode(H, Hkv, hd, window, n_splits):
     tok_pos = [299, 0, 76, 63, 16, 150]
     q = _rand((len(tok_seq), (H + 2 * Hkv) * hd), torch.bfloat16, 78)
     scale = hd ** -0.5
-    out = ops.attn_decode(q, case.k_pages, case.v_pages, case.table, _ints(tok_pos), _ints(tok_seq), case.slots,
-                          H, Hkv, hd, case.page_size, scale, window, n_splits)
     ref = case.reference(q[:, :H * hd].reshape(-1, H, hd).float(), tok_seq, tok_pos, H, scale, window)
-    _close(out.reshape(-1, H, hd), ref, _attn_tol(case, ref), BF16_ULP)
+    for early in (False, True):       # with early loads the old keys are requested before the wait for the kernel ahead
+        out = ops.attn_decode(q, case.k_pages, case.v_pages, case.table, _ints(tok_pos), _ints(tok_seq), case.slots,
+                              H, Hkv, hd, case.page_size, scale, window, n_splits, early_loads=early)
+        _close(out.reshape(-1, H, hd), ref, _attn_tol(case, ref), BF16_ULP)
 
 
 @pytest.mark.parametrize("far_key", [0, 5, 250, 511, 700])
