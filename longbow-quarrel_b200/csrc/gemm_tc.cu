@@ -118,9 +118,12 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int BN, int STAGES>
+// AROWS: rows of x that a stage holds, 128 or (for at most 64 rows of x) 64.  With 64 the products still
+// read 128 rows: the upper 64 are whatever follows in shared memory, and give rows of the accumulator
+// that are never stored -- the stage is 8 KB smaller, so more stages of W are on their way.
+template <int BN, int STAGES, int AROWS>
 struct Smem {
-    alignas(1024) uint8_t a[STAGES][BM * BK * 2];
+    alignas(1024) uint8_t a[STAGES][AROWS * BK * 2];
     alignas(1024) uint8_t b[STAGES][BN * BK * 2];
     alignas(8) uint64_t full[STAGES];
     uint64_t empty[STAGES];
@@ -131,12 +134,13 @@ struct Smem {
 
 // ------------------------------------------------------------------ epilogue of 32 columns of one row
 template <int EPI>
+// n_lim: the tile's columns end there (at most N); columns from n_lim on are not stored.
 __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], void* Cout,
-                                            const float* residual, int m, int n, int M, int N) {
-    if (m >= M || n >= N) return;
+                                            const float* residual, int m, int n, int M, int N, int n_lim) {
+    if (m >= M || n >= n_lim) return;
     if (EPI == EPI_SWIGLU) {
         // 32 columns = [8 gate, 8 up, 8 gate, 8 up] -> 16 outputs at column n / 2 of [M, N / 2].
-        const int NO = N >> 1, no = n >> 1;
+        const int NO = N >> 1, no = n >> 1, no_lim = n_lim >> 1;
         float o[16];
 #pragma unroll
         for (int h = 0; h < 2; ++h)
@@ -146,18 +150,18 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], void* Cout,
                 o[h * 8 + i] = u * (g / (1.0f + __expf(-g)));
             }
         __nv_bfloat16* dst = (__nv_bfloat16*)Cout + (size_t)m * NO + no;
-        if (no + 16 <= NO && (NO & 7) == 0) {
+        if (no + 16 <= no_lim && (NO & 7) == 0) {
             uint4* d4 = reinterpret_cast<uint4*>(dst);
             d4[0] = make_uint4(pack2(o[0], o[1]), pack2(o[2], o[3]), pack2(o[4], o[5]), pack2(o[6], o[7]));
             d4[1] = make_uint4(pack2(o[8], o[9]), pack2(o[10], o[11]), pack2(o[12], o[13]), pack2(o[14], o[15]));
         } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i)
-                if (no + i < NO) dst[i] = __float2bfloat16_rn(o[i]);
+                if (no + i < no_lim) dst[i] = __float2bfloat16_rn(o[i]);
         }
         return;
     }
-    const bool whole = n + 32 <= N;
+    const bool whole = n + 32 <= n_lim;
     if (EPI == EPI_BF16) {
         __nv_bfloat16* dst = (__nv_bfloat16*)Cout + (size_t)m * N + n;
         if (whole && (N & 7) == 0) {
@@ -171,7 +175,7 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], void* Cout,
         } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-                if (n + i < N) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
+                if (n + i < n_lim) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
         }
     } else {
         float* dst = (float*)Cout + (size_t)m * N + n;
@@ -190,18 +194,18 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], void* Cout,
         } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-                if (n + i < N) dst[i] = __uint_as_float(r[i]) + (EPI == EPI_RESID ? res[i] : 0.f);
+                if (n + i < n_lim) dst[i] = __uint_as_float(r[i]) + (EPI == EPI_RESID ? res[i] : 0.f);
         }
     }
 }
 
 // ------------------------------------------------------------------ the kernel
-template <int BN, int STAGES, int EPI>
+template <int BN, int STAGES, int EPI, int AROWS>
 __global__ void __launch_bounds__(N_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                void* Cout, const float* residual, int M, int N, int K, int splits) {
     extern __shared__ uint8_t smem_raw[];
-    using S = Smem<BN, STAGES>;
+    using S = Smem<BN, STAGES, AROWS>;
     S& sm = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
@@ -209,8 +213,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // is the float32-store one and Cout the scratch [splits, M, N].
     const int total = m_tiles * n_tiles * splits;
     const int n_kb = (K + BK - 1) / BK;
-    constexpr uint32_t STAGE_BYTES = (BM + BN) * BK * 2;
-    constexpr uint32_t TMEM_COLS = 2 * BN;             // two accumulators of BN float32 columns
+    constexpr uint32_t STAGE_BYTES = (AROWS + BN) * BK * 2;
+    constexpr uint32_t ACC_COLS = BN <= 128 ? 128 : 256;   // columns of tensor memory per accumulator (BN of them used)
+    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&sm.full[s]), 1); mbar_init(smem_u32(&sm.empty[s]), 1); }
@@ -269,7 +274,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint32_t acc = t & 1;
                 if (!mbar_wait(smem_u32(&sm.acc_empty[acc]), ((t >> 1) & 1) ^ 1)) { atomicExch(&g_status, 2); ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * BN;
+                const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
                 for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(smem_u32(&sm.full[s]), (it / STAGES) & 1)) { atomicExch(&g_status, 3); ok = false; break; }
@@ -297,13 +302,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!mbar_wait(smem_u32(&sm.acc_full[acc]), (t >> 1) & 1)) { atomicExch(&g_status, 4); ok = false; break; }
             tc_fence_after();
             const int m = m0 + quarter * 32 + lane;
-            const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+            const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+            const int n_lim = n0 + BN < N ? n0 + BN : N;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = 0; c < (BN + 31) / 32; ++c) {      // a last half chunk reads columns that are not stored
                 uint32_t r[32];
                 tc_ld32(taddr + c * 32, r);
                 tc_wait_ld();
-                store_chunk<EPI>(r, dst, residual, m, n0 + c * 32, M, N);
+                store_chunk<EPI>(r, dst, residual, m, n0 + c * 32, M, N, n_lim);
             }
             tc_fence_before();
             __syncwarp();
@@ -411,32 +417,33 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) 
     return r == CUDA_SUCCESS ? LQ_OK : LQ_BAD_SIZE;
 }
 
-template <int BN, int STAGES, int EPI>
+template <int BN, int STAGES, int EPI, int AROWS>
 int launch_epi(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const float* residual, int M, int N, int K,
                int n_sms, int splits, cudaStream_t stream) {
-    constexpr size_t smem = sizeof(Smem<BN, STAGES>) + 1024;
+    constexpr size_t smem = sizeof(Smem<BN, STAGES, AROWS>) + 1024;
+    static_assert(smem <= 232448, "more shared memory than a block may have");
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI, AROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return lq_launch_status();
         configured = true;
     }
     int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * splits;
     int grid = tiles < n_sms ? tiles : n_sms;
-    return launch_pdl(gemm_tc_kernel<BN, STAGES, EPI>, dim3(grid), dim3(N_THREADS), smem, stream, ma, mb, C, residual, M, N, K,
+    return launch_pdl(gemm_tc_kernel<BN, STAGES, EPI, AROWS>, dim3(grid), dim3(N_THREADS), smem, stream, ma, mb, C, residual, M, N, K,
                       splits);
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int AROWS = BM>
 int launch_bn(const void* A, const void* W, void* C, const float* residual, int M, int N, int K, int epi, int n_sms,
               int splits, float* scratch, cudaStream_t stream) {
     CUtensorMap ma, mb;
-    int rc = make_map(&ma, A, M, K, BM);
+    int rc = make_map(&ma, A, M, K, AROWS);
     if (rc != LQ_OK) return rc;
     rc = make_map(&mb, W, N, K, BN);
     if (rc != LQ_OK) return rc;
     if (splits > 1) {
-        rc = launch_epi<BN, STAGES, EPI_F32>(ma, mb, scratch, nullptr, M, N, K, n_sms, splits, stream);
+        rc = launch_epi<BN, STAGES, EPI_F32, AROWS>(ma, mb, scratch, nullptr, M, N, K, n_sms, splits, stream);
         if (rc != LQ_OK) return rc;
         switch (epi) {
             case EPI_BF16: return launch_reduce<EPI_BF16>(scratch, splits, C, residual, M, N, stream);
@@ -447,10 +454,10 @@ int launch_bn(const void* A, const void* W, void* C, const float* residual, int 
         return LQ_BAD_DTYPE;
     }
     switch (epi) {
-        case EPI_BF16: return launch_epi<BN, STAGES, EPI_BF16>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
-        case EPI_F32: return launch_epi<BN, STAGES, EPI_F32>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
-        case EPI_RESID: return launch_epi<BN, STAGES, EPI_RESID>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
-        case EPI_SWIGLU: return launch_epi<BN, STAGES, EPI_SWIGLU>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
+        case EPI_BF16: return launch_epi<BN, STAGES, EPI_BF16, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
+        case EPI_F32: return launch_epi<BN, STAGES, EPI_F32, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
+        case EPI_RESID: return launch_epi<BN, STAGES, EPI_RESID, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
+        case EPI_SWIGLU: return launch_epi<BN, STAGES, EPI_SWIGLU, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
     }
     return LQ_BAD_DTYPE;
 }
@@ -495,9 +502,27 @@ LQ_EXPORT int lq_gemm_tc(const void* A, const void* W, void* C, const float* res
     const int splits = plan_splits(M, N, K);
     if (splits > 1) {
         if (!scratch || ((uintptr_t)scratch & 15)) return LQ_BAD_SIZE;
+        if (M <= 64) return launch_bn<256, 5, 64>(A, W, C, residual, M, N, K, epi, n_sms, splits, scratch, stream);
         return launch_bn<256, 4>(A, W, C, residual, M, N, K, epi, n_sms, splits, scratch, stream);
     }
-    // Wide tiles when they still fill the GPU, narrower ones otherwise.
+    if (M <= 64) {
+        // At most 64 rows: one row of tiles, bound by reading W: the tile width whose rounds over the SMs read the least
+        // (rounds x width), so that no round leaves most SMs idle.  28672 columns: 138 tiles of 208 in one
+        // round instead of 224 tiles of 128 in two.
+        static const int widths[] = {256, 224, 208, 192, 176, 160, 144, 128};
+        int best = 256;
+        long best_cost = -1;
+        for (int w : widths) {
+            const long tiles = (N + w - 1) / w, cost = (tiles + n_sms - 1) / n_sms * w;
+            if (best_cost < 0 || cost < best_cost) { best = w; best_cost = cost; }
+        }
+#define LQ_W(w, st) case w: return launch_bn<w, st, 64>(A, W, C, residual, M, N, K, epi, n_sms, 1, nullptr, stream)
+        switch (best) {       // as many stages as the shared memory holds
+            LQ_W(256, 5); LQ_W(224, 6); LQ_W(208, 6); LQ_W(192, 7); LQ_W(176, 7); LQ_W(160, 8); LQ_W(144, 8); LQ_W(128, 9);
+        }
+#undef LQ_W
+    }
+    // Many rows: wide tiles when they still fill the GPU, narrower ones otherwise.
     long tiles256 = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
     if (tiles256 >= n_sms) return launch_bn<256, 4>(A, W, C, residual, M, N, K, epi, n_sms, 1, nullptr, stream);
     return launch_bn<128, 6>(A, W, C, residual, M, N, K, epi, n_sms, 1, nullptr, stream);

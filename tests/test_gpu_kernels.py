@@ -376,6 +376,31 @@ def test_gemm_tc_cuts_the_contraction_when_tiles_are_few(M, N, K):
     assert ops.gemm_tc_status() == 0
 
 
+@pytest.mark.parametrize("M", [17, 64])
+@pytest.mark.parametrize("N", [33008, 30000, 28000, 26000, 23008, 40000, 18000])   # tile widths 224 ... 128
+def test_gemm_tc_one_row_of_tiles_of_every_width(M, N):
+    """At most 64 rows: the tile width is chosen so that the rounds over the SMs read the least; a tile
+    whose width is no multiple of 32 ends in a half chunk, and the last tile of the row is partial."""
+    ops = _ops()
+    from longbow_quarrel_b200.kernels.linear import interleave_gate_up
+    K = 136
+    a, w = _rand((M, K), torch.bfloat16, 76), _rand((N, K), torch.bfloat16, 77, 0.3)
+    ref = (a.float() @ w.float().T).double()
+    _close(ops.gemm_tc(a, w, ops.EPI_F32), ref, _acc_tol(K) + 1e-6)
+    _close(ops.gemm_tc(a, w, ops.EPI_BF16), ref, _acc_tol(K) + 1e-6, BF16_ULP)
+    res = _rand((M, N), torch.float32, 78)
+    expect = res.double() + ref
+    _close(ops.gemm_tc(a, w, ops.EPI_RESID, residual=res), expect, _acc_tol(K) + 1e-6)
+    F = N // 2
+    wg, wu = w[:F].contiguous(), w[F:].contiguous()
+    g, u = (a.float() @ wg.float().T).double(), (a.float() @ wu.float().T).double()
+    out = ops.gemm_tc(a, interleave_gate_up(wg, wu), ops.EPI_SWIGLU)
+    assert out.shape == (M, F)
+    _close(out, u * (g / (1 + torch.exp(-g))), 1e-4, BF16_ULP)
+    torch.cuda.synchronize()
+    assert ops.gemm_tc_status() == 0
+
+
 def test_gemm_tc_large_many_tiles_per_block():
     """More tiles than SMs: blocks walk over several tiles and both accumulators are used."""
     ops = _ops()
