@@ -434,7 +434,8 @@ int launch_epi(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const floa
                       splits);
 }
 
-template <int BN, int STAGES, int AROWS = BM>
+// ALL: every epilogue; otherwise only the two that products with many columns have (SwiGLU, float32 store).
+template <int BN, int STAGES, int AROWS = BM, bool ALL = true>
 int launch_bn(const void* A, const void* W, void* C, const float* residual, int M, int N, int K, int epi, int n_sms,
               int splits, float* scratch, cudaStream_t stream) {
     CUtensorMap ma, mb;
@@ -453,12 +454,12 @@ int launch_bn(const void* A, const void* W, void* C, const float* residual, int 
         }
         return LQ_BAD_DTYPE;
     }
-    switch (epi) {
-        case EPI_BF16: return launch_epi<BN, STAGES, EPI_BF16, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
-        case EPI_F32: return launch_epi<BN, STAGES, EPI_F32, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
-        case EPI_RESID: return launch_epi<BN, STAGES, EPI_RESID, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
-        case EPI_SWIGLU: return launch_epi<BN, STAGES, EPI_SWIGLU, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
+    if constexpr (ALL) {
+        if (epi == EPI_BF16) return launch_epi<BN, STAGES, EPI_BF16, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
+        if (epi == EPI_RESID) return launch_epi<BN, STAGES, EPI_RESID, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
     }
+    if (epi == EPI_F32) return launch_epi<BN, STAGES, EPI_F32, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
+    if (epi == EPI_SWIGLU) return launch_epi<BN, STAGES, EPI_SWIGLU, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
     return LQ_BAD_DTYPE;
 }
 
@@ -505,25 +506,30 @@ LQ_EXPORT int lq_gemm_tc(const void* A, const void* W, void* C, const float* res
         if (M <= 64) return launch_bn<256, 5, 64>(A, W, C, residual, M, N, K, epi, n_sms, splits, scratch, stream);
         return launch_bn<256, 4>(A, W, C, residual, M, N, K, epi, n_sms, splits, scratch, stream);
     }
+    long tiles256 = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
     if (M <= 64) {
-        // At most 64 rows: one row of tiles, bound by reading W: the tile width whose rounds over the SMs read the least
-        // (rounds x width), so that no round leaves most SMs idle.  28672 columns: 138 tiles of 208 in one
-        // round instead of 224 tiles of 128 in two.
-        static const int widths[] = {256, 224, 208, 192, 176, 160, 144, 128};
-        int best = 256;
-        long best_cost = -1;
-        for (int w : widths) {
-            const long tiles = (N + w - 1) / w, cost = (tiles + n_sms - 1) / n_sms * w;
-            if (best_cost < 0 || cost < best_cost) { best = w; best_cost = cost; }
+        // At most 64 rows: one row of tiles, bound by reading W: the tile width whose rounds over the SMs read
+        // the least (rounds x width), so that no round leaves most SMs idle.  28672 columns: 138 tiles of 208 in
+        // one round instead of 224 tiles of 128 in two.  The two epilogues that products with many columns have
+        // choose among all widths; the others (q/k/v, residual) have few columns in the models at hand and take
+        // 256 or 128.  As many stages as the shared memory holds.
+        int best = tiles256 >= n_sms ? 256 : 128;
+        if (epi == EPI_SWIGLU || epi == EPI_F32) {
+            static const int widths[] = {256, 224, 208, 192, 176, 160, 144, 128};
+            long best_cost = -1;
+            for (int w : widths) {
+                const long tiles = (N + w - 1) / w, cost = (tiles + n_sms - 1) / n_sms * w;
+                if (best_cost < 0 || cost < best_cost) { best = w; best_cost = cost; }
+            }
         }
-#define LQ_W(w, st) case w: return launch_bn<w, st, 64>(A, W, C, residual, M, N, K, epi, n_sms, 1, nullptr, stream)
-        switch (best) {       // as many stages as the shared memory holds
-            LQ_W(256, 5); LQ_W(224, 6); LQ_W(208, 6); LQ_W(192, 7); LQ_W(176, 7); LQ_W(160, 8); LQ_W(144, 8); LQ_W(128, 9);
+#define LQ_W(w, st, all) case w: return launch_bn<w, st, 64, all>(A, W, C, residual, M, N, K, epi, n_sms, 1, nullptr, stream)
+        switch (best) {
+            LQ_W(256, 5, true); LQ_W(224, 6, false); LQ_W(208, 6, false); LQ_W(192, 7, false); LQ_W(176, 7, false);
+            LQ_W(160, 8, false); LQ_W(144, 8, false); LQ_W(128, 9, true);
         }
 #undef LQ_W
     }
     // Many rows: wide tiles when they still fill the GPU, narrower ones otherwise.
-    long tiles256 = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
     if (tiles256 >= n_sms) return launch_bn<256, 4>(A, W, C, residual, M, N, K, epi, n_sms, 1, nullptr, stream);
     return launch_bn<128, 6>(A, W, C, residual, M, N, K, epi, n_sms, 1, nullptr, stream);
 }
