@@ -11,11 +11,20 @@
 //               keys).  S of the next tile is issued as soon as S of this one has been read,
 //               so the tensor cores work on it while the softmax of this tile runs;
 //   warps 2..9  two threads per query row (64 keys each): read the row of S from tensor
-//               memory, scale and mask it, keep the running maximum and sum in 32-bit, write
+//               memory, mask it, keep the running maximum and sum in 32-bit, write
 //               bfloat16 probabilities into shared memory in the layout the tensor cores read.  The
 //               reference maximum of a row is only moved (and O rescaled in tensor memory)
 //               when the true maximum has grown by more than 2^8 since; the result is the
-//               same, as O and the sum always share one reference.
+//               same, as O and the sum always share one reference.  The probabilities are
+//               2^(s * scale - m) by one multiply-add and the special-function unit, rounded
+//               to bfloat16 by integer arithmetic (conversion instructions share the
+//               special-function pipe), and are made before the wait for the last product with
+//               V, so only their stores lie behind it.
+// Measured on B200: with this a tile of 128 keys takes about 3300 cycles, of which the products are
+// 1050; removing the exponentials, the maxima or the stores of P from the loop changes nothing, and
+// the keys and values streamed from L2 (64 KB a tile, every block its own) come to 5.6 TB/s over all
+// SMs: the kernel is bound by that stream, not by the softmax.  Two query tiles per block that share
+// each tile of keys would halve it.
 // A row at position p sees keys max(0, p - window + 1) .. p of its own sequence.  Whole pages
 // are loaded, so rows of a page beyond a sequence's length are multiplied by probability zero:
 // the cache must hold finite values everywhere (it is zero-filled when it is made).
@@ -35,7 +44,9 @@ constexpr int BN = 128;                 // keys per tile
 constexpr int HD = 128;                 // head dimension
 constexpr int PAGE = 64;
 constexpr int PANEL = 128 * 128;        // bytes of a [128 rows, 64 elements] panel
-constexpr int N_THREADS = 320;         // TMA warp, MMA warp, 8 softmax warps
+constexpr int PARTS = 2;                // softmax threads per query row: each has 128 / PARTS of a tile's keys
+constexpr int N_SOFTMAX = PARTS * BM;   // softmax threads
+constexpr int N_THREADS = 64 + N_SOFTMAX;   // TMA warp, MMA warp, 4 softmax warps per part
 constexpr float RESCALE_STEP = 8.0f;    // log2 units the maximum may run ahead of the reference
 
 __device__ int g_status = 0;
@@ -49,15 +60,19 @@ struct Smem {
     uint64_t k_full[2], v_full[2], kv_empty[2];
     uint64_t s_full, s_empty, p_full, pv_done;
     uint32_t tmem_base;
-    float row_max[2][2][BM];                    // [tile parity][column half][row]: the halves' maxima of a row
-    float row_sum[2][BM];                       // [column half][row]: the halves' sums at the end
+    float row_max[2][PARTS][BM];                // [tile parity][part][row]: the parts' maxima of a row
+    float row_sum[PARTS][BM];                   // [part][row]: the parts' sums at the end
 };
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
-__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+// The bits of x rounded to bfloat16 precision (nearest, ties to even), low 16 bits zero; x finite, x >= 0.
+__device__ __forceinline__ uint32_t bf16_bits(float x) {
+    const uint32_t u = __float_as_uint(x);
+    return (u + 0x7FFFu + ((u >> 16) & 1u)) & 0xFFFF0000u;
+}
 // 2^x by the special-function unit (relative error about 2^-22; -inf gives 0).
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -87,8 +102,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(smem_u32(&sm.kv_empty[s]), 1);
         }
         mbar_init(smem_u32(&sm.s_full), 1);
-        mbar_init(smem_u32(&sm.s_empty), 256);
-        mbar_init(smem_u32(&sm.p_full), 256);
+        mbar_init(smem_u32(&sm.s_empty), N_SOFTMAX);
+        mbar_init(smem_u32(&sm.p_full), N_SOFTMAX);
         mbar_init(smem_u32(&sm.pv_done), 1);
         mbar_fence_init();
         prefetch_map(&map_q);
@@ -185,14 +200,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         __syncwarp();
     } else {
-        // ---------------------------------------------------------------- softmax: two threads per query row,
-        // each with 64 of the tile's 128 keys (and, at the end, 64 of the 128 output columns)
-        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        // ---------------------------------------------------------------- softmax: PARTS threads per query row,
+        // each with 128 / PARTS of the tile's 128 keys (and, at the end, as many of the 128 output columns).
+        // A warp reads the 32 lanes of tensor memory that its number modulo 4 names.
+        const int quarter = warp & 3, part = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         const int pos_r = pos0 + r;
         const bool row_ok = r < n_rows;
-        constexpr int NC = BN / 2;                        // columns of this thread
+        constexpr int NC = BN / PARTS;                    // columns of this thread
+        static_assert(NC % 32 == 0, "a thread reads whole chunks of 32 columns");
         float m_ref = -CUDART_INF_F, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
@@ -202,35 +219,36 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             float t[NC];
 #pragma unroll
             for (int c = 0; c < NC / 32; ++c)
-                ld32(tmem_s + lane_base + half * NC + c * 32, reinterpret_cast<uint32_t*>(t) + c * 32);
+                ld32(tmem_s + lane_base + part * NC + c * 32, reinterpret_cast<uint32_t*>(t) + c * 32);
             wait_ld();
             fence_before();
             mbar_arrive(smem_u32(&sm.s_empty));          // S may be overwritten by the next tile's product
-            const int kb = (tile_lo + j) * BN + half * NC;
+            const int kb = (tile_lo + j) * BN + part * NC;
             // Tiles that lie wholly inside every row's range (most of them) need no mask.
             const bool whole = n_rows == BM && (tile_lo + j) * BN + BN - 1 <= pos0 && (tile_lo + j) * BN + BN <= len &&
                                (window <= 0 || (tile_lo + j) * BN > pos_last - window);
+            // Maxima of the raw scores (the scale is positive: it is applied to the maximum, and to the scores
+            // inside the exponent's multiply-add).
             float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
             if (whole) {
 #pragma unroll
-                for (int c = 0; c < NC; ++c) {
-                    t[c] *= scale_log2;
-                    mx[c & 3] = fmaxf(mx[c & 3], t[c]);
-                }
+                for (int c = 0; c < NC; ++c) mx[c & 3] = fmaxf(mx[c & 3], t[c]);
             } else {
 #pragma unroll
                 for (int c = 0; c < NC; ++c) {
                     const int key = kb + c;
                     const bool vis = row_ok && key <= pos_r && key < len && (window <= 0 || key > pos_r - window);
-                    t[c] = vis ? t[c] * scale_log2 : -CUDART_INF_F;
+                    t[c] = vis ? t[c] : -CUDART_INF_F;
                     mx[c & 3] = fmaxf(mx[c & 3], t[c]);
                 }
             }
-            // The row's maximum over both halves.
-            const float m_mine = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-            sm.row_max[j & 1][half][r] = m_mine;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            const float m_tile = fmaxf(m_mine, sm.row_max[j & 1][half ^ 1][r]);
+            // The row's maximum over all parts.
+            const float m_mine = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
+            sm.row_max[j & 1][part][r] = m_mine;
+            asm volatile("bar.sync 1, %0;" ::"n"(N_SOFTMAX) : "memory");
+            float m_tile = m_mine;
+#pragma unroll
+            for (int q = 1; q < PARTS; ++q) m_tile = fmaxf(m_tile, sm.row_max[j & 1][(part + q) % PARTS][r]);
             // Move the reference only when the maximum has run ahead of it by more than the step.
             const bool need = m_tile > m_ref + RESCALE_STEP;      // also true for the first visible key (m_ref = -inf)
             const float corr = need ? ex2(m_ref - m_tile) : 1.0f;     // m_ref = -inf gives 0
@@ -240,37 +258,41 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (!ok) break;
                 fence_after();
 #pragma unroll 1
-                for (int c = 0; c < NC / 32; ++c) {               // this thread's half of the row of O
+                for (int c = 0; c < NC / 32; ++c) {               // this thread's part of the row of O
                     uint32_t o[32];
-                    ld32(tmem_o + lane_base + half * NC + c * 32, o);
+                    ld32(tmem_o + lane_base + part * NC + c * 32, o);
                     wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-                    st32(tmem_o + lane_base + half * NC + c * 32, o);
+                    st32(tmem_o + lane_base + part * NC + c * 32, o);
                 }
                 wait_st();
             }
             const float base = m_ref == -CUDART_INF_F ? 0.f : m_ref;
+            // The probabilities, rounded to bfloat16 and packed in pairs, while the last tile's product with V
+            // still runs.  The sum runs over them as the product will see them.
+            // Rounded by integer arithmetic (nearest, ties to even): the values are finite and not negative,
+            // and the conversion instructions would share a pipe with the exponentials.
+            float sums[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t pk[NC / 2];
+#pragma unroll
+            for (int c = 0; c < NC / 2; ++c) {
+                const uint32_t b0 = bf16_bits(ex2(fmaf(t[2 * c], scale_log2, -base)));
+                const uint32_t b1 = bf16_bits(ex2(fmaf(t[2 * c + 1], scale_log2, -base)));
+                sums[c & 3] += __uint_as_float(b0) + __uint_as_float(b1);
+                pk[c] = __byte_perm(b0, b1, 0x7632);              // low half: b0's upper 16 bits, high half: b1's
+            }
             if (j > 0) {
                 LQ_WAIT(sm.pv_done, (j - 1) & 1, 8);              // the last product has read P
                 if (!ok) break;
             }
-            // Row r of this half's panel of P: 8 pieces of 8 keys; piece c lies at piece (c ^ (r % 8)) of the row.
-            // The sum runs over the probabilities as the product will see them (rounded to bfloat16).
-            float sums[4] = {0.f, 0.f, 0.f, 0.f};
+            // Row r of P: panels of 64 keys, 8 pieces of 8 keys each; piece q of a row lies at piece (q ^ (r % 8)).
+            uint8_t* prow = sm.p[(part * NC) / 64] + (r >> 3) * 1024 + (r & 7) * 128;
+            const int piece0 = ((part * NC) % 64) / 8;
 #pragma unroll
-            for (int c = 0; c < NC / 8; ++c) {
-                uint32_t pk[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float p0 = round_bf16(ex2(t[8 * c + 2 * i] - base));
-                    const float p1 = round_bf16(ex2(t[8 * c + 2 * i + 1] - base));
-                    sums[i] += p0 + p1;
-                    pk[i] = pack2(p0, p1);
-                }
-                uint8_t* dst = sm.p[half] + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
-                *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            }
+            for (int c = 0; c < NC / 8; ++c)
+                *reinterpret_cast<uint4*>(prow + (((piece0 + c) ^ (r & 7)) << 4)) =
+                    make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
             l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
             fence_async_shared();
             fence_before();
@@ -281,14 +303,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         if (ok) {
             fence_after();
-            sm.row_sum[half][r] = l;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            const float inv = 1.0f / (sm.row_sum[0][r] + sm.row_sum[1][r]);
-            __nv_bfloat16* orow = out + ((size_t)(row0 + r) * H + h) * HD + half * NC;
+            sm.row_sum[part][r] = l;
+            asm volatile("bar.sync 1, %0;" ::"n"(N_SOFTMAX) : "memory");
+            float total = 0.f;
+#pragma unroll
+            for (int q = 0; q < PARTS; ++q) total += sm.row_sum[q][r];
+            const float inv = 1.0f / total;
+            __nv_bfloat16* orow = out + ((size_t)(row0 + r) * H + h) * HD + part * NC;
 #pragma unroll 1
             for (int c = 0; c < NC / 32; ++c) {
                 uint32_t o[32];
-                ld32(tmem_o + lane_base + half * NC + c * 32, o);
+                ld32(tmem_o + lane_base + part * NC + c * 32, o);
                 wait_ld();
                 if (row_ok) {
 #pragma unroll
