@@ -239,11 +239,17 @@ def _norm_in(a):
 PREFETCH_BYTES = int(float(os.environ.get("LQ_PREFETCH_MB", "8")) * (1 << 20))   # of the weights read next; 0: none
 
 
-def _next(next_w):
+# The same, asked by the decode attention, which leaves HBM a third idle: all of a 34 MB output projection
+# (measured: a decode step 0.8 % shorter than with 8 MB).
+PREFETCH_BYTES_ATTN = int(float(os.environ.get("LQ_PREFETCH_ATTN_MB", "48")) * (1 << 20))
+
+
+def _next(next_w, limit=None):
     """(pointer, bytes) of the piece of the next weights to ask into L2."""
-    if next_w is None or PREFETCH_BYTES <= 0:
+    limit = PREFETCH_BYTES if limit is None else limit
+    if next_w is None or limit <= 0:
         return None, 0
-    return _p(next_w), min(PREFETCH_BYTES, next_w.numel() * next_w.element_size())
+    return _p(next_w), min(limit, next_w.numel() * next_w.element_size())
 
 
 def gemm_skinny(a, w: torch.Tensor, epi: int, residual: torch.Tensor | None = None,
@@ -438,7 +444,7 @@ def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq,
                                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                     c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_long,
                                                     c_int, c_void_p])
-    next_p, next_n = _next(next_w)
+    next_p, next_n = _next(next_w, PREFETCH_BYTES_ATTN)
     _check(fn(_p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0), _p(tok_pos),
               _p(tok_seq), _p(slots), _p(part_o), _p(part_ml), _p(counters), _p(out), T, H, Hkv, hd, page_size,
               float(scale), int(window or 0), n_splits, next_p, next_n, int(early_loads), _stream()), "attn_decode",
