@@ -24,6 +24,40 @@ def test_whole_sequence_matches_plain(tmp_path, name, dtype):
     assert eng.cache.pages_in_use() == 0
 
 
+UNUSUAL = {
+    # a width that is no multiple of 8: the bfloat16 products take the plain kernel
+    "width 100": dict(hidden_size=100, num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=5, head_dim=16,
+                      intermediate_size=150, vocab_size=333, rms_norm_eps=1e-6),
+    # a head size between the templates of the tensor-core attention kernels
+    "head 96": dict(hidden_size=192, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2, head_dim=96,
+                    intermediate_size=344, vocab_size=1001),
+    # a head size above 128: the plain attention kernel
+    "head 160": dict(hidden_size=320, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1, head_dim=160,
+                     intermediate_size=520, vocab_size=777, tie_word_embeddings=True),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", sorted(UNUSUAL))
+def test_sizes_that_the_fast_kernels_do_not_take(tmp_path, case, dtype):
+    """Whole and with the last tokens one by one: every size the configuration allows gives the right
+    result, through whichever kernel takes it."""
+    from longbow_quarrel_b200.engine import Engine
+    overrides = {"max_position_embeddings": 512, **UNUSUAL[case]}
+    folder = make_model_folder(tmp_path, "A", seed=4, overrides=overrides)
+    eng = Engine.from_pretrained(folder, dtype=dtype, max_tokens=512)
+    tokens = random_tokens(150, UNUSUAL[case]["vocab_size"], 5)
+    ref = plain_logits(folder, tokens)
+    slot = eng.new_sequence()
+    whole = eng.step([(slot, tokens)], want=[list(range(150))]).cpu().numpy()
+    eng.end_sequence(slot)
+    slot = eng.new_sequence()
+    eng.step([(slot, tokens[:118])], want=[[]])
+    tail = np.stack([eng.step([(slot, [t])]).cpu().numpy()[0] for t in tokens[118:]])
+    eng.end_sequence(slot)
+    assert rel_err(whole, ref) < TOL[dtype] and rel_err(tail, ref[118:]) < TOL[dtype]
+
+
 def test_weights_stored_in_32_bit_stay_32_bit(tmp_path):
     """A checkpoint stored in float32 is read as float32: the 32-bit path then agrees with the
     plain implementation on weights that bfloat16 could not hold."""
