@@ -13,7 +13,9 @@
 // block still waits (bounded) for its copies in flight, frees its tensor memory and ends.
 //
 // Epilogues: bfloat16 store; float32 store; float32 residual add in place; SwiGLU over
-// weight rows interleaved in blocks of 8 (8 gate rows, then their 8 up rows).
+// weight rows interleaved in blocks of 8 (8 gate rows, then their 8 up rows); q/k/v (head sizes 64
+// and 128): q and k rotated by the cos/sin tables at each row's position, q stored, k and v written
+// into the row's cache page -- no rotation kernel and no buffer of unrotated q/k/v in between.
 //
 // Few rows and a narrow weight give fewer tiles than SMs, and the product is then bound by
 // reading W: the contraction is cut into `splits` ranges, a block's piece of work is (tile, range),
@@ -29,6 +31,7 @@
 #define EPI_F32 1
 #define EPI_RESID 2
 #define EPI_SWIGLU 3
+#define EPI_QKV 4       // q, k, v rows: rotate q and k, store k and v into the cache pages
 
 namespace {
 
@@ -199,11 +202,65 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], void* Cout,
     }
 }
 
+// What the q/k/v epilogue needs beside the product: where each row stands and where its cache page is.
+// W holds H query heads, then Hkv key heads, then Hkv value heads, hd rows each.
+struct QkvArgs {
+    const float* cos_t;       // [positions, hd / 2] or null (no rotation)
+    const float* sin_t;
+    const int* tok_pos;
+    const int* tok_seq;
+    const int* slots;
+    const int* page_table;
+    __nv_bfloat16* k_pages;
+    __nv_bfloat16* v_pages;
+    int pt_stride, H, Hkv, hd, page_size;
+};
+
+// Where elements j .. of head `head` of row m go: q_out, or the row's place in a cache page.
+__device__ __forceinline__ __nv_bfloat16* qkv_dest(const QkvArgs& q, __nv_bfloat16* q_out, int m, int head, int pos) {
+    if (head < q.H) return q_out + ((size_t)m * q.H + head) * q.hd;
+    const int kvh = (head - q.H) % q.Hkv;
+    __nv_bfloat16* pages = head < q.H + q.Hkv ? q.k_pages : q.v_pages;
+    const int page = q.page_table[(size_t)q.slots[q.tok_seq[m]] * q.pt_stride + pos / q.page_size];
+    return pages + (((size_t)page * q.Hkv + kvh) * q.page_size + pos % q.page_size) * q.hd;
+}
+
+// 32 elements j0 .. j0+31 of a head's first half (a) and their partners in the second half (b) of one row:
+// rotated (heads of q and k, when there are tables) and stored at dst + j0 and dst + half + j0.
+__device__ __forceinline__ void store_qkv_pair(const uint32_t (&a)[32], const uint32_t (&b)[32], __nv_bfloat16* dst,
+                                               const float* cos_row, const float* sin_row, int j0, int half) {
+    uint4* lo = reinterpret_cast<uint4*>(dst + j0);
+    uint4* hi = reinterpret_cast<uint4*>(dst + half + j0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float x0[8], x1[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { x0[e] = __uint_as_float(a[8 * i + e]); x1[e] = __uint_as_float(b[8 * i + e]); }
+        if (cos_row) {
+#pragma unroll
+            for (int e4 = 0; e4 < 2; ++e4) {
+                const float4 c = reinterpret_cast<const float4*>(cos_row + j0)[2 * i + e4];
+                const float4 sn = reinterpret_cast<const float4*>(sin_row + j0)[2 * i + e4];
+                const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float y0 = x0[4 * e4 + e] * cc[e] - x1[4 * e4 + e] * ss[e];
+                    const float y1 = x0[4 * e4 + e] * ss[e] + x1[4 * e4 + e] * cc[e];
+                    x0[4 * e4 + e] = y0;
+                    x1[4 * e4 + e] = y1;
+                }
+            }
+        }
+        lo[i] = make_uint4(pack2(x0[0], x0[1]), pack2(x0[2], x0[3]), pack2(x0[4], x0[5]), pack2(x0[6], x0[7]));
+        hi[i] = make_uint4(pack2(x1[0], x1[1]), pack2(x1[2], x1[3]), pack2(x1[4], x1[5]), pack2(x1[6], x1[7]));
+    }
+}
+
 // ------------------------------------------------------------------ the kernel
 template <int BN, int STAGES, int EPI, int AROWS>
 __global__ void __launch_bounds__(N_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               void* Cout, const float* residual, int M, int N, int K, int splits) {
+               void* Cout, const float* residual, int M, int N, int K, int splits, const QkvArgs qkv) {
     extern __shared__ uint8_t smem_raw[];
     using S = Smem<BN, STAGES, AROWS>;
     S& sm = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -304,12 +361,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int m = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
             const int n_lim = n0 + BN < N ? n0 + BN : N;
+            if (EPI == EPI_QKV) {
+                // The tile holds whole heads (BN is a multiple of hd); a head's halves are hd / 2 = 32 or 64 columns.
+                const int hd = qkv.hd, half = hd >> 1;
+                const int pos = m < M ? qkv.tok_pos[m] : 0;
 #pragma unroll 1
-            for (int c = 0; c < (BN + 31) / 32; ++c) {      // a last half chunk reads columns that are not stored
-                uint32_t r[32];
-                tc_ld32(taddr + c * 32, r);
-                tc_wait_ld();
-                store_chunk<EPI>(r, dst, residual, m, n0 + c * 32, M, N, n_lim);
+                for (int col = 0; col < BN && n0 + col < N; col += hd) {
+                    const int head = (n0 + col) / hd;
+                    const bool rotate = qkv.cos_t != nullptr && head < qkv.H + qkv.Hkv;
+                    __nv_bfloat16* row = m < M ? qkv_dest(qkv, (__nv_bfloat16*)Cout, m, head, pos) : nullptr;
+#pragma unroll 1
+                    for (int j0 = 0; j0 < half; j0 += 32) {
+                        uint32_t a[32], b[32];
+                        tc_ld32(taddr + col + j0, a);
+                        tc_ld32(taddr + col + half + j0, b);
+                        tc_wait_ld();
+                        if (m < M)
+                            store_qkv_pair(a, b, row, rotate ? qkv.cos_t + (size_t)pos * half : nullptr,
+                                           rotate ? qkv.sin_t + (size_t)pos * half : nullptr, j0, half);
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < (BN + 31) / 32; ++c) {      // a last half chunk reads columns that are not stored
+                    uint32_t r[32];
+                    tc_ld32(taddr + c * 32, r);
+                    tc_wait_ld();
+                    store_chunk<EPI>(r, dst, residual, m, n0 + c * 32, M, N, n_lim);
+                }
             }
             tc_fence_before();
             __syncwarp();
@@ -329,10 +408,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // One thread makes four neighbouring outputs.
 template <int EPI>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int splits, void* Cout,
-                                                            const float* residual, int M, int N) {
+                                                            const float* residual, int M, int N, const QkvArgs qkv) {
     pdl_launch_dependents();
     pdl_wait();
-    const int NO = EPI == EPI_SWIGLU ? N >> 1 : N;          // output columns
+    const int NO = (EPI == EPI_SWIGLU || EPI == EPI_QKV) ? N >> 1 : N;    // output columns (for q/k/v: pairs)
     const int groups = (NO + 3) >> 2;
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long)M * groups) return;
@@ -355,6 +434,30 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
         }
     };
     float v[4];
+    if (EPI == EPI_QKV) {
+        // pairs c..c+3 of one head: elements j..j+3 of its first half and their partners in the second half
+        const int hd = qkv.hd, half = hd >> 1;
+        const int head = c / half, j = c % half;
+        float u[4];
+        sum4(head * hd + j, v);
+        sum4(head * hd + half + j, u);
+        const int pos = qkv.tok_pos[m];
+        if (qkv.cos_t && head < qkv.H + qkv.Hkv) {
+            const float4 cs = *reinterpret_cast<const float4*>(qkv.cos_t + (size_t)pos * half + j);
+            const float4 sn = *reinterpret_cast<const float4*>(qkv.sin_t + (size_t)pos * half + j);
+            const float cc[4] = {cs.x, cs.y, cs.z, cs.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float y0 = v[i] * cc[i] - u[i] * ss[i], y1 = v[i] * ss[i] + u[i] * cc[i];
+                v[i] = y0;
+                u[i] = y1;
+            }
+        }
+        __nv_bfloat16* row = qkv_dest(qkv, (__nv_bfloat16*)Cout, m, head, pos);
+        *reinterpret_cast<uint2*>(row + j) = make_uint2(pack2(v[0], v[1]), pack2(v[2], v[3]));
+        *reinterpret_cast<uint2*>(row + half + j) = make_uint2(pack2(u[0], u[1]), pack2(u[2], u[3]));
+        return;
+    }
     if (EPI == EPI_SWIGLU) {
         // outputs c..c+3 lie in one block of 8: their gate columns and, 8 further, their up columns
         const int gcol = (c >> 3) * 16 + (c & 7);
@@ -379,11 +482,12 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
 }
 
 template <int EPI>
-int launch_reduce(const float* part, int splits, void* C, const float* residual, int M, int N, cudaStream_t stream) {
-    const int NO = EPI == EPI_SWIGLU ? N >> 1 : N;
+int launch_reduce(const float* part, int splits, void* C, const float* residual, int M, int N, const QkvArgs& qkv,
+                  cudaStream_t stream) {
+    const int NO = (EPI == EPI_SWIGLU || EPI == EPI_QKV) ? N >> 1 : N;
     const long threads = (long)M * ((NO + 3) >> 2);
     return launch_pdl(splitk_reduce_kernel<EPI>, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, stream, part, splits,
-                      C, residual, M, N);
+                      C, residual, M, N, qkv);
 }
 
 // ------------------------------------------------------------------ host side
@@ -419,7 +523,7 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) 
 
 template <int BN, int STAGES, int EPI, int AROWS>
 int launch_epi(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const float* residual, int M, int N, int K,
-               int n_sms, int splits, cudaStream_t stream) {
+               int n_sms, int splits, const QkvArgs& qkv, cudaStream_t stream) {
     constexpr size_t smem = sizeof(Smem<BN, STAGES, AROWS>) + 1024;
     static_assert(smem <= 232448, "more shared memory than a block may have");
     static bool configured = false;
@@ -431,35 +535,39 @@ int launch_epi(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const floa
     int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * splits;
     int grid = tiles < n_sms ? tiles : n_sms;
     return launch_pdl(gemm_tc_kernel<BN, STAGES, EPI, AROWS>, dim3(grid), dim3(N_THREADS), smem, stream, ma, mb, C, residual, M, N, K,
-                      splits);
+                      splits, qkv);
 }
 
 // ALL: every epilogue; otherwise only the two that products with many columns have (SwiGLU, float32 store).
 template <int BN, int STAGES, int AROWS = BM, bool ALL = true>
 int launch_bn(const void* A, const void* W, void* C, const float* residual, int M, int N, int K, int epi, int n_sms,
-              int splits, float* scratch, cudaStream_t stream) {
+              int splits, float* scratch, cudaStream_t stream, const QkvArgs& qkv = QkvArgs{}) {
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, M, K, AROWS);
     if (rc != LQ_OK) return rc;
     rc = make_map(&mb, W, N, K, BN);
     if (rc != LQ_OK) return rc;
     if (splits > 1) {
-        rc = launch_epi<BN, STAGES, EPI_F32, AROWS>(ma, mb, scratch, nullptr, M, N, K, n_sms, splits, stream);
+        rc = launch_epi<BN, STAGES, EPI_F32, AROWS>(ma, mb, scratch, nullptr, M, N, K, n_sms, splits, QkvArgs{}, stream);
         if (rc != LQ_OK) return rc;
         switch (epi) {
-            case EPI_BF16: return launch_reduce<EPI_BF16>(scratch, splits, C, residual, M, N, stream);
-            case EPI_F32: return launch_reduce<EPI_F32>(scratch, splits, C, residual, M, N, stream);
-            case EPI_RESID: return launch_reduce<EPI_RESID>(scratch, splits, C, residual, M, N, stream);
-            case EPI_SWIGLU: return launch_reduce<EPI_SWIGLU>(scratch, splits, C, residual, M, N, stream);
+            case EPI_BF16: return launch_reduce<EPI_BF16>(scratch, splits, C, residual, M, N, qkv, stream);
+            case EPI_F32: return launch_reduce<EPI_F32>(scratch, splits, C, residual, M, N, qkv, stream);
+            case EPI_RESID: return launch_reduce<EPI_RESID>(scratch, splits, C, residual, M, N, qkv, stream);
+            case EPI_SWIGLU: return launch_reduce<EPI_SWIGLU>(scratch, splits, C, residual, M, N, qkv, stream);
+            case EPI_QKV: return launch_reduce<EPI_QKV>(scratch, splits, C, residual, M, N, qkv, stream);
         }
         return LQ_BAD_DTYPE;
     }
-    if constexpr (ALL) {
-        if (epi == EPI_BF16) return launch_epi<BN, STAGES, EPI_BF16, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
-        if (epi == EPI_RESID) return launch_epi<BN, STAGES, EPI_RESID, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
+    if constexpr (ALL && (BN == 128 || BN == 256)) {
+        if (epi == EPI_QKV) return launch_epi<BN, STAGES, EPI_QKV, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, qkv, stream);
     }
-    if (epi == EPI_F32) return launch_epi<BN, STAGES, EPI_F32, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
-    if (epi == EPI_SWIGLU) return launch_epi<BN, STAGES, EPI_SWIGLU, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, stream);
+    if constexpr (ALL) {
+        if (epi == EPI_BF16) return launch_epi<BN, STAGES, EPI_BF16, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, qkv, stream);
+        if (epi == EPI_RESID) return launch_epi<BN, STAGES, EPI_RESID, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, qkv, stream);
+    }
+    if (epi == EPI_F32) return launch_epi<BN, STAGES, EPI_F32, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, qkv, stream);
+    if (epi == EPI_SWIGLU) return launch_epi<BN, STAGES, EPI_SWIGLU, AROWS>(ma, mb, C, residual, M, N, K, n_sms, 1, qkv, stream);
     return LQ_BAD_DTYPE;
 }
 
@@ -487,13 +595,9 @@ int plan_splits(int M, int N, int K) {
     return s < 1 ? 1 : (int)s;
 }
 
-}  // namespace
-
-// A [M, K] and W [N, K] bfloat16, row-major, 16-byte aligned, K % 8 == 0.
-// For EPI_SWIGLU, N counts the interleaved gate and up rows (N % 16 == 0) and C is [M, N / 2].
-// scratch: lq_gemm_tc_splits(M, N, K) * M * N floats when that number is above 1 (else unused).
-LQ_EXPORT int lq_gemm_tc(const void* A, const void* W, void* C, const float* residual, int M, int N, int K, int epi,
-                         float* scratch, cudaStream_t stream) {
+// The choice of tile shape and of ranges of K for a product, and its launch.
+int gemm_tc_dispatch(const void* A, const void* W, void* C, const float* residual, int M, int N, int K, int epi,
+                            float* scratch, const QkvArgs& qkv, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return LQ_OK;
     if (K <= 0 || K % 8 != 0) return LQ_BAD_SIZE;
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return LQ_BAD_SIZE;
@@ -503,8 +607,8 @@ LQ_EXPORT int lq_gemm_tc(const void* A, const void* W, void* C, const float* res
     const int splits = plan_splits(M, N, K);
     if (splits > 1) {
         if (!scratch || ((uintptr_t)scratch & 15)) return LQ_BAD_SIZE;
-        if (M <= 64) return launch_bn<256, 5, 64>(A, W, C, residual, M, N, K, epi, n_sms, splits, scratch, stream);
-        return launch_bn<256, 4>(A, W, C, residual, M, N, K, epi, n_sms, splits, scratch, stream);
+        if (M <= 64) return launch_bn<256, 5, 64>(A, W, C, residual, M, N, K, epi, n_sms, splits, scratch, stream, qkv);
+        return launch_bn<256, 4>(A, W, C, residual, M, N, K, epi, n_sms, splits, scratch, stream, qkv);
     }
     long tiles256 = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
     if (M <= 64) {
@@ -513,7 +617,7 @@ LQ_EXPORT int lq_gemm_tc(const void* A, const void* W, void* C, const float* res
         // one round instead of 224 tiles of 128 in two.  The two epilogues that products with many columns have
         // choose among all widths; the others (q/k/v, residual) have few columns in the models at hand and take
         // 256 or 128.  As many stages as the shared memory holds.
-        int best = tiles256 >= n_sms ? 256 : 128;
+        int best = (tiles256 >= n_sms || epi == EPI_QKV) ? 256 : 128;
         if (epi == EPI_SWIGLU || epi == EPI_F32) {
             static const int widths[] = {256, 224, 208, 192, 176, 160, 144, 128};
             long best_cost = -1;
@@ -522,7 +626,7 @@ LQ_EXPORT int lq_gemm_tc(const void* A, const void* W, void* C, const float* res
                 if (best_cost < 0 || cost < best_cost) { best = w; best_cost = cost; }
             }
         }
-#define LQ_W(w, st, all) case w: return launch_bn<w, st, 64, all>(A, W, C, residual, M, N, K, epi, n_sms, 1, nullptr, stream)
+#define LQ_W(w, st, all) case w: return launch_bn<w, st, 64, all>(A, W, C, residual, M, N, K, epi, n_sms, 1, nullptr, stream, qkv)
         switch (best) {
             LQ_W(256, 5, true); LQ_W(224, 6, false); LQ_W(208, 6, false); LQ_W(192, 7, false); LQ_W(176, 7, false);
             LQ_W(160, 8, false); LQ_W(144, 8, false); LQ_W(128, 9, true);
@@ -530,8 +634,36 @@ LQ_EXPORT int lq_gemm_tc(const void* A, const void* W, void* C, const float* res
 #undef LQ_W
     }
     // Many rows: wide tiles when they still fill the GPU, narrower ones otherwise.
-    if (tiles256 >= n_sms) return launch_bn<256, 4>(A, W, C, residual, M, N, K, epi, n_sms, 1, nullptr, stream);
-    return launch_bn<128, 6>(A, W, C, residual, M, N, K, epi, n_sms, 1, nullptr, stream);
+    if (tiles256 >= n_sms) return launch_bn<256, 4>(A, W, C, residual, M, N, K, epi, n_sms, 1, nullptr, stream, qkv);
+    return launch_bn<128, 6>(A, W, C, residual, M, N, K, epi, n_sms, 1, nullptr, stream, qkv);
+}
+
+}  // namespace
+
+// A [M, K] and W [N, K] bfloat16, row-major, 16-byte aligned, K % 8 == 0.
+// For EPI_SWIGLU, N counts the interleaved gate and up rows (N % 16 == 0) and C is [M, N / 2].
+// scratch: lq_gemm_tc_splits(M, N, K) * M * N floats when that number is above 1 (else unused).
+LQ_EXPORT int lq_gemm_tc(const void* A, const void* W, void* C, const float* residual, int M, int N, int K, int epi,
+                         float* scratch, cudaStream_t stream) {
+    if (epi < EPI_BF16 || epi > EPI_SWIGLU) return LQ_BAD_DTYPE;
+    return gemm_tc_dispatch(A, W, C, residual, M, N, K, epi, scratch, QkvArgs{}, stream);
+}
+
+// The q/k/v projection with its epilogue fused: X [M, K] . W^T for W [(H + 2 Hkv) hd, K]; q and k are rotated
+// by the cos/sin tables at each row's position (tables null: no rotation); q goes to q_out [M, H hd], k and v go
+// into the row's cache page.  hd is 64 or 128.  scratch: lq_gemm_tc_splits(M, (H + 2 Hkv) hd, K) * M * N floats
+// when that number is above 1.
+LQ_EXPORT int lq_gemm_tc_qkv(const void* X, const void* W, void* q_out, int M, int K, const float* cos_t,
+                             const float* sin_t, const int* tok_pos, const int* tok_seq, const int* slots,
+                             const int* page_table, int pt_stride, void* k_pages, void* v_pages, int H, int Hkv, int hd,
+                             int page_size, float* scratch, cudaStream_t stream) {
+    if (M <= 0) return LQ_OK;
+    if ((hd != 64 && hd != 128) || H <= 0 || Hkv <= 0 || page_size <= 0) return LQ_BAD_SIZE;
+    if (((uintptr_t)q_out & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15)) return LQ_BAD_SIZE;
+    if (cos_t && (((uintptr_t)cos_t & 15) || ((uintptr_t)sin_t & 15))) return LQ_BAD_SIZE;
+    const QkvArgs a{cos_t, sin_t, tok_pos, tok_seq, slots, page_table, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages,
+                    pt_stride, H, Hkv, hd, page_size};
+    return gemm_tc_dispatch(X, W, q_out, nullptr, M, (H + 2 * Hkv) * hd, K, EPI_QKV, scratch, a, stream);
 }
 
 LQ_EXPORT int lq_gemm_tc_splits(int M, int N, int K) {

@@ -352,6 +352,32 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, epi: int, residual: torch.Tensor |
     return out
 
 
+def gemm_tc_qkv(a: torch.Tensor, w: torch.Tensor, cos, sin, tok_pos, tok_seq, slots, page_table, k_pages, v_pages,
+                H: int, Hkv: int, hd: int, page_size: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """The q/k/v projection of many rows (or of 17 and more decoded tokens) with rotation and cache
+    write in its epilogue, on the tcgen05 kernel: returns the rotated q [M, H*hd]; the rotated k and v
+    are stored in each row's cache page.  head_dim 64 or 128."""
+    M, K = a.shape
+    N = (H + 2 * Hkv) * hd
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc_qkv takes bfloat16 inputs and cache")
+    if tuple(w.shape) != (N, K):
+        raise KernelError(f"gemm_tc_qkv: weight shape {tuple(w.shape)} is not [(H + 2 Hkv) hd, K]")
+    if K % 8 or hd not in (64, 128):
+        raise KernelError(f"gemm_tc_qkv: width {K} (multiple of 8), head_dim {hd} (64 or 128)")
+    if out is None:
+        out = torch.empty((M, H * hd), dtype=torch.bfloat16, device=a.device)
+    splits = int(_fn("gemm_tc", "lq_gemm_tc_splits", [c_int, c_int, c_int])(M, N, K))
+    scratch = torch.empty(splits * M * N, dtype=torch.float32, device=a.device) if splits > 1 else None
+    fn = _fn("gemm_tc", "lq_gemm_tc_qkv", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                                           c_int, c_void_p, c_void_p])
+    _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), M, K, _p(cos), _p(sin), _p(tok_pos), _p(tok_seq),
+              _p(slots), _p(page_table), page_table.stride(0), _p(k_pages), _p(v_pages), H, Hkv, hd, page_size,
+              _p(scratch), _stream()), "gemm_tc_qkv", 2 if splits > 1 else 1)
+    return out
+
+
 def gemm_tc_status() -> int:
     """0, or the code of a wait inside gemm_tc that gave up (after a synchronize)."""
     fn = build.load("gemm_tc").lq_gemm_tc_status

@@ -69,15 +69,18 @@ class Attention(Mixer):
     def forward(self, h, ctx: StepContext, cache_view, residual, writes_cache: bool = True, emit=None):
         store = self.own_kv and writes_cache
         tables = self.position.tables() if self.position is not None else None
-        if (store and h.dtype == torch.bfloat16 and self.w_qkv.tensor.dtype == torch.bfloat16
-                and h.shape[0] <= ops.SKINNY_BEST_ROWS and self.D % 8 == 0 and cache_view.k_pages.dtype == torch.bfloat16
-                and (self.position is None or tables is not None)):
-            # Few tokens: projection, rotation and cache write are one kernel.
+        fused = (store and h.dtype == torch.bfloat16 and self.w_qkv.tensor.dtype == torch.bfloat16 and self.D % 8 == 0
+                 and cache_view.k_pages.dtype == torch.bfloat16 and (self.position is None or tables is not None))
+        few = h.shape[0] <= ops.SKINNY_BEST_ROWS
+        if fused and (few or (self.hd in (64, 128) and not isinstance(h, ops.NormedRows))):
+            # Projection, rotation and cache write are one kernel (for few tokens the one that streams the
+            # weights through registers, else the tcgen05 one).
             cos, sin = tables if tables is not None else (None, None)
             linear.note(self.w_qkv)
-            q = ops.gemm_skinny_qkv(h, self.w_qkv.tensor, cos, sin, ctx.tok_pos, ctx.tok_seq, ctx.slots,
-                                    cache_view.page_table, cache_view.k_pages, cache_view.v_pages, self.H, self.Hkv,
-                                    self.hd, cache_view.page_size)
+            qkv_kernel = ops.gemm_skinny_qkv if few else ops.gemm_tc_qkv
+            q = qkv_kernel(h, self.w_qkv.tensor, cos, sin, ctx.tok_pos, ctx.tok_seq, ctx.slots,
+                           cache_view.page_table, cache_view.k_pages, cache_view.v_pages, self.H, self.Hkv,
+                           self.hd, cache_view.page_size)
             out = attention_kernels.attention(q, cache_view, ctx, self.H, self.Hkv, self.hd, self.scale, self.window,
                                               next_w=self.w_o.tensor)
             return self._project(out, residual, emit)

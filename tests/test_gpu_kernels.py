@@ -553,6 +553,47 @@ def test_gemm_skinny_qkv_rotates_and_stores(M, H, Hkv, hd, rotate):
         assert bool((same | touched).all())          # nothing else in the cache was written
 
 
+@pytest.mark.parametrize("M,K", [(17, 4096), (64, 328), (300, 200), (1100, 1024)])
+@pytest.mark.parametrize("H,Hkv,hd,rotate", [(4, 2, 128, True), (6, 1, 64, True), (3, 3, 128, False)])
+def test_gemm_tc_qkv_rotates_and_stores(M, K, H, Hkv, hd, rotate):
+    """The fused projection of many rows (tiles, or ranges of K added by the second kernel) against
+    product, rotation and cache write done apart; rows of several sequences, some continuing."""
+    ops = _ops()
+    n_seq = 5
+    new = [M // n_seq + (1 if b < M % n_seq else 0) for b in range(n_seq)]
+    past = [0, 70, 3, 129, 64]
+    lens = [p + n for p, n in zip(past, new)]
+    case = PagedCase(lens, Hkv, hd, torch.bfloat16, seed=21)
+    k_before, v_before = case.k_pages.clone(), case.v_pages.clone()
+    a = _rand((M, K), torch.bfloat16, 90)
+    w = _rand(((H + 2 * Hkv) * hd, K), torch.bfloat16, 91, 0.1)
+    tok_seq = [b for b, n in enumerate(new) for _ in range(n)]
+    tok_pos = [past[b] + i for b, n in enumerate(new) for i in range(n)]
+    freqs = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)
+    ang = torch.arange(max(lens) + 1, dtype=torch.float64)[:, None] * freqs[None]
+    cos, sin = torch.cos(ang).float().to(DEV).contiguous(), torch.sin(ang).float().to(DEV).contiguous()
+    q = ops.gemm_tc_qkv(a, w, cos if rotate else None, sin if rotate else None, _ints(tok_pos), _ints(tok_seq),
+                        case.slots, case.table, case.k_pages, case.v_pages, H, Hkv, hd, 64)
+    torch.cuda.synchronize()
+    assert ops.gemm_tc_status() == 0
+    full = (a.float().double() @ w.float().double().T).reshape(M, H + 2 * Hkv, hd).cpu()
+    c = cos[torch.tensor(tok_pos)].double().cpu().unsqueeze(1) if rotate else 1.0
+    s = sin[torch.tensor(tok_pos)].double().cpu().unsqueeze(1) if rotate else 0.0
+    x0, x1 = full[:, :H + Hkv, :hd // 2], full[:, :H + Hkv, hd // 2:]
+    rot = torch.cat([x0 * c - x1 * s, x0 * s + x1 * c], dim=-1)
+    tol = _acc_tol(K) + 1e-6
+    _close(q.reshape(M, H, hd), rot[:, :H], tol, BF16_ULP)
+    touched = torch.zeros_like(case.k_pages, dtype=torch.bool)
+    pages = torch.tensor([int(case.table[case.slot_of[tok_seq[m]], tok_pos[m] // 64]) for m in range(M)])
+    offs = torch.tensor([p % 64 for p in tok_pos])
+    _close(case.k_pages[pages, :, offs], rot[:, H:], tol, BF16_ULP)
+    _close(case.v_pages[pages, :, offs], full[:, H + Hkv:], tol, BF16_ULP)
+    touched[pages, :, offs] = True
+    for pg, before in ((case.k_pages, k_before), (case.v_pages, v_before)):
+        same = (pg == before) | (pg.isnan() & before.isnan())
+        assert bool((same | touched).all())          # nothing else in the cache was written
+
+
 def _query_blocks128(new, past):
     out, row = [], 0
     for b, (n, p) in enumerate(zip(new, past)):
