@@ -6,6 +6,7 @@
     python -m longbow_quarrel_b200.kernels.microbench attn_prefill --tokens 2048
     python -m longbow_quarrel_b200.kernels.microbench step --batch 8 --context 4096 --layers 4
     python -m longbow_quarrel_b200.kernels.microbench prefill --tokens 2048 --layers 4
+    python -m longbow_quarrel_b200.kernels.microbench timeline --batch 8 --layers 6
 
 Each kernel is timed with CUDA events over `--iters` launches after `--warmup`, captured
 into one CUDA graph so that no host time lies between the launches (`--no-graph` launches
@@ -15,6 +16,10 @@ them from the host one by one); operands are rotated through enough copies to ex
 of `--batch` sequences to `--context` tokens with random keys and values (no prefill),
 and runs decode steps; with `--eager` the step's kernels are launched one by one instead
 of replaying a captured graph, which is what a launch-by-launch profile wants.
+`timeline` runs the same steps as captured graphs under the CUDA activity records of
+torch.profiler and prints, for each kind of kernel of the last step, how long it ran and how
+much later it ended than the kernel before it (kernels overlap through programmatic dependent
+launch, so the second number is what a kernel adds to the step).
 """
 from __future__ import annotations
 
@@ -168,7 +173,9 @@ def bench_attn_prefill(args) -> dict:
             "tflops": flops / ms / 1e9}
 
 
-def bench_step(args) -> dict:
+def _decode_setup(args, use_graphs: bool):
+    """A model of Llama-3.1-8B layer sizes whose cache holds random keys and values, and a
+    function that runs decode step i."""
     import numpy as np
 
     from ..engine import Engine
@@ -179,7 +186,7 @@ def bench_step(args) -> dict:
                                  original_max_position_embeddings=8192))
     B, C = args.batch, args.context
     eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=B * (C + 64), max_batch=B,
-                             max_context=C + 64, use_graphs=not args.eager)
+                             max_context=C + 64, use_graphs=use_graphs)
     for g in eng.cache.kv_groups:
         g.k_pages.normal_()
         g.v_pages.normal_()
@@ -193,9 +200,53 @@ def bench_step(args) -> dict:
 
     def run(i):
         eng.step([(s, [int(t)]) for s, t in zip(slots, feed[i])])
+    return run
+
+
+def bench_step(args) -> dict:
+    B, C = args.batch, args.context
+    run = _decode_setup(args, not args.eager)
     ms = _time(run, args.iters, args.warmup, graph=False)
     return {"kernel": "decode step", "batch": B, "context": C, "layers": args.layers, "graph": not args.eager,
             "ms": ms, "tokens_per_s": B / ms * 1e3}
+
+
+def bench_timeline(args) -> dict:
+    """Kernel records of the last of `--iters` decode steps: per kind of kernel the launches, the
+    mean run time, and the mean time by which it ended after the kernel before it."""
+    import re
+
+    from torch.profiler import ProfilerActivity, profile
+    run = _decode_setup(args, True)
+    for i in range(args.warmup):
+        run(i)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for i in range(args.iters):
+            run(args.warmup + i)
+        torch.cuda.synchronize()
+    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+          and not re.search("[Mm]emcpy|[Mm]emset", e.name)]
+    ev.sort(key=lambda e: e.time_range.start)
+    starts = [i for i, e in enumerate(ev) if e.name == ev[0].name]          # the step's first kernel runs once a step
+    last = ev[starts[-2]:starts[-1]] if len(starts) >= 2 else ev
+
+    def kind(name: str) -> str:
+        m = re.search(r"(\w+)_kernel<([^>]*)>", name)
+        return f"{m.group(1)}<{m.group(2)[:40]}>" if m else name[:60]
+    t0 = prev_end = last[0].time_range.start
+    kinds: dict = {}
+    for e in last:
+        k = kinds.setdefault(kind(e.name), dict(launches=0, run_us=0.0, adds_us=0.0))
+        k["launches"] += 1
+        k["run_us"] += e.time_range.end - e.time_range.start
+        k["adds_us"] += e.time_range.end - prev_end if e is not last[0] else e.time_range.end - t0
+        prev_end = max(prev_end, e.time_range.end)
+    for k in kinds.values():
+        k["run_us"] = round(k["run_us"] / k["launches"], 2)
+        k["adds_us"] = round(k["adds_us"] / k["launches"], 2)
+    return {"kernel": "decode step, kernel by kernel", "batch": args.batch, "context": args.context, "layers": args.layers,
+            "step_us": round(prev_end - t0, 1), "kinds": kinds}
 
 
 def bench_prefill(args) -> dict:
@@ -222,7 +273,7 @@ def bench_prefill(args) -> dict:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("what", choices=["gemm_skinny", "gemm_tc", "attn_decode", "attn_prefill", "attn_prefill_tc", "chain", "step",
-                                     "prefill"])
+                                     "prefill", "timeline"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -252,6 +303,8 @@ def main(argv=None) -> int:
         out = bench_attn_prefill(args)
     elif args.what == "prefill":
         out = bench_prefill(args)
+    elif args.what == "timeline":
+        out = bench_timeline(args)
     else:
         out = bench_step(args)
     print(json.dumps(out))
