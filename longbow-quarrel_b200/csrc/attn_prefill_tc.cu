@@ -1,5 +1,5 @@
 // Causal grouped-query attention of many query tokens over the paged cache on the
-// fifth-generation tensor cores (prefill, head_dim 128, pages of 64 keys).
+// fifth-generation tensor cores (prefill, head_dim 64 or 128, pages of 64 keys).
 //
 // A block takes 128 consecutive query tokens of one sequence and one query head and walks
 // over the keys in tiles of 128 (two cache pages).  Inside a block
@@ -41,20 +41,21 @@ namespace {
 
 constexpr int BM = 128;                 // query rows per block
 constexpr int BN = 128;                 // keys per tile
-constexpr int HD = 128;                 // head dimension
 constexpr int PAGE = 64;
 constexpr int PANEL = 128 * 128;        // bytes of a [128 rows, 64 elements] panel
-constexpr int PARTS = 2;                // softmax threads per query row: each has 128 / PARTS of a tile's keys
+constexpr int PARTS = 2;                // softmax threads per query row: each has 128 / PARTS of a tile's keys and HD / PARTS output columns
 constexpr int N_SOFTMAX = PARTS * BM;   // softmax threads
 constexpr int N_THREADS = 64 + N_SOFTMAX;   // TMA warp, MMA warp, 4 softmax warps per part
 constexpr float RESCALE_STEP = 8.0f;    // log2 units the maximum may run ahead of the reference
 
 __device__ int g_status = 0;
 
+// HD: the head dimension, 64 or 128: one or two panels of 64 elements.
+template <int HD>
 struct Smem {
-    alignas(1024) uint8_t q[2][PANEL];          // [d half][128 rows x 128 B]
-    alignas(1024) uint8_t k[2][2][PANEL];       // [stage][d half][128 keys x 128 B]
-    alignas(1024) uint8_t v[2][2][PANEL];       // [stage][d half][128 keys x 128 B]
+    alignas(1024) uint8_t q[HD / 64][PANEL];          // [d half][128 rows x 128 B]
+    alignas(1024) uint8_t k[2][HD / 64][PANEL];       // [stage][d half][128 keys x 128 B]
+    alignas(1024) uint8_t v[2][HD / 64][PANEL];       // [stage][d half][128 keys x 128 B]
     alignas(1024) uint8_t p[2][PANEL];          // [key half][128 rows x 128 B]
     alignas(8) uint64_t q_full;
     uint64_t k_full[2], v_full[2], kv_empty[2];
@@ -83,6 +84,7 @@ __device__ __forceinline__ float ex2(float x) {
 #define LQ_WAIT(bar, parity, code) \
     if (!mbar_wait(smem_u32(&(bar)), (parity))) { atomicExch(&g_status, (code)); ok = false; }
 
+template <int HD>
 __global__ void __launch_bounds__(N_THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table, int pt_stride,
@@ -90,7 +92,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const int* __restrict__ qb_row, const int* __restrict__ qb_rows, const int* __restrict__ qb_pos,
                        __nv_bfloat16* __restrict__ out, int H, int Hkv, int oob_row, float scale_log2, int window) {
     extern __shared__ uint8_t smem_raw[];
-    Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int DH = HD / 64;                  // panels of 64 elements along the head dimension
+    Smem<HD>& sm = *reinterpret_cast<Smem<HD>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr uint32_t TMEM_COLS = 256;          // S in columns 0..127, O in 128..255
 
@@ -133,8 +136,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
             bool ok = true;
-            mbar_expect_tx(smem_u32(&sm.q_full), 2 * PANEL);
-            for (int half = 0; half < 2; ++half)
+            mbar_expect_tx(smem_u32(&sm.q_full), DH * PANEL);
+            for (int half = 0; half < DH; ++half)
                 tma_load_2d(smem_u32(sm.q[half]), &map_q, h * HD + half * 64, row0, smem_u32(&sm.q_full));
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int s = j & 1;
@@ -146,12 +149,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     const int page = pg <= last_page ? pt[pg] : -1;
                     rows[i] = page >= 0 ? (page * Hkv + kvh) * PAGE : oob_row;   // out of range: TMA fills zeros
                 }
-                mbar_expect_tx(smem_u32(&sm.k_full[s]), 2 * PANEL);
-                for (int half = 0; half < 2; ++half)
+                mbar_expect_tx(smem_u32(&sm.k_full[s]), DH * PANEL);
+                for (int half = 0; half < DH; ++half)
                     for (int i = 0; i < 2; ++i)
                         tma_load_2d(smem_u32(sm.k[s][half]) + i * (PANEL / 2), &map_k, half * 64, rows[i], smem_u32(&sm.k_full[s]));
-                mbar_expect_tx(smem_u32(&sm.v_full[s]), 2 * PANEL);
-                for (int half = 0; half < 2; ++half)
+                mbar_expect_tx(smem_u32(&sm.v_full[s]), DH * PANEL);
+                for (int half = 0; half < DH; ++half)
                     for (int i = 0; i < 2; ++i)
                         tma_load_2d(smem_u32(sm.v[s][half]) + i * (PANEL / 2), &map_v, half * 64, rows[i], smem_u32(&sm.v_full[s]));
             }
@@ -201,15 +204,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         __syncwarp();
     } else {
         // ---------------------------------------------------------------- softmax: PARTS threads per query row,
-        // each with 128 / PARTS of the tile's 128 keys (and, at the end, as many of the 128 output columns).
+        // each with 128 / PARTS of the tile's 128 keys (and HD / PARTS of the output columns).
         // A warp reads the 32 lanes of tensor memory that its number modulo 4 names.
         const int quarter = warp & 3, part = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         const int pos_r = pos0 + r;
         const bool row_ok = r < n_rows;
-        constexpr int NC = BN / PARTS;                    // columns of this thread
-        static_assert(NC % 32 == 0, "a thread reads whole chunks of 32 columns");
+        constexpr int NC = BN / PARTS;                    // keys of a tile of this thread
+        constexpr int OC = HD / PARTS;                    // output columns of this thread
+        static_assert(NC % 32 == 0 && OC % 32 == 0, "a thread reads whole chunks of 32 columns");
         float m_ref = -CUDART_INF_F, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
@@ -258,13 +262,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (!ok) break;
                 fence_after();
 #pragma unroll 1
-                for (int c = 0; c < NC / 32; ++c) {               // this thread's part of the row of O
+                for (int c = 0; c < OC / 32; ++c) {               // this thread's part of the row of O
                     uint32_t o[32];
-                    ld32(tmem_o + lane_base + part * NC + c * 32, o);
+                    ld32(tmem_o + lane_base + part * OC + c * 32, o);
                     wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-                    st32(tmem_o + lane_base + part * NC + c * 32, o);
+                    st32(tmem_o + lane_base + part * OC + c * 32, o);
                 }
                 wait_st();
             }
@@ -309,11 +313,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
             for (int q = 0; q < PARTS; ++q) total += sm.row_sum[q][r];
             const float inv = 1.0f / total;
-            __nv_bfloat16* orow = out + ((size_t)(row0 + r) * H + h) * HD + part * NC;
+            __nv_bfloat16* orow = out + ((size_t)(row0 + r) * H + h) * HD + part * OC;
 #pragma unroll 1
-            for (int c = 0; c < NC / 32; ++c) {
+            for (int c = 0; c < OC / 32; ++c) {
                 uint32_t o[32];
-                ld32(tmem_o + lane_base + part * NC + c * 32, o);
+                ld32(tmem_o + lane_base + part * OC + c * 32, o);
                 wait_ld();
                 if (row_ok) {
 #pragma unroll
@@ -337,8 +341,33 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
 }  // namespace
 
-// q: [T, q_stride] bfloat16 rows whose first H*128 elements hold the query heads; out [T, H*128].
-// k_pages, v_pages: [n_pages, Hkv, 64, 128] bfloat16 of one cache entry, finite everywhere.
+namespace {
+template <int HD>
+int launch_hd(const void* q, int q_stride, int T, const void* k_pages, const void* v_pages, int n_pages,
+              const int* page_table, int pt_stride, const int* slots, const int* kv_len, const int* qb_seq,
+              const int* qb_row, const int* qb_rows, const int* qb_pos, void* out, int n_blocks, int H, int Hkv,
+              float scale, int window, cudaStream_t stream) {
+    CUtensorMap mq, mk, mv;
+    const long kv_rows = (long)n_pages * Hkv * PAGE;
+    int rc = make_map_bf16(&mq, q, T, q_stride, q_stride, BM);
+    if (rc == LQ_OK) rc = make_map_bf16(&mk, k_pages, kv_rows, HD, HD, PAGE);
+    if (rc == LQ_OK) rc = make_map_bf16(&mv, v_pages, kv_rows, HD, HD, PAGE);
+    if (rc != LQ_OK) return rc;
+    constexpr size_t smem = sizeof(Smem<HD>) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return lq_launch_status();
+        configured = true;
+    }
+    return launch_pdl(attn_prefill_tc_kernel<HD>, dim3(n_blocks * H), dim3(N_THREADS), smem, stream, mq, mk, mv, page_table,
+                      pt_stride, slots, kv_len, qb_seq, qb_row, qb_rows, qb_pos, (__nv_bfloat16*)out, H, Hkv,
+                      (int)kv_rows, scale * 1.4426950408889634f, window);
+}
+}  // namespace
+
+// q: [T, q_stride] bfloat16 rows whose first H*hd elements hold the query heads; out [T, H*hd].  hd is 64 or 128.
+// k_pages, v_pages: [n_pages, Hkv, 64, hd] bfloat16 of one cache entry, finite everywhere.
 // qb_*: the work list, n_blocks entries: sequence, first packed row, rows (<= 128), position of the first row.
 LQ_EXPORT int lq_attn_prefill_tc(const void* q, int q_stride, int T, const void* k_pages, const void* v_pages,
                                  int n_pages, const int* page_table, int pt_stride, const int* slots, const int* kv_len,
@@ -346,23 +375,12 @@ LQ_EXPORT int lq_attn_prefill_tc(const void* q, int q_stride, int T, const void*
                                  int n_blocks, int H, int Hkv, int hd, int page_size, float scale, int window,
                                  cudaStream_t stream) {
     if (n_blocks <= 0) return LQ_OK;
-    if (hd != HD || page_size != PAGE || H % Hkv || q_stride % 8 || ((uintptr_t)q & 15)) return LQ_BAD_SIZE;
-    CUtensorMap mq, mk, mv;
-    const long kv_rows = (long)n_pages * Hkv * PAGE;
-    int rc = make_map_bf16(&mq, q, T, q_stride, q_stride, BM);
-    if (rc == LQ_OK) rc = make_map_bf16(&mk, k_pages, kv_rows, HD, HD, PAGE);
-    if (rc == LQ_OK) rc = make_map_bf16(&mv, v_pages, kv_rows, HD, HD, PAGE);
-    if (rc != LQ_OK) return rc;
-    constexpr size_t smem = sizeof(Smem) + 1024;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return lq_launch_status();
-        configured = true;
-    }
-    return launch_pdl(attn_prefill_tc_kernel, dim3(n_blocks * H), dim3(N_THREADS), smem, stream, mq, mk, mv, page_table,
-                      pt_stride, slots, kv_len, qb_seq, qb_row, qb_rows, qb_pos, (__nv_bfloat16*)out, H, Hkv,
-                      (int)kv_rows, scale * 1.4426950408889634f, window);
+    if ((hd != 64 && hd != 128) || page_size != PAGE || H % Hkv || q_stride % 8 || ((uintptr_t)q & 15)) return LQ_BAD_SIZE;
+    if (hd == 64)
+        return launch_hd<64>(q, q_stride, T, k_pages, v_pages, n_pages, page_table, pt_stride, slots, kv_len, qb_seq, qb_row,
+                             qb_rows, qb_pos, out, n_blocks, H, Hkv, scale, window, stream);
+    return launch_hd<128>(q, q_stride, T, k_pages, v_pages, n_pages, page_table, pt_stride, slots, kv_len, qb_seq, qb_row,
+                          qb_rows, qb_pos, out, n_blocks, H, Hkv, scale, window, stream);
 }
 
 LQ_EXPORT int lq_attn_prefill_tc_status() {

@@ -411,12 +411,12 @@ def attn_prefill_tc(q: torch.Tensor, k_pages, v_pages, page_table, slots, kv_len
                     hd: int, page_size: int, scale: float, window: int | None,
                     out: torch.Tensor | None = None) -> torch.Tensor:
     """attn_prefill on the tcgen05 tensor cores (TMA-fed, S and O in tensor memory): blocks of at
-    most 128 query rows, head_dim 128, pages of 64 keys, a cache that is finite everywhere."""
+    most 128 query rows, head_dim 64 or 128, pages of 64 keys, a cache that is finite everywhere."""
     T = q.shape[0]
     if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
         raise KernelError("attn_prefill_tc takes bfloat16 queries and cache")
-    if hd != 128 or page_size != 64:
-        raise KernelError(f"attn_prefill_tc: head_dim {hd} (128) and page size {page_size} (64)")
+    if hd not in (64, 128) or page_size != 64:
+        raise KernelError(f"attn_prefill_tc: head_dim {hd} (64 or 128) and page size {page_size} (64)")
     if out is None:
         out = torch.empty((T, H * hd), dtype=torch.bfloat16, device=q.device)
     qb_seq, qb_row, qb_rows, qb_pos = query_blocks128

@@ -604,13 +604,13 @@ def _query_blocks128(new, past):
     return tuple(torch.from_numpy(np.ascontiguousarray(arr[:, i])).to(DEV) for i in range(4))
 
 
+@pytest.mark.parametrize("hd", [128, 64])
 @pytest.mark.parametrize("H,Hkv,window", [(8, 2, None), (4, 4, 100), (2, 1, 300)])
-def test_attn_prefill_tc(H, Hkv, window):
+def test_attn_prefill_tc(H, Hkv, window, hd):
     """The tcgen05 prefill attention: three sequences in one call (whole from position 0; one
     token; one continuing after 70 cached tokens), unused cache rows poisoned with huge finite
     values, so that a key read beyond a sequence shows."""
     ops = _ops()
-    hd = 128
     lens, new, past = [700, 1, 330], [700, 1, 260], [0, 0, 70]
     case = PagedCase(lens, Hkv, hd, torch.bfloat16, seed=12, poison=3.0e38)
     tok_seq = [b for b, n in enumerate(new) for _ in range(n)]
@@ -625,12 +625,13 @@ def test_attn_prefill_tc(H, Hkv, window):
     _close(out.reshape(-1, H, hd), ref, _attn_tol(case, ref), BF16_ULP)
 
 
-def test_attn_prefill_tc_far_key_and_growing_maximum():
+@pytest.mark.parametrize("hd", [128, 64])
+def test_attn_prefill_tc_far_key_and_growing_maximum(hd):
     """Scores that grow along the keys (the reference maximum has to move and O be rescaled
     several times), and a key made to stand out at position 0 of a long sequence."""
     ops = _ops()
     H = Hkv = 1
-    hd, n = 128, 900
+    n = 900
     case = PagedCase([n], Hkv, hd, torch.bfloat16, seed=13, poison=3.0e38)
     q = _rand((n, hd), torch.bfloat16, 84)
     slot = case.slot_of[0]
