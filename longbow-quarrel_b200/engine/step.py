@@ -13,7 +13,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from ..cache import Cache, CacheError
+from ..cache import Cache
 from ..kernels import ops
 from ..parts.base import StepContext
 

@@ -6,7 +6,6 @@ fallback: a tensor on the CPU, or a library that cannot be built, is an error.
 """
 from __future__ import annotations
 
-import ctypes
 import os
 from ctypes import c_float, c_int, c_long, c_void_p
 

@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels import linear, ops
+from ..kernels import linear
 from ..weights.spec import WeightSpec
 from .base import FeedForward, Runtime, StepContext
 from .registry import register_part

@@ -2,7 +2,6 @@
 that the engine tests share."""
 from __future__ import annotations
 
-import json
 from pathlib import Path
 
 import numpy as np

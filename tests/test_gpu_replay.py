@@ -1,7 +1,6 @@
 """Trace replay through bin/trace_run: the same requests whole, with the last 32
 tokens one by one, and in batches of unequal lengths whose slots are used again,
 in 32-bit and in bfloat16, all against the plain implementation."""
-import numpy as np
 import pytest
 
 from helpers import TINY, TOL, make_model_folder, plain_logits, random_tokens, rel_err
