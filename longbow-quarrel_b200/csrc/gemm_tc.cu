@@ -136,8 +136,8 @@ struct Smem {
 };
 
 // ------------------------------------------------------------------ epilogue of 32 columns of one row
-template <int EPI>
 // n_lim: the tile's columns end there (at most N); columns from n_lim on are not stored.
+template <int EPI>
 __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], void* Cout,
                                             const float* residual, int m, int n, int M, int N, int n_lim) {
     if (m >= M || n >= n_lim) return;
