@@ -1,0 +1,78 @@
+"""What a step checks before it launches anything, and the integers it hands to the kernels
+(no GPU: the packing is plain host code)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+import longbow_quarrel_b200  # noqa: F401
+from longbow_quarrel_b200.engine.step import QUERY_BLOCK, StepError, check_entries, pack_step
+
+
+def _part(flat, info, name):
+    o, n = info["layout"][name]
+    return flat[o:o + n]
+
+
+def test_errors_are_found_before_a_launch():
+    check_entries([(0, [1, 2]), (3, [5])], None, 10)
+    check_entries([(0, [1, 2]), (3, [5])], [[0, 1], []], 10)
+    with pytest.raises(StepError, match="at least one"):
+        check_entries([], None, 10)
+    with pytest.raises(StepError, match="twice"):
+        check_entries([(2, [1]), (2, [3])], None, 10)
+    with pytest.raises(StepError, match="no tokens"):
+        check_entries([(0, [1]), (1, [])], None, 10)
+    with pytest.raises(StepError, match=r"token 10 at place 1 of sequence 0"):
+        check_entries([(0, [1, 10])], None, 10)
+    with pytest.raises(StepError, match="outside the vocabulary"):
+        check_entries([(0, [-1])], None, 10)
+    with pytest.raises(StepError, match="one list for each"):
+        check_entries([(0, [1]), (1, [2])], [[0]], 10)
+    with pytest.raises(StepError, match="wanted place 2 of sequence 1"):
+        check_entries([(0, [1]), (1, [2, 3])], [[0], [2]], 10)
+
+
+def test_positions_follow_each_sequences_own_past():
+    entries = [(4, [7, 8, 9]), (1, [5]), (6, [3, 3, 3, 3, 3])]
+    past = [0, 70, 129]
+    flat, info = pack_step(entries, [[0, 2], [], [4]], past)
+    assert flat.dtype == np.int32
+    assert info["B"] == 3 and info["T"] == 9 and info["max_new"] == 5 and info["max_kv"] == 134
+    assert _part(flat, info, "tokens").tolist() == [7, 8, 9, 5, 3, 3, 3, 3, 3]
+    assert _part(flat, info, "tok_seq").tolist() == [0, 0, 0, 1, 2, 2, 2, 2, 2]
+    assert _part(flat, info, "tok_pos").tolist() == [0, 1, 2, 70, 129, 130, 131, 132, 133]
+    assert _part(flat, info, "slots").tolist() == [4, 1, 6]
+    assert _part(flat, info, "kv_len").tolist() == [3, 71, 134]
+    assert _part(flat, info, "cu_rows").tolist() == [0, 3, 4, 9]
+    assert _part(flat, info, "want_rows").tolist() == [0, 2, 8]            # in the order of the entries and of want
+    for name, (offset, _) in info["layout"].items():
+        assert offset % 4 == 0, name                                      # every part starts on a 16-byte boundary
+
+
+def test_without_want_the_last_row_of_every_sequence_is_asked_for():
+    flat, info = pack_step([(0, [1, 2, 3]), (1, [4])], None, [0, 5])
+    assert _part(flat, info, "want_rows").tolist() == [2, 3]
+    flat, info = pack_step([(0, [1, 2, 3])], [[]], [0])
+    assert len(_part(flat, info, "want_rows")) == 0
+
+
+@pytest.mark.parametrize("prefix,size", [("qb", QUERY_BLOCK), ("qc", 2 * QUERY_BLOCK)])
+def test_query_blocks_cover_every_row_once_longest_first(prefix, size):
+    rng = np.random.default_rng(3)
+    new = [1, 64, 65, 200, 128, 129, 17]
+    past = [0, 0, 100, 3, 64, 0, 700]
+    entries = [(b, rng.integers(0, 50, n).tolist()) for b, n in enumerate(new)]
+    flat, info = pack_step(entries, None, past)
+    seq, row, rows, pos = (_part(flat, info, f"{prefix}_{k}") for k in ("seq", "row", "rows", "pos"))
+    tok_seq, tok_pos = _part(flat, info, "tok_seq"), _part(flat, info, "tok_pos")
+    covered = np.zeros(sum(new), dtype=int)
+    for s, r, n, p in zip(seq, row, rows, pos):
+        assert 1 <= n <= size
+        covered[r:r + n] += 1
+        assert (tok_seq[r:r + n] == s).all()                               # a block stays inside one sequence
+        assert tok_pos[r:r + n].tolist() == list(range(p, p + n))          # and its rows are consecutive positions
+        assert (p - past[s]) % size == 0                                   # blocks start at multiples of the size
+    assert (covered == 1).all()
+    assert list(pos) == sorted(pos, reverse=True)                          # the blocks with the most keys come first
+    assert len(seq) == sum(-(-n // size) for n in new)
