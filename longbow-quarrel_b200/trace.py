@@ -57,7 +57,7 @@ def main(argv=None) -> int:
                 slots[rid] = engine.new_sequence()
             entries.append((slots[rid], e["tokens"]))
             want.append(e.get("want", []))
-        logits = engine.step(entries, want)
+        logits = engine.step(entries, want) if entries else None      # a step may only end requests
         if logits is not None:
             arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
             np.ascontiguousarray(arr).tofile(out / f"{step}.f32")
