@@ -62,7 +62,9 @@ def main(argv=None) -> int:
             arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
             np.ascontiguousarray(arr).tofile(out / f"{step}.f32")
         for rid in obj.get("end", []):
-            engine.end_sequence(slots.pop(str(rid)))
+            slot = slots.pop(str(rid), None)          # a request that never brought a token holds nothing
+            if slot is not None:
+                engine.end_sequence(slot)
         print(f"done {step}", flush=True)
     engine.close()
     return 0
