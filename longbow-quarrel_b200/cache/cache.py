@@ -10,8 +10,9 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from ..parts.base import KVNeed, StateNeed
-from .paged import KVView, PagedKVGroup
+from ..parts.base import CacheNeed
+from .group import CacheGroup, CacheSizing
+from .paged import PagedKVGroup
 from .slots import CacheError, SlotAllocator
 from .state import StateGroup
 
@@ -19,7 +20,7 @@ PAGE_SIZE = 64
 
 
 class Cache:
-    def __init__(self, needs: dict[int, KVNeed | StateNeed | None], max_tokens: int, max_context: int,
+    def __init__(self, needs: dict[int, CacheNeed | None], max_tokens: int, max_context: int,
                  dtype: torch.dtype, device, max_slots: int | None = None, page_size: int = PAGE_SIZE):
         if max_tokens < 1:
             raise CacheError("max_tokens must be positive")
@@ -31,40 +32,41 @@ class Cache:
         self.slots = SlotAllocator(self.max_slots)
         self.lengths = np.zeros(self.max_slots, dtype=np.int64)
         self.device, self.dtype = device, dtype
+        sizing = CacheSizing(self.n_pages, page_size, self.max_slots, pages_per_seq, max_context, dtype, device)
 
-        kv: dict[KVNeed, list[int]] = {}
-        st: dict[StateNeed, list[int]] = {}
+        # Entries with equal needs share a group; each need makes the group that suits it.
+        by_need: dict[CacheNeed, list[int]] = {}
         for entry, need in sorted(needs.items()):
-            if isinstance(need, KVNeed):
-                kv.setdefault(need, []).append(entry)
-            elif isinstance(need, StateNeed):
-                st.setdefault(need, []).append(entry)
-            elif need is not None:
-                raise CacheError(f"cache entry {entry}: unknown need {need!r}")
-        self.kv_groups = [PagedKVGroup(entries, need.n_kv_heads, need.head_dim, need.window, self.n_pages, page_size,
-                                       self.max_slots, pages_per_seq, dtype, device)
-                          for need, entries in kv.items()]
-        self.state_groups = [StateGroup(entries, need.shape, need.dtype, self.max_slots, device)
-                             for need, entries in st.items()]
+            if need is None:
+                continue
+            if not isinstance(need, CacheNeed):
+                raise CacheError(f"cache entry {entry}: {need!r} is no CacheNeed")
+            by_need.setdefault(need, []).append(entry)
+        self.groups: list[CacheGroup] = [need.make_group(entries, sizing) for need, entries in by_need.items()]
         self._views: dict[int, object] = {}
-        for g in self.kv_groups:
-            for e in g.entries:
-                self._views[e] = KVView(g, e)
-        for g in self.state_groups:
+        for g in self.groups:
             for e in g.entries:
                 self._views[e] = g.view(e)
+
+    @property
+    def kv_groups(self) -> list[PagedKVGroup]:
+        return [g for g in self.groups if isinstance(g, PagedKVGroup)]
+
+    @property
+    def state_groups(self) -> list[StateGroup]:
+        return [g for g in self.groups if isinstance(g, StateGroup)]
 
     # ------------------------------------------------------------------ slots
     def alloc_slot(self) -> int:
         slot = self.slots.alloc()
         self.lengths[slot] = 0
-        for g in self.state_groups:
-            g.reset(slot)
+        for g in self.groups:
+            g.start(slot)
         return slot
 
     def free_slot(self, slot: int) -> None:
         self.slots.free(slot)
-        for g in self.kv_groups:
+        for g in self.groups:
             g.release(slot)
         self.lengths[slot] = 0
 
@@ -79,27 +81,26 @@ class Cache:
         old = int(self.lengths[slot])
         if old + n_new > self.max_context:
             raise CacheError(f"sequence would reach {old + n_new} tokens; the context limit is {self.max_context}")
-        for g in self.kv_groups:
+        for g in self.groups:
             g.reserve(slot, old, old + n_new)
 
     def commit(self, slot: int, n_new: int) -> None:
         """The step stored n_new tokens; pages that fell out of a window go back to their pool."""
         self.lengths[slot] += n_new
-        for g in self.kv_groups:
-            g.trim(slot, int(self.lengths[slot]))
+        for g in self.groups:
+            g.commit(slot, int(self.lengths[slot]))
 
     def upload(self) -> None:
-        for g in self.kv_groups:
+        for g in self.groups:
             g.upload()
 
     def view(self, entry: int):
-        """KVView or state tensor of a cache entry (None for an entry without cache)."""
+        """What the mixer of a cache entry works on (None for an entry without cache)."""
         return self._views.get(entry)
 
     # ------------------------------------------------------------------ accounting (tests, stats)
     def pages_in_use(self) -> int:
-        return sum(g.n_pages - g.n_free_pages for g in self.kv_groups)
+        return sum(g.pages_in_use() for g in self.groups)
 
     def bytes(self) -> int:
-        n = sum(g.k_pages.numel() * g.k_pages.element_size() * 2 for g in self.kv_groups)
-        return n + sum(g.data.numel() * g.data.element_size() for g in self.state_groups)
+        return sum(g.nbytes() for g in self.groups)

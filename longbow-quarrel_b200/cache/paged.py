@@ -13,12 +13,13 @@ from __future__ import annotations
 import numpy as np
 import torch
 
+from .group import CacheGroup
 from .slots import CacheError
 
 NO_PAGE = -1
 
 
-class PagedKVGroup:
+class PagedKVGroup(CacheGroup):
     def __init__(self, entries: list[int], n_kv_heads: int, head_dim: int, window: int | None, n_pages: int,
                  page_size: int, max_slots: int, max_pages_per_seq: int, dtype: torch.dtype, device):
         self.entries = list(entries)
@@ -26,14 +27,16 @@ class PagedKVGroup:
         self.n_kv_heads, self.head_dim, self.window = n_kv_heads, head_dim, window
         self.page_size, self.n_pages, self.max_pages_per_seq = page_size, n_pages, max_pages_per_seq
         shape = (len(self.entries), n_pages, n_kv_heads, page_size, head_dim)
-        # Zero-filled: kernels that load whole pages multiply the rows beyond a sequence's length by
-        # probability zero, which needs finite values there.
+        # Kernels that load whole pages multiply the rows beyond a sequence's length by probability zero,
+        # which needs finite values there: the pool starts zero-filled, and a page that is handed out
+        # again has the rows that its new owner's step does not write cleared first (`_to_clear`).
         self.k_pages = torch.zeros(shape, dtype=dtype, device=device)
         self.v_pages = torch.zeros(shape, dtype=dtype, device=device)
         self.table = np.full((max_slots, max_pages_per_seq), NO_PAGE, dtype=np.int32)
         self.table_dev = torch.full((max_slots, max_pages_per_seq), NO_PAGE, dtype=torch.int32, device=device)
         self._free = list(range(n_pages - 1, -1, -1))
         self._dirty: set[int] = set()
+        self._to_clear: list[tuple[int, int]] = []      # (page, first row that the step does not write)
 
     @property
     def n_free_pages(self) -> int:
@@ -62,7 +65,11 @@ class PagedKVGroup:
             raise CacheError(f"the cache is full: {len(need)} more pages of {self.page_size} tokens are needed, "
                              f"{len(self._free)} of {self.n_pages} are free")
         for p in need:
-            self.table[slot, p] = self._free.pop()
+            page = self._free.pop()
+            self.table[slot, p] = page
+            written_to = min(new_len - p * self.page_size, self.page_size)
+            if written_to < self.page_size:
+                self._to_clear.append((page, written_to))
         if need:
             self._dirty.add(slot)
 
@@ -78,6 +85,9 @@ class PagedKVGroup:
                 row[p] = NO_PAGE
                 self._dirty.add(slot)
 
+    def commit(self, slot: int, length: int) -> None:
+        self.trim(slot, length)
+
     def release(self, slot: int) -> None:
         row = self.table[slot]
         for p in np.nonzero(row != NO_PAGE)[0]:
@@ -86,10 +96,29 @@ class PagedKVGroup:
         self._dirty.add(slot)
 
     def upload(self) -> None:
-        """Copy the rows of the page table that changed to the device."""
+        """Copy the rows of the page table that changed to the device, and clear the unwritten ends of
+        pages that were handed out since the last step."""
         for slot in sorted(self._dirty):
             self.table_dev[slot].copy_(torch.from_numpy(self.table[slot]), non_blocking=False)
         self._dirty.clear()
+        if self._to_clear:
+            todo, self._to_clear = self._to_clear, []
+            if self.k_pages.is_cuda:
+                from ..kernels import ops
+                ops.clear_page_tails(self.k_pages, self.v_pages, todo)
+            else:                                   # bookkeeping tests keep their pools on the CPU
+                for page, first in todo:
+                    self.k_pages[:, page, :, first:].zero_()
+                    self.v_pages[:, page, :, first:].zero_()
+
+    def view(self, entry: int) -> "KVView":
+        return KVView(self, entry)
+
+    def nbytes(self) -> int:
+        return 2 * self.k_pages.numel() * self.k_pages.element_size()
+
+    def pages_in_use(self) -> int:
+        return self.n_pages - len(self._free)
 
 
 class KVView:

@@ -9,16 +9,23 @@ from __future__ import annotations
 
 import torch
 
+from .group import CacheGroup
 
-class StateGroup:
+
+class StateGroup(CacheGroup):
     def __init__(self, entries: list[int], shape: tuple[int, ...], dtype: torch.dtype, max_slots: int, device):
         self.entries = list(entries)
         self.index = {e: i for i, e in enumerate(self.entries)}
         self.shape, self.dtype = tuple(shape), dtype
         self.data = torch.zeros((len(self.entries), max_slots, *self.shape), dtype=dtype, device=device)
 
-    def reset(self, slot: int) -> None:
+    def start(self, slot: int) -> None:
         self.data[:, slot].zero_()
+
+    reset = start
+
+    def nbytes(self) -> int:
+        return self.data.numel() * self.data.element_size()
 
     def view(self, entry: int) -> torch.Tensor:
         """[max_slots, *shape] of one cache entry."""

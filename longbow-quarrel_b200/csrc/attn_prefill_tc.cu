@@ -48,8 +48,6 @@ constexpr int N_SOFTMAX = PARTS * BM;   // softmax threads
 constexpr int N_THREADS = 64 + N_SOFTMAX;   // TMA warp, MMA warp, 4 softmax warps per part
 constexpr float RESCALE_STEP = 8.0f;    // log2 units the maximum may run ahead of the reference
 
-__device__ int g_status = 0;
-
 // HD: the head dimension, 64 or 128: one or two panels of 64 elements.
 template <int HD>
 struct Smem {
@@ -82,7 +80,7 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 #define LQ_WAIT(bar, parity, code) \
-    if (!mbar_wait(smem_u32(&(bar)), (parity))) { atomicExch(&g_status, (code)); ok = false; }
+    if (!mbar_wait(smem_u32(&(bar)), (parity))) { give_up(code); ok = false; }
 
 template <int HD>
 __global__ void __launch_bounds__(N_THREADS, 1)
@@ -383,9 +381,8 @@ LQ_EXPORT int lq_attn_prefill_tc(const void* q, int q_stride, int T, const void*
                           qb_rows, qb_pos, out, n_blocks, H, Hkv, scale, window, stream);
 }
 
-LQ_EXPORT int lq_attn_prefill_tc_status() {
-    int v = 0, zero = 0;
-    cudaMemcpyFromSymbol(&v, g_status, sizeof(int));
-    if (v) cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
-    return v;
-}
+LQ_EXPORT int lq_attn_prefill_tc_status() { return tc::status_read(); }
+
+// The same word in host memory that the device writes through (readable without a CUDA call); null when
+// it could not be set up.
+LQ_EXPORT int* lq_attn_prefill_tc_status_word() { return tc::status_word(); }

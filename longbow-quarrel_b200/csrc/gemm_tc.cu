@@ -24,8 +24,7 @@
 //
 // Reference counterpart: the per-row linear_f16 kernels and the library GEMM of
 // internal/device/metal.go:886-964; its CUDA path calls cublasSgemmEx (internal/device/cuda.go:293-318).
-#include "common.cuh"
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 #define EPI_BF16 0
 #define EPI_F32 1
@@ -39,82 +38,7 @@ constexpr int BM = 128;
 constexpr int BK = 64;                 // 64 bf16 = 128 bytes: one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int N_THREADS = 192;
-constexpr unsigned long long WAIT_NS = 2000000000ull;
-
-__device__ int g_status = 0;           // 0 = fine; else the code of the wait that gave up
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ unsigned long long globaltimer() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the phase did not complete within WAIT_NS.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    if (mbar_try(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer();
-    for (;;) {
-        for (int i = 0; i < 64; ++i)
-            if (mbar_try(bar, parity)) return true;
-        if (globaltimer() - t0 > WAIT_NS) return false;
-    }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled in
-// 8-row groups of 1024 bytes (what a TMA load with 128-byte swizzle writes).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    uint64_t d = (uint64_t)((addr & 0x3FFFFu) >> 4);   // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                            // leading byte offset: unused with a swizzle (1)
-    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset: 8 rows x 128 bytes
-    d |= (uint64_t)1 << 46;                            // descriptor version of sm_100
-    d |= (uint64_t)2 << 61;                            // layout: 128-byte swizzle
-    return d;
-}
-// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M 128, N n.
-__host__ __device__ constexpr uint32_t instr_desc(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
+using namespace tc;       // mbarriers with bounded waits, TMA, tcgen05 wrappers, descriptors, status word
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -277,18 +201,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&sm.full[s]), 1); mbar_init(smem_u32(&sm.empty[s]), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&sm.acc_full[a]), 1); mbar_init(smem_u32(&sm.acc_empty[a]), 4); }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+        mbar_fence_init();
+        prefetch_map(&map_a);
+        prefetch_map(&map_b);
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        tmem_alloc(smem_u32(&sm.tmem_base), TMEM_COLS);
     }
     pdl_launch_dependents();
-    tc_fence_before();
+    fence_before();
     __syncthreads();
-    tc_fence_after();
+    fence_after();
     const uint32_t tmem_base = sm.tmem_base;
     pdl_wait();     // barriers and tensor memory were set up while the kernel ahead was draining
 
@@ -303,7 +226,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int kb_lo = (int)((long)n_kb * range / splits), kb_hi = (int)((long)n_kb * (range + 1) / splits);
                 for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
                     const int s = it % STAGES;
-                    if (!mbar_wait(smem_u32(&sm.empty[s]), ((it / STAGES) & 1) ^ 1)) { atomicExch(&g_status, 1); ok = false; break; }
+                    if (!mbar_wait(smem_u32(&sm.empty[s]), ((it / STAGES) & 1) ^ 1)) { give_up(1); ok = false; break; }
                     const uint32_t full = smem_u32(&sm.full[s]);
                     mbar_expect_tx(full, STAGE_BYTES);
                     tma_load_2d(smem_u32(sm.a[s]), &map_a, kb * BK, m0, full);
@@ -322,27 +245,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc(BN);
+            constexpr uint32_t idesc = idesc_bf16(BM, BN, false);
             uint32_t it = 0, t = 0;
             bool ok = true;
             for (int piece = blockIdx.x; piece < total && ok; piece += gridDim.x, ++t) {
                 const int range = piece % splits;
                 const int kb_lo = (int)((long)n_kb * range / splits), kb_hi = (int)((long)n_kb * (range + 1) / splits);
                 const uint32_t acc = t & 1;
-                if (!mbar_wait(smem_u32(&sm.acc_empty[acc]), ((t >> 1) & 1) ^ 1)) { atomicExch(&g_status, 2); ok = false; break; }
-                tc_fence_after();
+                if (!mbar_wait(smem_u32(&sm.acc_empty[acc]), ((t >> 1) & 1) ^ 1)) { give_up(2); ok = false; break; }
+                fence_after();
                 const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
                 for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
                     const int s = it % STAGES;
-                    if (!mbar_wait(smem_u32(&sm.full[s]), (it / STAGES) & 1)) { atomicExch(&g_status, 3); ok = false; break; }
-                    tc_fence_after();
-                    const uint64_t da = smem_desc(smem_u32(sm.a[s])), db = smem_desc(smem_u32(sm.b[s]));
+                    if (!mbar_wait(smem_u32(&sm.full[s]), (it / STAGES) & 1)) { give_up(3); ok = false; break; }
+                    fence_after();
+                    const uint64_t da = desc_k_major(smem_u32(sm.a[s])), db = desc_k_major(smem_u32(sm.b[s]));
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)   // 32 bytes further along K: 2 units of 16 bytes
-                        tc_mma(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > kb_lo || k > 0) ? 1u : 0u);
-                    tc_commit(smem_u32(&sm.empty[s]));      // the stage is free once these products have read it
+                        mma_f16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > kb_lo || k > 0) ? 1u : 0u);
+                    commit(smem_u32(&sm.empty[s]));      // the stage is free once these products have read it
                 }
-                if (ok) tc_commit(smem_u32(&sm.acc_full[acc]));
+                if (ok) commit(smem_u32(&sm.acc_full[acc]));
             }
         }
         __syncwarp();
@@ -356,8 +279,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
             void* dst = splits > 1 ? (void*)((float*)Cout + (size_t)range * M * N) : Cout;
             const uint32_t acc = t & 1;
-            if (!mbar_wait(smem_u32(&sm.acc_full[acc]), (t >> 1) & 1)) { atomicExch(&g_status, 4); ok = false; break; }
-            tc_fence_after();
+            if (!mbar_wait(smem_u32(&sm.acc_full[acc]), (t >> 1) & 1)) { give_up(4); ok = false; break; }
+            fence_after();
             const int m = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
             const int n_lim = n0 + BN < N ? n0 + BN : N;
@@ -373,9 +296,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll 1
                     for (int j0 = 0; j0 < half; j0 += 32) {
                         uint32_t a[32], b[32];
-                        tc_ld32(taddr + col + j0, a);
-                        tc_ld32(taddr + col + half + j0, b);
-                        tc_wait_ld();
+                        ld32(taddr + col + j0, a);
+                        ld32(taddr + col + half + j0, b);
+                        wait_ld();
                         if (m < M)
                             store_qkv_pair(a, b, row, rotate ? qkv.cos_t + (size_t)pos * half : nullptr,
                                            rotate ? qkv.sin_t + (size_t)pos * half : nullptr, j0, half);
@@ -385,21 +308,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll 1
                 for (int c = 0; c < (BN + 31) / 32; ++c) {      // a last half chunk reads columns that are not stored
                     uint32_t r[32];
-                    tc_ld32(taddr + c * 32, r);
-                    tc_wait_ld();
+                    ld32(taddr + c * 32, r);
+                    wait_ld();
                     store_chunk<EPI>(r, dst, residual, m, n0 + c * 32, M, N, n_lim);
                 }
             }
-            tc_fence_before();
+            fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sm.acc_empty[acc]));
         }
     }
-    tc_fence_before();
+    fence_before();
     __syncthreads();
     if (warp == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 
@@ -491,34 +414,9 @@ int launch_reduce(const float* part, int splits, void* C, const float* residual,
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-    static EncodeTiled fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiled)p;
-    }
-    return fn;
-}
-
 // A row-major bf16 matrix [rows, K] as a 2-D tensor map with boxes of [box_rows, 64].
 int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-    EncodeTiled fn = encode_fn();
-    if (!fn) return LQ_NO_DRIVER;
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? LQ_OK : LQ_BAD_SIZE;
+    return make_map_bf16(map, base, rows, K, K, box_rows);
 }
 
 template <int BN, int STAGES, int EPI, int AROWS>
@@ -673,9 +571,8 @@ LQ_EXPORT int lq_gemm_tc_splits(int M, int N, int K) {
 
 // The status word of the bounded waits: 0, or the code of the first wait that gave up
 // (1 producer, 2 accumulator free, 3 stage full, 4 accumulator full).  Reading it resets it.
-LQ_EXPORT int lq_gemm_tc_status() {
-    int v = 0, zero = 0;
-    cudaMemcpyFromSymbol(&v, g_status, sizeof(int));
-    if (v) cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
-    return v;
-}
+LQ_EXPORT int lq_gemm_tc_status() { return tc::status_read(); }
+
+// The same word in host memory that the device writes through (readable without a CUDA call, so polling
+// it never waits for work that is queued); null when it could not be set up.
+LQ_EXPORT int* lq_gemm_tc_status_word() { return tc::status_word(); }

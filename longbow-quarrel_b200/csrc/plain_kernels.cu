@@ -489,3 +489,49 @@ LQ_EXPORT int lq_swiglu(const void* gu, void* out, int dtype, int T, int F, int 
         return LQ_BAD_DTYPE;
     return lq_launch_status();
 }
+
+// ------------------------------------------------------------------ clearing the unwritten end of a page
+// A page that a sequence is given may hold what another sequence left there.  Kernels that load whole
+// pages multiply the rows beyond the sequence's length by probability zero, which gives zero only for
+// finite values; so the rows of a new page that the step will not write are cleared before the step.
+// pages [entry][page][kv head][token][head_dim]; work item = (page, first row to clear).
+#define LQ_CLEAR_MAX 120
+struct ClearList { int page[LQ_CLEAR_MAX]; int first_row[LQ_CLEAR_MAX]; };
+
+__global__ void clear_page_tails_kernel(uint32_t* __restrict__ k_pages, uint32_t* __restrict__ v_pages, ClearList list,
+                                        size_t entry_words, size_t page_words, int Hkv, int page_size, int row_words) {
+    const int item = blockIdx.x, entry = blockIdx.y, head = blockIdx.z;
+    const int first = list.first_row[item];
+    const size_t base = (size_t)entry * entry_words + (size_t)list.page[item] * page_words
+                      + ((size_t)head * page_size + first) * row_words;
+    const int n = (page_size - first) * row_words;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        k_pages[base + i] = 0u;
+        v_pages[base + i] = 0u;
+    }
+}
+
+LQ_EXPORT int lq_clear_page_tails(void* k_pages, void* v_pages, int dtype, const int* pages, const int* first_rows,
+                                  int n_items, int n_entries, int n_pages, int Hkv, int page_size, int hd,
+                                  cudaStream_t stream) {
+    if (n_items <= 0 || n_entries <= 0) return LQ_OK;
+    if (dtype != LQ_F32 && dtype != LQ_BF16) return LQ_BAD_DTYPE;
+    const int elt = dtype == LQ_F32 ? 4 : 2;
+    if ((hd * elt) % 4) return LQ_BAD_SIZE;
+    const int row_words = hd * elt / 4;
+    const size_t page_words = (size_t)Hkv * page_size * row_words;
+    for (int at = 0; at < n_items; at += LQ_CLEAR_MAX) {
+        ClearList list;
+        const int n = n_items - at < LQ_CLEAR_MAX ? n_items - at : LQ_CLEAR_MAX;
+        for (int i = 0; i < n; ++i) {
+            if (pages[at + i] < 0 || pages[at + i] >= n_pages || first_rows[at + i] < 0 || first_rows[at + i] > page_size)
+                return LQ_BAD_SIZE;
+            list.page[i] = pages[at + i];
+            list.first_row[i] = first_rows[at + i];
+        }
+        int rc = launch_after(clear_page_tails_kernel, dim3(n, n_entries, Hkv), dim3(256), 0, stream, (uint32_t*)k_pages,
+                              (uint32_t*)v_pages, list, page_words * (size_t)n_pages, page_words, Hkv, page_size, row_words);
+        if (rc != LQ_OK) return rc;
+    }
+    return LQ_OK;
+}

@@ -9,6 +9,56 @@ namespace tc {
 
 constexpr unsigned long long WAIT_NS = 2000000000ull;   // a wait gives up after about two seconds
 
+// ------------------------------------------------------------------ the status word of the bounded waits
+// A wait that gives up records a code: in device memory, and in a word of mapped host memory that the
+// host reads without any CUDA call (polling it cannot wait for, or fall behind, queued work).
+__device__ int g_status = 0;
+__device__ volatile int* g_status_mapped = nullptr;
+
+__device__ __forceinline__ void give_up(int code) {
+    atomicExch(&g_status, code);
+    volatile int* p = g_status_mapped;
+    if (p) { *p = code; __threadfence_system(); }
+}
+
+// Host: the mapped word, made on first use and announced to the current device (once per device).
+static inline int* status_word() {
+    static int* host = nullptr;
+    static bool told[64] = {};
+    static bool failed = false;
+    if (failed) return nullptr;
+    if (!host) {
+        if (cudaHostAlloc((void**)&host, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+            (void)cudaGetLastError();
+            failed = true;
+            host = nullptr;
+            return nullptr;
+        }
+        *host = 0;
+    }
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return host;
+    if (!told[dev]) {
+        int* dptr = nullptr;
+        if (cudaHostGetDevicePointer((void**)&dptr, host, 0) == cudaSuccess &&
+            cudaMemcpyToSymbol(g_status_mapped, &dptr, sizeof(dptr)) == cudaSuccess)
+            told[dev] = true;
+        else
+            (void)cudaGetLastError();
+    }
+    return host;
+}
+
+// Host: the code in device memory (a synchronous copy: it waits for the device); reading resets both words.
+static inline int status_read() {
+    int v = 0, zero = 0;
+    cudaMemcpyFromSymbol(&v, g_status, sizeof(int));
+    if (v) cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+    int* host = status_word();
+    if (host && *host) { if (!v) v = *host; *host = 0; }
+    return v;
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ unsigned long long globaltimer() {
     unsigned long long t;

@@ -16,6 +16,7 @@ from dataclasses import dataclass
 import torch
 
 from ..cache import CacheError
+from ..kernels import ops
 from ..sampling import SamplingParams, history_window, sample
 
 
@@ -25,12 +26,14 @@ class _Sampled:
     copy is queued right behind the sampler, before any later step, so that waiting for it does
     not wait for a step that was queued ahead)."""
     handles: tuple[int, ...]
+    asked: tuple                  # (handle, request, step) of each row: which step of which request this is
     device: torch.Tensor          # int32 [len(handles)]
     host: torch.Tensor            # pinned int32 [>= len(handles)]
     ready: torch.cuda.Event
 
     def ids(self) -> list[int]:
         self.ready.synchronize()
+        ops.check_status()          # a kernel whose bounded wait gave up left garbage: say so
         return self.host[:len(self.handles)].tolist()
 
 
@@ -78,17 +81,31 @@ class EngineBackend:
 
     def run(self, entries, requests, steps, histories) -> list[int]:
         handles = tuple(h for h, _ in entries)
+        asked = tuple(zip(handles, requests, steps))
         ahead, self._ahead = self._ahead, None
         single = all(len(t) == 1 for _, t in entries)
-        if ahead is not None and single and set(handles) <= set(ahead.handles):
-            current, rows = ahead, [ahead.handles.index(h) for h in handles]   # queued during the last call
+        # The step queued during the last call serves this one only if it is this very step of these very
+        # requests.  Handles alone do not say so: a slot that was given back is handed out again, and a new
+        # request in it that starts with a one-token prompt looks like the old one going on.
+        if ahead is not None and single and set(asked) <= set(ahead.asked):
+            current, rows = ahead, [ahead.asked.index(a) for a in asked]
         else:
+            if ahead is not None:
+                queued = {(h, r) for h, r, _ in ahead.asked}
+                wrong = [r for h, r, _ in asked if (h, r) in queued]
+                if wrong:
+                    # The queued step already stored a token for these requests; it cannot be taken back.
+                    raise RuntimeError(f"requests {wrong}: the step after the last one was queued ahead, and another "
+                                       f"step is asked for; a backend that runs ahead takes the steps in order")
             logits = self.engine.stepper.step(entries, None)
-            current, rows = _Sampled(handles, *self._sample(logits, requests, steps, histories)), list(range(len(handles)))
+            current = _Sampled(handles, asked, *self._sample(logits, requests, steps, histories))
+            rows = list(range(len(handles)))
         if self.run_ahead:
             try:
                 logits = self.engine.stepper.step_fed(list(handles), current.device, rows)
-                self._ahead = _Sampled(handles, *self._sample(logits, requests, [s + 1 for s in steps], None))
+                after = [s + 1 for s in steps]
+                self._ahead = _Sampled(handles, tuple(zip(handles, requests, after)),
+                                       *self._sample(logits, requests, after, None))
             except CacheError:
                 self._ahead = None       # no room for one more token: the loop will end these sequences or fail itself
         ids = current.ids()

@@ -105,6 +105,11 @@ class Engine:
         with torch.cuda.device(self.device):
             return self.stepper.step(entries, want)
 
+    def check(self) -> None:
+        """Raise if a kernel of an earlier step gave up a bounded wait (its results are then not valid).  Sees
+        the steps that the host has waited for: call it after reading a step's logits."""
+        ops.check_status()
+
     # ------------------------------------------------------------------ generation
     def generate(self, prompts, max_new_tokens: int = 20, sampling: SamplingParams | None = None, stop_ids=None,
                  callback=None, include_stop: bool = False, batch_size: int | None = None) -> list[list[int]]:

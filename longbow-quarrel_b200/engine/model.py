@@ -19,6 +19,10 @@ class Model:
         self.final_norm = make_part("norm", spec.final_norm, runtime)
         self.head = make_part("head", spec.head, runtime)
         self._order_known = False
+        # probe(run, x, ctx): called with the residual stream after the embedding (run -1) and after every
+        # scheduled run of a layer, for looking into a step (trace replay's per-layer statistics).  Steps
+        # with a probe are not replayed from CUDA graphs.
+        self.probe = None
         for n, entry in enumerate(spec.schedule):
             if not 0 <= entry.layer < len(self.blocks):
                 raise ValueError(f"schedule entry {n} names layer {entry.layer}; the model has {len(self.blocks)}")
@@ -92,16 +96,23 @@ class Model:
                 return self.forward(ctx, cache)
         x = self.embedding.forward(ctx.tokens)
         schedule = self.spec.schedule
+        probe = self.probe
+        if probe is not None:
+            probe(-1, x, ctx)
         normed = None           # rows of the next layer's first norm, when this layer's last product made them
         for i, entry in enumerate(schedule):
             block = self.blocks[entry.layer]
             if not getattr(block, "folds_norm", False):
                 block.forward(x, ctx, cache.view(entry.cache), entry.writes_cache)
                 normed = None
+                if probe is not None:
+                    probe(i, x, ctx)
                 continue
             after = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
             emit = after.input_norm(x.shape[0]) if getattr(after, "folds_norm", False) else None
             normed = block.forward(x, ctx, cache.view(entry.cache), entry.writes_cache, normed=normed, emit=emit)
+            if probe is not None:
+                probe(i, x, ctx)
         if ctx.want_rows is None or ctx.want_rows.numel() == 0:
             return None
         h = self.final_norm.forward(x, rows=ctx.want_rows)

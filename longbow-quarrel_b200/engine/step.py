@@ -125,7 +125,7 @@ class Stepper:
         self.cache.upload()
         B = len(entries)
         decode = all(len(t) == 1 for _, t in entries)
-        if decode and self.use_graphs:
+        if decode and self.use_graphs and self.model.probe is None:
             logits = self._decode_step(entries, want, past)
         else:
             flat, info = pack_step(entries, want, past)
@@ -150,7 +150,7 @@ class Stepper:
             source = source[torch.tensor(rows, dtype=torch.long, device=self.device)]
         elif source.numel() != len(slots):
             source = source[:len(slots)]
-        if self.use_graphs:
+        if self.use_graphs and self.model.probe is None:
             logits = self._decode_step(entries, None, past, fed=source)
         else:
             flat, info = pack_step(entries, None, past)
@@ -206,12 +206,12 @@ class _DecodeGraph:
         self.graph = torch.cuda.CUDAGraph()
         stream = torch.cuda.Stream(device=device)
         stream.wait_stream(torch.cuda.current_stream(device))
-        before = ops.launch_count()
+        before, names = ops.launch_count(), ops.launches_by_name()
         with torch.cuda.stream(stream):
             with torch.cuda.graph(self.graph, stream=stream):
                 self.logits = model.forward(ctx, cache)
-        self.kernels = ops.launch_count() - before
-        ops.add_launches(-self.kernels)      # recorded, not run
+        self.kernels, self.by_name = ops.launch_count() - before, ops.launches_since(names)
+        ops.add_launches(-self.kernels, self.by_name, -1)      # recorded, not run
         torch.cuda.current_stream(device).wait_stream(stream)
         self.copied.record()
 
@@ -224,5 +224,5 @@ class _DecodeGraph:
             o, n = self.info["layout"]["tokens"]
             self.flat_dev[o:o + n].copy_(fed)
         self.graph.replay()
-        ops.add_launches(self.kernels)
+        ops.add_launches(self.kernels, self.by_name)
         return self.logits

@@ -42,6 +42,7 @@ def _stream():
 
 
 _launches = 0
+_by_name: dict[str, int] = {}
 
 
 def launch_count() -> int:
@@ -50,15 +51,31 @@ def launch_count() -> int:
     return _launches
 
 
-def add_launches(n: int) -> None:
+def launches_by_name() -> dict[str, int]:
+    """How often each launcher has run so far (a copy): which kernels a piece of work went through."""
+    return dict(_by_name)
+
+
+def add_launches(n: int, by_name: dict[str, int] | None = None, sign: int = 1) -> None:
+    """Count `n` kernels that were recorded or replayed rather than launched here; `by_name` says which."""
     global _launches
     _launches += n
+    for name, k in (by_name or {}).items():
+        _by_name[name] = _by_name.get(name, 0) + sign * k
 
 
-def _check(code: int, what: str, kernels: int = 1) -> None:
+def launches_since(before: dict[str, int]) -> dict[str, int]:
+    return {name: k - before.get(name, 0) for name, k in _by_name.items() if k != before.get(name, 0)}
+
+
+def _check(code: int, what: str, kernels: int = 1, variant: str | None = None) -> None:
+    """`variant` names the path inside the launcher that the sizes chose (counted beside the launcher)."""
     global _launches
     if code == 0:
         _launches += kernels
+        _by_name[what] = _by_name.get(what, 0) + 1
+        if variant:
+            _by_name[variant] = _by_name.get(variant, 0) + 1
         return
     reason = {-1: "unsupported dtype", -2: "unsupported size", -3: "CUDA driver entry point not found",
               -4: "scratch too small"}.get(code, f"CUDA error {code}")
@@ -68,8 +85,41 @@ def _check(code: int, what: str, kernels: int = 1) -> None:
 _declared: set[tuple[str, str]] = set()
 
 
+# Libraries whose kernels wait on barriers with a time limit, and what their status codes mean.
+_WATCHED = {"gemm_tc": {1: "the TMA producer waited for a free stage", 2: "the product issuer waited for a free accumulator",
+                        3: "the product issuer waited for a stage's copies", 4: "the epilogue waited for an accumulator"},
+            "attn_prefill_tc": {}}
+_status_words: dict[str, object] = {}
+
+
+def _watch(lib: str, handle) -> None:
+    """Set up the library's status word in mapped host memory (once; not while a stream is being captured,
+    since the set-up copies a pointer to the device)."""
+    if lib in _status_words or torch.cuda.is_current_stream_capturing():
+        return
+    from ctypes import POINTER
+    fn = getattr(handle, f"lq_{lib}_status_word")
+    fn.restype = POINTER(c_int)
+    fn.argtypes = []
+    _status_words[lib] = fn()
+
+
+def check_status() -> None:
+    """Raise if a bounded wait inside a tensor-core kernel gave up since the last check.  It reads words
+    in host memory that such a kernel writes through, so it costs no CUDA call and sees everything that
+    ran before the host's last synchronisation: call it where the host has just waited for results."""
+    for lib, word in _status_words.items():
+        if word and word[0]:
+            code = int(word[0])
+            word[0] = 0
+            why = _WATCHED[lib].get(code, "a wait on a barrier")
+            raise KernelError(f"{lib}: {why} for two seconds and gave up (code {code}); the step's results are not valid")
+
+
 def _fn(lib: str, name: str, argtypes):
     handle = build.load(lib)
+    if lib in _WATCHED:
+        _watch(lib, handle)
     fn = getattr(handle, name)
     if (lib, name) not in _declared:
         fn.argtypes = argtypes
@@ -143,6 +193,21 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, residua
     return out
 
 
+def _check_tables(what: str, cos, sin, hd: int, tok_pos=None) -> None:
+    """The fused q/k/v epilogues read cos/sin at [position, head_dim / 2]: tables of another width (a part
+    that rotates only some of a head's dimensions) would be read across rows."""
+    if cos is None and sin is None:
+        return
+    if cos is None or sin is None:
+        raise KernelError(f"{what}: cos and sin tables come together")
+    for t in (cos, sin):
+        if t.dtype != torch.float32 or t.dim() != 2 or t.shape[1] != hd // 2 or not t.is_contiguous():
+            raise KernelError(f"{what}: cos/sin tables must be contiguous float32 [positions, head_dim / 2 = {hd // 2}], "
+                              f"found {tuple(t.shape)} {t.dtype}")
+    if cos.shape != sin.shape:
+        raise KernelError(f"{what}: cos {tuple(cos.shape)} and sin {tuple(sin.shape)} differ")
+
+
 def rope_kv_write(qkv: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tensor | None, tok_pos, tok_seq, slots,
                   page_table: torch.Tensor | None, k_pages: torch.Tensor | None, v_pages: torch.Tensor | None,
                   H: int, Hkv: int, hd: int, page_size: int) -> None:
@@ -154,8 +219,7 @@ def rope_kv_write(qkv: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tensor
         raise KernelError(f"rope: qkv rows are {qkv.shape[1]} wide, expected {width}")
     if has_kv and (k_pages.dtype != qkv.dtype or v_pages.dtype != qkv.dtype):
         raise KernelError("rope: the cache and the activations must have one dtype")
-    if cos is not None and (cos.dtype != torch.float32 or cos.shape[1] != hd // 2):
-        raise KernelError("rope: cos/sin tables must be float32 [positions, head_dim / 2]")
+    _check_tables("rope", cos, sin, hd)
     fn = _fn("plain_kernels", "lq_rope_kv_write", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                    c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                    c_int, c_int, c_void_p])
@@ -193,6 +257,23 @@ def swiglu(gu: torch.Tensor, block: int = 0, out: torch.Tensor | None = None) ->
     fn = _fn("plain_kernels", "lq_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
     _check(fn(_p(_contig(gu, "gu")), _p(out), dtype_code(gu), T, F, block, _stream()), "swiglu")
     return out
+
+
+def clear_page_tails(k_pages: torch.Tensor, v_pages: torch.Tensor, items: list[tuple[int, int]]) -> None:
+    """Zero the rows [first, page_size) of the pages in `items` = [(page, first)], in every entry and kv
+    head of the pools k_pages, v_pages [entries, pages, kv heads, page_size, head_dim]."""
+    from ctypes import c_int as _int
+    E, P, Hkv, page_size, hd = k_pages.shape
+    if v_pages.shape != k_pages.shape or v_pages.dtype != k_pages.dtype:
+        raise KernelError("clear_page_tails: keys and values must have one shape and dtype")
+    n = len(items)
+    pages = (_int * n)(*[int(p) for p, _ in items])
+    first = (_int * n)(*[int(f) for _, f in items])
+    from ctypes import POINTER
+    fn = _fn("plain_kernels", "lq_clear_page_tails", [c_void_p, c_void_p, c_int, POINTER(c_int), POINTER(c_int), c_int,
+                                                      c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(k_pages, "k_pages")), _p(_contig(v_pages, "v_pages")), dtype_code(k_pages), pages, first, n,
+              E, P, Hkv, page_size, hd, _stream()), "clear_page_tails", -(-n // 120))
 
 
 # ------------------------------------------------------------------ bfloat16 tensor-core kernels
@@ -290,7 +371,8 @@ def gemm_skinny(a, w: torch.Tensor, epi: int, residual: torch.Tensor | None = No
     next_p, next_n = _next(next_w)
     _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), _p(residual), M, N, K, epi, in_sums, in_blocks, in_inv,
               in_eps, _p(gain), _p(rows.data) if rows else None, _p(rows.sums) if rows else None, next_p, next_n,
-              _stream()), "gemm_skinny")
+              _stream()), "gemm_skinny", 1, f"gemm_skinny:rows{-(-M // 8) * 8}" + (":norm_in" if in_blocks else "")
+           + (":norm_out" if rows else ""))
     return (out, rows) if emit is not None else out
 
 
@@ -308,6 +390,7 @@ def gemm_skinny_qkv(a, w: torch.Tensor, cos, sin, tok_pos, tok_seq, slots, page_
         raise KernelError(f"gemm_skinny_qkv: weight shape {tuple(w.shape)} is not [(H + 2 Hkv) hd, K]")
     if M > SKINNY_BEST_ROWS or K % 8 or hd % 16:
         raise KernelError(f"gemm_skinny_qkv: {M} rows (at most 16), width {K} (multiple of 8), head_dim {hd} (multiple of 16)")
+    _check_tables("gemm_skinny_qkv", cos, sin, hd)
     if out is None:
         out = torch.empty((M, H * hd), dtype=torch.bfloat16, device=a.device)
     fn = _fn("gemm_skinny", "lq_gemm_skinny_qkv", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
@@ -317,7 +400,8 @@ def gemm_skinny_qkv(a, w: torch.Tensor, cos, sin, tok_pos, tok_seq, slots, page_
     next_p, next_n = _next(next_w)
     _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), M, K, _p(cos), _p(sin), _p(tok_pos), _p(tok_seq),
               _p(slots), _p(page_table), page_table.stride(0), _p(k_pages), _p(v_pages), H, Hkv, hd, page_size,
-              in_sums, in_blocks, in_inv, in_eps, next_p, next_n, _stream()), "gemm_skinny_qkv")
+              in_sums, in_blocks, in_inv, in_eps, next_p, next_n, _stream()), "gemm_skinny_qkv", 1,
+           f"gemm_skinny_qkv:rows{-(-M // 8) * 8}" + (":norm_in" if in_blocks else ""))
     return out
 
 
@@ -347,7 +431,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, epi: int, residual: torch.Tensor |
     fn = _fn("gemm_tc", "lq_gemm_tc", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                        c_void_p])
     _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), _p(residual), M, N, K, epi, _p(scratch), _stream()),
-           "gemm_tc", 2 if splits > 1 else 1)
+           "gemm_tc", 2 if splits > 1 else 1, "gemm_tc:split_k" if splits > 1 else ("gemm_tc:few_rows" if M <= 64 else None))
     return out
 
 
@@ -364,6 +448,7 @@ def gemm_tc_qkv(a: torch.Tensor, w: torch.Tensor, cos, sin, tok_pos, tok_seq, sl
         raise KernelError(f"gemm_tc_qkv: weight shape {tuple(w.shape)} is not [(H + 2 Hkv) hd, K]")
     if K % 8 or hd not in (64, 128):
         raise KernelError(f"gemm_tc_qkv: width {K} (multiple of 8), head_dim {hd} (64 or 128)")
+    _check_tables("gemm_tc_qkv", cos, sin, hd)
     if out is None:
         out = torch.empty((M, H * hd), dtype=torch.bfloat16, device=a.device)
     splits = int(_fn("gemm_tc", "lq_gemm_tc_splits", [c_int, c_int, c_int])(M, N, K))
@@ -373,7 +458,8 @@ def gemm_tc_qkv(a: torch.Tensor, w: torch.Tensor, cos, sin, tok_pos, tok_seq, sl
                                            c_int, c_void_p, c_void_p])
     _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), M, K, _p(cos), _p(sin), _p(tok_pos), _p(tok_seq),
               _p(slots), _p(page_table), page_table.stride(0), _p(k_pages), _p(v_pages), H, Hkv, hd, page_size,
-              _p(scratch), _stream()), "gemm_tc_qkv", 2 if splits > 1 else 1)
+              _p(scratch), _stream()), "gemm_tc_qkv", 2 if splits > 1 else 1,
+           "gemm_tc_qkv:split_k" if splits > 1 else ("gemm_tc_qkv:few_rows" if M <= 64 else None))
     return out
 
 
@@ -473,7 +559,7 @@ def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq,
     _check(fn(_p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0), _p(tok_pos),
               _p(tok_seq), _p(slots), _p(part_o), _p(part_ml), _p(counters), _p(out), T, H, Hkv, hd, page_size,
               float(scale), int(window or 0), n_splits, next_p, next_n, int(early_loads), _stream()), "attn_decode",
-           2 if n_splits > 1 and counters is None else 1)
+           2 if n_splits > 1 and counters is None else 1, "attn_decode:one_slice" if n_splits == 1 else "attn_decode:slices")
     return out
 
 

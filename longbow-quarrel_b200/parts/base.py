@@ -74,19 +74,40 @@ class Part:
         """Take the tensors named by weights() (already on the device)."""
 
 
+class CacheNeed:
+    """What a mixer asks of the cache for one cache entry.  Entries whose needs are equal (needs are
+    hashable values) share one group of storage; the need itself says which kind of group that is, so a
+    mixer with storage of another shape brings its own: a frozen dataclass derived from this, whose
+    `make_group` returns a `cache.group.CacheGroup`."""
+
+    def make_group(self, entries: list[int], sizing):
+        """Storage for the cache entries `entries` (all with this need).  `sizing` is a
+        `cache.group.CacheSizing`: pages, page size, slots, dtype, device."""
+        raise NotImplementedError
+
+
 @dataclass(frozen=True)
-class KVNeed:
+class KVNeed(CacheNeed):
     """A mixer that keeps keys and values of every position (or of the last `window`)."""
     n_kv_heads: int
     head_dim: int
     window: int | None = None
 
+    def make_group(self, entries, sizing):
+        from ..cache.paged import PagedKVGroup
+        return PagedKVGroup(entries, self.n_kv_heads, self.head_dim, self.window, sizing.n_pages, sizing.page_size,
+                            sizing.max_slots, sizing.pages_per_seq, sizing.dtype, sizing.device)
+
 
 @dataclass(frozen=True)
-class StateNeed:
+class StateNeed(CacheNeed):
     """A mixer that keeps a state of fixed size for each sequence."""
     shape: tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+    def make_group(self, entries, sizing):
+        from ..cache.state import StateGroup
+        return StateGroup(entries, self.shape, self.dtype, sizing.max_slots, sizing.device)
 
 
 class Mixer(Part):
@@ -96,7 +117,7 @@ class Mixer(Part):
     # A part that leaves it False is always given finished rows and its return value is not read.
     folds_norm = False
 
-    def cache_need(self) -> KVNeed | StateNeed | None:
+    def cache_need(self) -> CacheNeed | None:
         return None
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache_view, residual: torch.Tensor,

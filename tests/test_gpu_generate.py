@@ -49,6 +49,25 @@ def test_greedy_generation_matches_plain(tmp_path, name, dtype):
     assert eng.last_stats.batches == 2 and eng.last_stats.prompt_tokens == 43
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_one_token_prompts_in_reused_slots_do_not_take_the_step_queued_for_the_batch_before(tmp_path, dtype):
+    """Batches of one sequence, prompts of one token: every batch gets the slot of the one before it, whose
+    last step was still queued ahead.  The new prompt must run; the old request's queued token is not its first."""
+    from longbow_quarrel_b200.sampling import SamplingParams
+    folder = make_model_folder(tmp_path, "A", seed=24)
+    cfg, weights = plain_llama.load_folder(folder)
+    eng = _engine(folder, dtype)
+    prompts = [[5], [6], [5], [200], [17, 3], [9]]
+    for batch_size in (1, 2):
+        out = eng.generate(prompts, max_new_tokens=5, sampling=SamplingParams(temperature=0.0), stop_ids=[],
+                           batch_size=batch_size)
+        assert out[0] == out[2]
+        for p, o in zip(prompts, out):
+            assert len(o) == 5
+            _check_greedy(cfg, weights, p, o, dtype)
+    assert eng.cache.pages_in_use() == 0 and eng.cache.slots.n_live == 0
+
+
 def test_stop_tokens_end_sequences_early(tmp_path):
     from longbow_quarrel_b200.sampling import SamplingParams
     folder = make_model_folder(tmp_path, "A", seed=22)

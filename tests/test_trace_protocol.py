@@ -44,6 +44,9 @@ class ScriptedEngine:
         self.log.append(("step", [s for s, _ in entries]))
         return torch.tensor(rows, dtype=torch.float32) if rows else None
 
+    def check(self):
+        self.checks = getattr(self, "checks", 0) + 1
+
     def close(self):
         self.log.append(("close",))
 
@@ -73,3 +76,30 @@ def test_steps_files_and_slots(tmp_path, monkeypatch, capsys):
     assert eng.log == [("step", [0, 1]), ("step", [0, 1]), ("end", 1), ("end", 0), ("step", [int(got[0, 0])]),
                        ("end", int(got[0, 0])), ("close",)]
     assert sorted(eng.free) == [0, 1, 2]                                    # every slot came back once
+    assert eng.checks == 2                                                  # after each read of a step's logits
+
+
+def test_a_wait_that_gave_up_is_raised_where_the_host_reads_results():
+    """The kernels with bounded waits write a code into a word of host memory; the check raises on it, names
+    the library and the wait, and clears the word.  (No device wait is made to run out: the word is set here.)"""
+    import ctypes
+
+    import pytest
+
+    from longbow_quarrel_b200.kernels import ops
+    word = (ctypes.c_int * 1)(0)
+    saved = dict(ops._status_words)
+    ops._status_words.clear()
+    ops._status_words["gemm_tc"] = word
+    try:
+        ops.check_status()                       # nothing recorded: no error
+        word[0] = 3
+        with pytest.raises(ops.KernelError, match="gemm_tc.*stage's copies.*code 3"):
+            ops.check_status()
+        assert word[0] == 0
+        ops.check_status()
+        ops._status_words["attn_prefill_tc"] = None      # a word that could not be set up is skipped
+        ops.check_status()
+    finally:
+        ops._status_words.clear()
+        ops._status_words.update(saved)
