@@ -21,8 +21,7 @@ def describe(cfg: LlamaConfig) -> ModelSpec:
     position = PartSpec("rope", {"head_dim": cfg.head_dim, "theta": cfg.rope_theta, "scaling": cfg.rope_scaling})
     layers = []
     for i in range(cfg.num_hidden_layers):
-        layers.append(LayerSpec(
-            prefix=f"model.layers.{i}.",
+        layers.append(LayerSpec(prefix=f"model.layers.{i}.", arrangement="pre_norm", parts=dict(
             norm1=PartSpec("rms_norm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps,
                                         "name": "input_layernorm.weight"}),
             mixer=PartSpec("attention", {
@@ -36,8 +35,7 @@ def describe(cfg: LlamaConfig) -> ModelSpec:
             ffn=PartSpec("gated_mlp", {
                 "hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size, "activation": "silu",
                 "names": {"gate": "mlp.gate_proj.weight", "up": "mlp.up_proj.weight",
-                          "down": "mlp.down_proj.weight"}}),
-            arrangement="pre_norm"))
+                          "down": "mlp.down_proj.weight"}}))))
     return ModelSpec(
         name="LlamaForCausalLM",
         hidden_size=cfg.hidden_size,

@@ -58,13 +58,11 @@ class Model:
             for name, spec in part.weights().items():
                 if prefix + name in tensors:
                     mine[name] = tensors[prefix + name]
-                elif spec.fallback is not None:
-                    mine[spec.fallback] = tensors[spec.fallback]
-                else:
+                elif spec.fallback is None:
                     raise KeyError(prefix + name)
-            tied = getattr(part, "tied_to", None)
-            if tied is not None and getattr(part, "tied", False):
-                mine[tied] = tensors[tied]
+            for full in part.borrows():              # tensors of other parts that this one reads as well
+                if full in tensors:
+                    mine[full] = tensors[full]
             part.load(mine)
 
     @property
@@ -74,7 +72,14 @@ class Model:
 
     def cache_needs(self) -> dict:
         """Cache entry -> what the mixer that writes it needs."""
-        return {e.cache: self.blocks[e.layer].mixer.cache_need() for e in self.spec.schedule if e.writes_cache}
+        return {e.cache: self.blocks[e.layer].cache_need() for e in self.spec.schedule if e.writes_cache}
+
+    def step_needs(self) -> dict:
+        """Name -> builder of every per-step integer array that some part asks for (see Part.step_needs)."""
+        out = {}
+        for _, part in self._named_parts():
+            out.update(part.step_needs())
+        return out
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0

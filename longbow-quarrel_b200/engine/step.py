@@ -15,10 +15,7 @@ import torch
 
 from ..cache import Cache
 from ..kernels import ops
-from ..parts.base import StepContext
-
-
-QUERY_BLOCK = 64
+from ..parts.base import StepContext, StepShape
 
 
 class StepError(ValueError):
@@ -49,9 +46,10 @@ def check_entries(entries, want, vocab_size: int) -> None:
                     raise StepError(f"wanted place {w} of sequence {b} is outside its {len(tokens)} tokens")
 
 
-def pack_step(entries, want, past: list[int]) -> tuple[np.ndarray, dict]:
+def pack_step(entries, want, past: list[int], needs: dict | None = None) -> tuple[np.ndarray, dict]:
     """All integers a step's kernels read, in one int32 array, and where each part lies.
-    `want` None asks for the last row of every sequence."""
+    `want` None asks for the last row of every sequence.  `needs`: name -> function of the step's
+    shape, for the arrays that parts of the model asked for (`Part.step_needs`)."""
     B = len(entries)
     new = [len(t) for _, t in entries]
     T = sum(new)
@@ -66,16 +64,14 @@ def pack_step(entries, want, past: list[int]) -> tuple[np.ndarray, dict]:
         rows = cu[1:] - 1
     else:
         rows = np.asarray([cu[b] + int(w) for b, ws in enumerate(want) for w in ws], dtype=np.int64)
-    # Work list of the prefill attention: blocks of at most 64 consecutive rows of one sequence.
-    def blocks(size):
-        qb = [(b, int(cu[b]) + r, min(size, n - r), p + r)
-              for b, (p, n) in enumerate(zip(past, new)) for r in range(0, n, size)]
-        qb.sort(key=lambda e: -e[3])          # blocks with the most keys first
-        return np.asarray(qb, dtype=np.int64).reshape(-1, 4)
-    qb, qc = blocks(QUERY_BLOCK), blocks(2 * QUERY_BLOCK)
     parts = {"tokens": tokens, "tok_seq": tok_seq, "tok_pos": tok_pos, "slots": slots, "kv_len": kv_len,
-             "cu_rows": cu, "want_rows": rows, "qb_seq": qb[:, 0], "qb_row": qb[:, 1], "qb_rows": qb[:, 2],
-             "qb_pos": qb[:, 3], "qc_seq": qc[:, 0], "qc_row": qc[:, 1], "qc_rows": qc[:, 2], "qc_pos": qc[:, 3]}
+             "cu_rows": cu, "want_rows": rows}
+    if needs:
+        shape = StepShape(B=B, T=T, past=tuple(int(p) for p in past), new=tuple(new), cu=tuple(int(c) for c in cu))
+        for name, build in needs.items():
+            if name in parts:
+                raise StepError(f"a part asks for a step array named {name!r}, which the step context uses itself")
+            parts[name] = np.asarray(build(shape)).reshape(-1)
     layout, offset = {}, 0
     for name, arr in parts.items():
         layout[name] = (offset, len(arr))
@@ -85,7 +81,7 @@ def pack_step(entries, want, past: list[int]) -> tuple[np.ndarray, dict]:
         o, n = layout[name]
         flat[o:o + n] = arr
     info = {"layout": layout, "B": B, "T": T, "new": new, "past": list(past), "max_new": max(new),
-            "max_kv": int(kv_len.max())}
+            "max_kv": int(kv_len.max()), "extra": [n for n in parts if needs and n in needs]}
     return flat, info
 
 
@@ -96,11 +92,9 @@ def make_context(flat_dev: torch.Tensor, info: dict, h_slots: list[int]) -> Step
     want = part("want_rows")
     return StepContext(T=info["T"], B=info["B"], tokens=part("tokens"), tok_seq=part("tok_seq"),
                        tok_pos=part("tok_pos"), slots=part("slots"), kv_len=part("kv_len"), cu_rows=part("cu_rows"),
-                       want_rows=want if want.numel() else None,
-                       query_blocks=(part("qb_seq"), part("qb_row"), part("qb_rows"), part("qb_pos")),
-                       query_blocks128=(part("qc_seq"), part("qc_row"), part("qc_rows"), part("qc_pos")),
-                       h_slots=h_slots, h_new=info["new"],
-                       h_past=info["past"], max_new=info["max_new"], max_kv=info["max_kv"])
+                       want_rows=want if want.numel() else None, h_slots=h_slots, h_new=info["new"],
+                       h_past=info["past"], max_new=info["max_new"], max_kv=info["max_kv"],
+                       extra={name: part(name) for name in info.get("extra", [])})
 
 
 class Stepper:
@@ -112,6 +106,7 @@ class Stepper:
     def __init__(self, model, cache: Cache, device, use_graphs: bool = True):
         self.model, self.cache, self.device = model, cache, device
         self.use_graphs = use_graphs and model.graph_safe
+        self.needs = model.step_needs()
         self._graphs: dict[int, "_DecodeGraph"] = {}
         self._seen: set[int] = set()
 
@@ -128,7 +123,7 @@ class Stepper:
         if decode and self.use_graphs and self.model.probe is None:
             logits = self._decode_step(entries, want, past)
         else:
-            flat, info = pack_step(entries, want, past)
+            flat, info = pack_step(entries, want, past, self.needs)
             flat_dev = torch.from_numpy(flat).to(self.device)
             ctx = make_context(flat_dev, info, [s for s, _ in entries])
             logits = self.model.forward(ctx, self.cache)
@@ -153,7 +148,7 @@ class Stepper:
         if self.use_graphs and self.model.probe is None:
             logits = self._decode_step(entries, None, past, fed=source)
         else:
-            flat, info = pack_step(entries, None, past)
+            flat, info = pack_step(entries, None, past, self.needs)
             flat_dev = torch.from_numpy(flat).to(self.device)
             ctx = make_context(flat_dev, info, slots)
             ctx.tokens.copy_(source)
@@ -164,7 +159,7 @@ class Stepper:
 
     def _decode_step(self, entries, want, past, fed: torch.Tensor | None = None):
         B = len(entries)
-        flat, info = pack_step(entries, None, past)
+        flat, info = pack_step(entries, None, past, self.needs)
         if B not in self._seen:
             # The first step of a batch size runs eagerly: it loads kernels and sizes buffers.
             self._seen.add(B)

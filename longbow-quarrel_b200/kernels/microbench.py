@@ -132,7 +132,7 @@ def bench_attn_decode(args) -> dict:
     q = torch.randn(B, (H + 2 * Hkv) * hd, device=dev, dtype=torch.bfloat16)
     pos = torch.full((B,), C - 1, dtype=torch.int32, device=dev)
     seq = torch.arange(B, dtype=torch.int32, device=dev)
-    splits = args.splits or attention.decode_splits(B, Hkv, -(-(H // Hkv) // 16), C)
+    splits = args.splits or attention.decode_splits(B, Hkv, -(-(H // Hkv) // 16), C, attention.resident_blocks('cuda'))
 
     def run(i):
         k, v, table = caches[i % n]

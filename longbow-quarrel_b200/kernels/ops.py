@@ -478,8 +478,8 @@ def attn_prefill(q: torch.Tensor, k_pages, v_pages, page_table, slots, kv_len, q
     T = q.shape[0]
     if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
         raise KernelError("attn_prefill takes bfloat16 queries and cache")
-    if hd % 8 or hd > 128 or page_size != 64:
-        raise KernelError(f"attn_prefill: head_dim {hd} (multiple of 8, at most 128), page size {page_size} (64)")
+    if hd % 16 or hd > 128 or page_size != 64:
+        raise KernelError(f"attn_prefill: head_dim {hd} (multiple of 16, at most 128), page size {page_size} (64)")
     if out is None:
         out = torch.empty((T, H * hd), dtype=torch.bfloat16, device=q.device)
     qb_seq, qb_row, qb_rows, qb_pos = query_blocks
@@ -533,8 +533,8 @@ def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq,
     T = q.shape[0]
     if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
         raise KernelError("attn_decode takes bfloat16 queries and cache")
-    if hd % 8 or hd > 128:
-        raise KernelError(f"attn_decode: head_dim {hd} must be a multiple of 8 and at most 128")
+    if hd % 16 or hd > 128:
+        raise KernelError(f"attn_decode: head_dim {hd} must be a multiple of 16 and at most 128")
     if out is None:
         out = torch.empty((T, H * hd), dtype=torch.bfloat16, device=q.device)
     part_o = part_ml = None

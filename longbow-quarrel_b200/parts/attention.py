@@ -35,8 +35,10 @@ class Attention(Mixer):
                  own_kv: bool = True, names: dict | None = None):
         if n_heads % n_kv_heads:
             raise ValueError(f"attention: {n_heads} heads are not a multiple of {n_kv_heads} kv heads")
-        if head_dim % 16 or head_dim > 256:
-            raise ValueError(f"attention: head_dim {head_dim} must be a multiple of 16 and at most 256")
+        if head_dim % 2 or not 2 <= head_dim <= 256:
+            # Pairs of the rotation need an even size; the plain kernels hold a head in 256 threads' registers.
+            # Which of the faster kernels take a head size is each kernel's own rule (kernels/attention.py).
+            raise ValueError(f"attention: head_dim {head_dim} must be even and at most 256")
         self.runtime = runtime
         self.D, self.H, self.Hkv, self.hd = hidden_size, n_heads, n_kv_heads, head_dim
         self.scale, self.window, self.own_kv = float(scale), window, own_kv
@@ -47,6 +49,9 @@ class Attention(Mixer):
 
     def cache_need(self):
         return KVNeed(self.Hkv, self.hd, self.window)
+
+    def step_needs(self):
+        return attention_kernels.step_needs(self.runtime.act_dtype, self.hd)
 
     def weights(self):
         n = self.names
@@ -70,7 +75,7 @@ class Attention(Mixer):
         store = self.own_kv and writes_cache
         tables = self.position.tables() if self.position is not None else None
         fused = (store and h.dtype == torch.bfloat16 and self.w_qkv.tensor.dtype == torch.bfloat16 and self.D % 8 == 0
-                 and cache_view.k_pages.dtype == torch.bfloat16 and (self.position is None or tables is not None))
+                 and self.hd % 16 == 0 and cache_view.k_pages.dtype == torch.bfloat16 and (self.position is None or tables is not None))
         few = h.shape[0] <= ops.SKINNY_BEST_ROWS
         if fused and (few or (self.hd in (64, 128) and not isinstance(h, ops.NormedRows))):
             # Projection, rotation and cache write are one kernel (for few tokens the one that streams the

@@ -7,7 +7,9 @@ which rows belong to which sequence and where they stand.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
+from typing import Callable
 
+import numpy as np
 import torch
 
 from ..weights.spec import WeightSpec
@@ -28,12 +30,29 @@ class Runtime:
         return self.dtype
 
 
+@dataclass(frozen=True)
+class StepShape:
+    """What the host knows of a step before it is packed: for each of its B sequences how many tokens
+    it holds already (`past`) and how many it brings (`new`), and where each sequence's rows start in
+    the packed batch (`cu`, B + 1 entries).  Parts build their own per-step integers from it."""
+    B: int
+    T: int
+    past: tuple[int, ...]
+    new: tuple[int, ...]
+    cu: tuple[int, ...]
+
+    @property
+    def max_new(self) -> int:
+        return max(self.new)
+
+
 @dataclass
 class StepContext:
     """The packed rows of one step.  T rows of B sequences; row r belongs to sequence
     tok_seq[r] of the batch and stands at position tok_pos[r] of that sequence; the
     sequence lives in cache slot slots[b] and holds kv_len[b] tokens once this step's
-    rows are stored.  All tensors are int32 on the device; the `h_` twins are host lists."""
+    rows are stored.  All tensors are int32 on the device; the `h_` twins are host lists.
+    `extra` holds the int32 arrays that parts asked for through `Part.step_needs`, by name."""
     T: int
     B: int
     tokens: torch.Tensor
@@ -43,13 +62,12 @@ class StepContext:
     kv_len: torch.Tensor
     cu_rows: torch.Tensor
     want_rows: torch.Tensor | None
-    query_blocks: tuple | None      # (sequence, first row, rows, first position) of each 64-row block, int32
-    query_blocks128: tuple | None   # the same for blocks of 128 rows
     h_slots: list[int]
     h_new: list[int]
     h_past: list[int]
     max_new: int
     max_kv: int
+    extra: dict = field(default_factory=dict)
 
     @property
     def decode(self) -> bool:
@@ -72,6 +90,20 @@ class Part:
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         """Take the tensors named by weights() (already on the device)."""
+
+    def borrows(self) -> list[str]:
+        """Full names of tensors of other parts that this part reads as well (a head tied to the
+        embedding table); `load` is given them beside its own."""
+        return []
+
+    def step_needs(self) -> dict[str, Callable[[StepShape], np.ndarray]]:
+        """Integers that this part's kernels need for every step beyond the step context's own fields: a
+        name, and a function that makes the array from the step's shape on the host.  The step function
+        packs every array that some part of the model names (once per name) into the step's one buffer
+        and hands it over as `ctx.extra[name]` (int32, on the device).  For steps of one token per
+        sequence the array's length may depend on the number of sequences only (such steps are captured
+        once per batch size)."""
+        return {}
 
 
 class CacheNeed:

@@ -14,13 +14,26 @@ from .spec import LayerSpec
 class PreNormBlock(Part):
     def __init__(self, runtime: Runtime, layer: LayerSpec):
         self.prefix = layer.prefix
-        self.norm1 = make_part("norm", layer.norm1, runtime)
-        self.mixer = make_part("mixer", layer.mixer, runtime)
-        self.norm2 = make_part("norm", layer.norm2, runtime)
-        self.ffn = make_part("ffn", layer.ffn, runtime)
+        unknown = set(layer.parts) - {"norm1", "mixer", "norm2", "ffn"}
+        if unknown:
+            raise ValueError(f"layer {layer.prefix!r}: the arrangement 'pre_norm' has no place {sorted(unknown)}")
+        self.norm1 = make_part("norm", layer.part("norm1"), runtime)
+        self.mixer = make_part("mixer", layer.part("mixer"), runtime)
+        self.norm2 = make_part("norm", layer.part("norm2"), runtime)
+        self.ffn = make_part("ffn", layer.part("ffn"), runtime)
 
     def parts(self):
         return (self.norm1, self.mixer, self.norm2, self.ffn)
+
+    def cache_need(self):
+        """What the layer's cache entry must hold: its mixer's need."""
+        return self.mixer.cache_need()
+
+    def step_needs(self):
+        out = {}
+        for part in self.parts():
+            out.update(part.step_needs())
+        return out
 
     @property
     def graph_safe(self):

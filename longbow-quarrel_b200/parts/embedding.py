@@ -52,6 +52,9 @@ class LinearHead(Part):
             return {}
         return {self.name: WeightSpec((self.vocab_size, self.hidden_size), fallback=self.tied_to)}
 
+    def borrows(self):
+        return [self.tied_to] if self.tied_to is not None else []
+
     def load(self, tensors):
         w = tensors.get(self.name)
         if w is None:

@@ -7,7 +7,7 @@ parts it names from the part registry.  Nothing here knows an architecture.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any
+from typing import Any, Mapping
 
 
 @dataclass(frozen=True)
@@ -19,16 +19,25 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One block: how its parts are arranged, and the parts.
+    """One block: how its parts are arranged, and the parts by the names that the arrangement gives
+    their places.
 
-    prefix  what the tensor names of this layer's parts start with.
+    prefix       what the tensor names of this layer's parts start with.
+    parts        place -> part.  Which places there are is the arrangement's business: "pre_norm" has
+                 `norm1`, `mixer`, `norm2`, `ffn`; an arrangement with a third norm or with two branches
+                 side by side names more places and needs no change here.
+    arrangement  the block class (registered under the role "block") that reads `parts`.
     """
     prefix: str
-    mixer: PartSpec
-    ffn: PartSpec
-    norm1: PartSpec
-    norm2: PartSpec
+    parts: Mapping[str, PartSpec]
     arrangement: str = "pre_norm"
+
+    def part(self, place: str) -> PartSpec:
+        try:
+            return self.parts[place]
+        except KeyError:
+            raise ValueError(f"layer {self.prefix!r}: the arrangement {self.arrangement!r} needs a part in the "
+                             f"place {place!r} (given: {', '.join(sorted(self.parts)) or 'none'})") from None
 
 
 @dataclass(frozen=True)

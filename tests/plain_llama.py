@@ -117,13 +117,15 @@ def rope(x: torch.Tensor, positions, freqs: np.ndarray) -> torch.Tensor:
     return torch.cat([x0 * cos - x1 * sin, x0 * sin + x1 * cos], dim=-1)
 
 
-def attention(q, k, v, scale: float, window: int | None = None) -> torch.Tensor:
+def attention(q, k, v, scale: float, window: int | None = None, round_probabilities=None) -> torch.Tensor:
     """Causal grouped-query attention over one whole sequence.
     kv head of query head h is h // (H / Hkv): internal/device/kernels.metal:671;
     score = q.k * scale over keys start..p, own position included (:697-704);
     start = p - window + 1 when a window is set and p >= window (:676);
     softmax with the maximum subtracted (:710-756); out = sum_t p_t v_t (:759-766).
-    q [T, H, hd], k and v [T, Hkv, hd] -> [T, H, hd]."""
+    q [T, H, hd], k and v [T, Hkv, hd] -> [T, H, hd].
+    round_probabilities: a function applied to exp(s - max) before the sum and the product with v (see
+    `forward(storage=...)`)."""
     T, H, hd = q.shape
     Hkv = k.shape[1]
     group = H // Hkv
@@ -136,7 +138,11 @@ def attention(q, k, v, scale: float, window: int | None = None) -> torch.Tensor:
         kvh = h // group
         s = (q[:, h, :] @ k[:, kvh, :].T) * scale
         s = s.masked_fill(~allowed, float("-inf"))
-        p = torch.softmax(s, dim=-1)
+        if round_probabilities is None:
+            p = torch.softmax(s, dim=-1)
+        else:
+            e = round_probabilities(torch.exp(s - s.max(dim=-1, keepdim=True).values))
+            p = e / e.sum(dim=-1, keepdim=True)
         out[:, h, :] = p @ v[:, kvh, :]
     return out
 
@@ -170,36 +176,49 @@ def layer_window(cfg: dict, layer: int) -> int | None:
 
 
 def forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, start_pos: int = 0,
-            return_hidden: bool = False) -> torch.Tensor:
-    """Logits [T, vocab] at every position of one whole sequence.
+            return_hidden: bool = False, return_layers: bool = False, storage=None):
+    """Logits [T, vocab] at every position of one whole sequence (with return_layers: also the residual
+    stream after the embedding and after every layer, both as numpy arrays).
     Block order x += Attn(norm(x)); x += FFN(norm(x)) with two pre-norms:
     internal/device/metal.go:1347-1527 (Tensor.Layer); final norm and LM head:
     internal/engine/engine.go:1547,1561; tied head when there is no lm_head tensor:
-    internal/engine/engine.go:1108-1111."""
+    internal/engine/engine.go:1108-1111.
+
+    storage: a dtype (torch.bfloat16) in which activations are kept between the operations, as an engine
+    of that precision keeps them: the normed rows, q, k and v, the probabilities, the attention's output
+    and the feed-forward's inner rows are rounded to it; sums, norms, softmax and the residual stream stay
+    in `dtype`.  The difference to the unrounded result is the error that this storage precision alone
+    causes, whatever the kernels: the yardstick for what an engine of that precision may differ by."""
     D, H, Hkv, hd = _cfg(cfg)
+    keep = (lambda t: t) if storage is None else (lambda t: t.to(storage).to(dtype))
     eps = cfg.get("rms_norm_eps", 1e-5)
     freqs = rope_frequencies(hd, cfg.get("rope_theta", 10000.0), cfg.get("rope_scaling"))
     W = {k: v.to(dtype) for k, v in weights.items()}
     T = len(tokens)
     pos = np.arange(start_pos, start_pos + T)
     x = embedding(W["model.embed_tokens.weight"], tokens)
+    layers = [x.numpy().copy()]            # the residual stream after the embedding and after every layer
     for l in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{l}."
-        n = rms_norm(x, W[p + "input_layernorm.weight"], eps)
+        n = keep(rms_norm(x, W[p + "input_layernorm.weight"], eps))
         q = linear(n, W[p + "self_attn.q_proj.weight"]).reshape(T, H, hd)
         k = linear(n, W[p + "self_attn.k_proj.weight"]).reshape(T, Hkv, hd)
-        v = linear(n, W[p + "self_attn.v_proj.weight"]).reshape(T, Hkv, hd)
-        q, k = rope(q, pos, freqs), rope(k, pos, freqs)
-        a = attention(q, k, v, hd ** -0.5, layer_window(cfg, l)).reshape(T, H * hd)
+        v = keep(linear(n, W[p + "self_attn.v_proj.weight"]).reshape(T, Hkv, hd))
+        q, k = keep(rope(q, pos, freqs)), keep(rope(k, pos, freqs))
+        a = keep(attention(q, k, v, hd ** -0.5, layer_window(cfg, l),
+                           None if storage is None else keep).reshape(T, H * hd))
         x = x + linear(a, W[p + "self_attn.o_proj.weight"])
-        n = rms_norm(x, W[p + "post_attention_layernorm.weight"], eps)
+        n = keep(rms_norm(x, W[p + "post_attention_layernorm.weight"], eps))
         g = linear(n, W[p + "mlp.gate_proj.weight"])
         u = linear(n, W[p + "mlp.up_proj.weight"])
-        x = x + linear(swiglu(g, u), W[p + "mlp.down_proj.weight"])
+        x = x + linear(keep(swiglu(g, u)), W[p + "mlp.down_proj.weight"])
+        layers.append(x.numpy().copy())
     if return_hidden:
         return x
-    n = rms_norm(x, W["model.norm.weight"], eps)
+    n = keep(rms_norm(x, W["model.norm.weight"], eps))
     head = W["lm_head.weight"] if "lm_head.weight" in W else W["model.embed_tokens.weight"]
+    if return_layers:
+        return linear(n, head).numpy(), np.stack(layers)       # logits [T, vocab], stream [layers + 1, T, D]
     return linear(n, head)
 
 

@@ -105,13 +105,16 @@ def test_describe_takes_every_constant_from_the_config():
         cfg = LlamaConfig.from_dict(TINY[name])
         spec = describe(cfg)
         assert len(spec.layers) == cfg.num_hidden_layers == len(spec.schedule)
-        mixer = spec.layers[0].mixer.params
+        mixer = spec.layers[0].part("mixer").params
         assert mixer["n_heads"] == cfg.num_attention_heads and mixer["n_kv_heads"] == cfg.num_key_value_heads
         assert mixer["head_dim"] == cfg.head_dim and mixer["scale"] == cfg.head_dim ** -0.5
         assert mixer["position"].params["theta"] == cfg.rope_theta
         assert mixer["position"].params["scaling"] == cfg.rope_scaling
-        assert spec.layers[-1].ffn.params["intermediate_size"] == cfg.intermediate_size
+        assert spec.layers[-1].part("ffn").params["intermediate_size"] == cfg.intermediate_size
         assert spec.final_norm.params["eps"] == cfg.rms_norm_eps
         assert spec.head.params["tied"] == cfg.tie_word_embeddings
         assert spec.stop_tokens == cfg.eos_token_id
-        assert [l.mixer.params["window"] for l in spec.layers] == [cfg.window_of_layer(i) for i in range(len(spec.layers))]
+        assert sorted(spec.layers[0].parts) == ["ffn", "mixer", "norm1", "norm2"]
+        with pytest.raises(ValueError, match="needs a part in the place 'norm3'"):
+            spec.layers[0].part("norm3")
+        assert [l.part("mixer").params["window"] for l in spec.layers] == [cfg.window_of_layer(i) for i in range(len(spec.layers))]

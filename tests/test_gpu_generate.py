@@ -30,7 +30,7 @@ def _check_greedy(cfg, weights, prompt, generated, dtype, stop=()):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_greedy_generation_matches_plain(tmp_path, name, dtype):
     from longbow_quarrel_b200.sampling import SamplingParams
     folder = make_model_folder(tmp_path, name, seed=21)

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 import plain_llama as pl
-from helpers import rel_err
+from helpers import TOL, rel_err
 
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")
@@ -16,9 +16,9 @@ def _runtime(dtype, max_context=256):
     return Runtime(DEV, dtype, max_context)
 
 
-def _ctx(entries, past):
+def _ctx(entries, past, part=None):
     from longbow_quarrel_b200.engine.step import make_context, pack_step
-    flat, info = pack_step(entries, None, past)
+    flat, info = pack_step(entries, None, past, part.step_needs() if part is not None else None)
     return make_context(torch.from_numpy(flat).to(DEV), info, [s for s, _ in entries])
 
 
@@ -91,7 +91,7 @@ def test_attention_part(dtype, window):
     for s, n in zip(slots, lens):
         cache.reserve(s, n)
     cache.upload()
-    ctx = _ctx([(s, [0] * n) for s, n in zip(slots, lens)], [0, 0])
+    ctx = _ctx([(s, [0] * n) for s, n in zip(slots, lens)], [0, 0], part)
     h = torch.cat([x[:n] for x, n in zip(xs, lens)]).to(dtype).to(DEV)
     resid = torch.zeros((sum(lens), D), dtype=torch.float32, device=DEV)
     part.forward(h, ctx, cache.view(0), resid)
@@ -104,7 +104,7 @@ def test_attention_part(dtype, window):
     for s in slots:
         cache.reserve(s, 1)
     cache.upload()
-    ctx = _ctx([(s, [0]) for s in slots], lens)
+    ctx = _ctx([(s, [0]) for s in slots], lens, part)
     h = torch.stack([x[n] for x, n in zip(xs, lens)]).to(dtype).to(DEV)
     resid = torch.ones((2, D), dtype=torch.float32, device=DEV)
     part.forward(h, ctx, cache.view(0), resid)
@@ -197,8 +197,8 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
         ffn = PartSpec("gated_mlp", {"hidden_size": cfg.hidden_size, "intermediate_size": 48})
         attn = PartSpec("attention", {"hidden_size": cfg.hidden_size, "n_heads": 2, "n_kv_heads": 1, "head_dim": 16,
                                       "scale": 0.25, "position": PartSpec("rope", {"head_dim": 16, "theta": 1e4})})
-        layers = (LayerSpec("l0.", PartSpec("toy_running_sum", {"hidden_size": cfg.hidden_size}), ffn, norm("n1"), norm("n2")),
-                  LayerSpec("l1.", attn, ffn, norm("n1"), norm("n2")))
+        layer = lambda prefix, mixer: LayerSpec(prefix, dict(mixer=mixer, ffn=ffn, norm1=norm("n1"), norm2=norm("n2")))  # noqa: E731
+        layers = (layer("l0.", PartSpec("toy_running_sum", {"hidden_size": cfg.hidden_size})), layer("l1.", attn))
         return ModelSpec(name="ToyStateLM", hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size,
                          embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size,
                                                                 "hidden_size": cfg.hidden_size, "name": "emb"}),
@@ -301,10 +301,12 @@ def test_a_routed_feed_forward_and_a_learned_position_encoding_from_a_test():
         norm = lambda name: PartSpec("rms_norm", {"size": D, "eps": 1e-5, "name": name})  # noqa: E731
         attn = lambda position: PartSpec("attention", {"hidden_size": D, "n_heads": H, "n_kv_heads": Hkv,  # noqa: E731
                                                        "head_dim": hd, "scale": hd ** -0.5, "position": position})
-        layers = (LayerSpec("l0.", attn(PartSpec("toy_learned_shift", {"head_dim": hd, "positions": P})),
-                            PartSpec("toy_routed", {"hidden_size": D, "inner": F, "experts": E}), norm("n1"), norm("n2")),
-                  LayerSpec("l1.", attn(PartSpec("rope", {"head_dim": hd, "theta": 1e4})),
-                            PartSpec("gated_mlp", {"hidden_size": D, "intermediate_size": 64}), norm("n1"), norm("n2")))
+        layers = (LayerSpec("l0.", dict(mixer=attn(PartSpec("toy_learned_shift", {"head_dim": hd, "positions": P})),
+                                        ffn=PartSpec("toy_routed", {"hidden_size": D, "inner": F, "experts": E}),
+                                        norm1=norm("n1"), norm2=norm("n2"))),
+                  LayerSpec("l1.", dict(mixer=attn(PartSpec("rope", {"head_dim": hd, "theta": 1e4})),
+                                        ffn=PartSpec("gated_mlp", {"hidden_size": D, "intermediate_size": 64}),
+                                        norm1=norm("n1"), norm2=norm("n2"))))
         return ModelSpec(name="ToyRoutedLM", hidden_size=D, vocab_size=V,
                          embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": D, "name": "emb"}),
                          layers=layers, schedule=(ScheduleEntry(0, 0), ScheduleEntry(1, 1)), final_norm=norm("fn"),
@@ -397,8 +399,8 @@ def test_a_layer_run_twice_and_a_layer_that_reads_anothers_cache():
         attn = lambda own: PartSpec("attention", {"hidden_size": D, "n_heads": H, "n_kv_heads": Hkv, "head_dim": hd,  # noqa: E731
                                                   "scale": hd ** -0.5, "position": rope, "own_kv": own})
         ffn = PartSpec("gated_mlp", {"hidden_size": D, "intermediate_size": F})
-        layers = (LayerSpec("a.", attn(True), ffn, norm("n1"), norm("n2")),
-                  LayerSpec("b.", attn(False), ffn, norm("n1"), norm("n2")))
+        layers = (LayerSpec("a.", dict(mixer=attn(True), ffn=ffn, norm1=norm("n1"), norm2=norm("n2"))),
+                  LayerSpec("b.", dict(mixer=attn(False), ffn=ffn, norm1=norm("n1"), norm2=norm("n2"))))
         return ModelSpec(name="ToyScheduleLM", hidden_size=D, vocab_size=V,
                          embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": D, "name": "emb"}),
                          layers=layers,
@@ -468,3 +470,211 @@ def test_a_layer_run_twice_and_a_layer_that_reads_anothers_cache():
             got = eng.step([(slot, [tokens[i]])]).cpu().numpy()[0]
             assert rel_err(got, ref[i]) < tol, (dtype, i)
         eng.end_sequence(slot)
+
+
+# ------------------------------------------------------------------ storage, step integers and arrangement of a test's own
+def test_a_mixer_with_storage_of_its_own_a_step_array_and_a_block_with_a_third_norm():
+    """Three things that only registrations add, each defined here and none in the framework:
+    a mixer whose keys and values have different widths, with a cache need and a cache group of its own
+    (dense rows per slot, no pages); a per-step integer array of its own, packed by the step function and
+    found in `ctx.extra`; and an arrangement with a third norm (the feed-forward's output is normed before
+    it joins the residual stream).  Whole prompts, cut prompts and single tokens agree with the same
+    computation in float64, in slots that are used again."""
+    from dataclasses import dataclass
+
+    from longbow_quarrel_b200.cache import CacheError, CacheGroup
+    from longbow_quarrel_b200.config import register_architecture
+    from longbow_quarrel_b200.engine import Engine
+    from longbow_quarrel_b200.parts import (CacheNeed, LayerSpec, Mixer, ModelSpec, Part, PartSpec, ScheduleEntry,
+                                            make_part, register_part)
+    from longbow_quarrel_b200.weights import WeightSpec
+
+    D, DK, DV, V, F = 40, 12, 28, 70, 56
+
+    class DenseRows(CacheGroup):
+        """keys [entry, slot, position, dk] and values [entry, slot, position, dv]: a row per position."""
+
+        def __init__(self, entries, dk, dv, sizing):
+            self.entries, self.index = list(entries), {e: i for i, e in enumerate(entries)}
+            self.limit = sizing.max_context
+            self.k = torch.full((len(entries), sizing.max_slots, self.limit, dk), float("nan"), device=sizing.device)
+            self.v = torch.full((len(entries), sizing.max_slots, self.limit, dv), float("nan"), device=sizing.device)
+            self.started, self.released = [], []
+
+        def start(self, slot):
+            self.started.append(slot)
+
+        def reserve(self, slot, old_len, new_len):
+            if new_len > self.limit:
+                raise CacheError("toy rows are full")
+
+        def release(self, slot):
+            self.released.append(slot)
+            self.k[:, slot] = float("nan")           # what a sequence leaves must never be read again
+            self.v[:, slot] = float("nan")
+
+        def view(self, entry):
+            return self.k[self.index[entry]], self.v[self.index[entry]]
+
+        def nbytes(self):
+            return 4 * (self.k.numel() + self.v.numel())
+
+    @dataclass(frozen=True)
+    class RowsNeed(CacheNeed):
+        dk: int
+        dv: int
+
+        def make_group(self, entries, sizing):
+            return DenseRows(entries, self.dk, self.dv, sizing)
+
+    @register_part("mixer", "toy_wide_values")
+    class WideValues(Mixer):
+        """One head; scores over keys of width dk, values of width dv; causal."""
+
+        def __init__(self, runtime, hidden_size, dk, dv):
+            self.D, self.dk, self.dv = hidden_size, dk, dv
+
+        def weights(self):
+            return {"wq": WeightSpec((self.dk, self.D)), "wk": WeightSpec((self.dk, self.D)),
+                    "wv": WeightSpec((self.dv, self.D)), "wo": WeightSpec((self.D, self.dv))}
+
+        def load(self, tensors):
+            self.t = {k: v.float() for k, v in tensors.items()}
+
+        def cache_need(self):
+            return RowsNeed(self.dk, self.dv)
+
+        def step_needs(self):
+            # For every sequence of the step: its first row in the packed batch and its rows, as [2, B].
+            return {"toy_row_ranges": lambda step: np.asarray([step.cu[:-1], step.new], dtype=np.int32)}
+
+        def forward(self, h, ctx, rows, residual, writes_cache=True):
+            keys, values = rows
+            ranges = ctx.extra["toy_row_ranges"].view(2, -1).cpu().tolist()      # the part's own step integers
+            assert ranges[1] == ctx.h_new
+            x = h.float()
+            for b, (first, n) in enumerate(zip(*ranges)):
+                slot, past = ctx.h_slots[b], ctx.h_past[b]
+                xs = x[first:first + n]
+                keys[slot, past:past + n] = xs @ self.t["wk"].T
+                values[slot, past:past + n] = xs @ self.t["wv"].T
+                s = (xs @ self.t["wq"].T) @ keys[slot, :past + n].T / self.dk ** 0.5
+                pos = torch.arange(past, past + n, device=x.device)[:, None]
+                s = s.masked_fill(torch.arange(past + n, device=x.device)[None, :] > pos, float("-inf"))
+                residual[first:first + n] += torch.softmax(s, dim=-1) @ values[slot, :past + n] @ self.t["wo"].T
+
+    @register_part("block", "toy_sandwich")
+    class Sandwich(Part):
+        """x += mixer(norm1(x)); x += norm3(ffn(norm2(x))): the place `norm3` is this arrangement's own."""
+
+        def __init__(self, runtime, layer):
+            self.prefix = layer.prefix
+            self.norm1, self.norm2, self.norm3 = (make_part("norm", layer.part(p), runtime) for p in ("norm1", "norm2", "norm3"))
+            self.mixer = make_part("mixer", layer.part("mixer"), runtime)
+            self.ffn = make_part("ffn", layer.part("ffn"), runtime)
+
+        def parts(self):
+            return (self.norm1, self.mixer, self.norm2, self.ffn, self.norm3)
+
+        def weights(self):
+            return {name: spec for part in self.parts() for name, spec in part.weights().items()}
+
+        def load(self, tensors):
+            for part in self.parts():
+                part.load({n: tensors[n] for n in part.weights()})
+
+        def cache_need(self):
+            return self.mixer.cache_need()
+
+        def step_needs(self):
+            return self.mixer.step_needs()
+
+        def forward(self, x, ctx, cache_view, writes_cache=True):
+            self.mixer.forward(self.norm1.forward(x), ctx, cache_view, x, writes_cache)
+            branch = torch.zeros_like(x)
+            self.ffn.forward(self.norm2.forward(x), ctx, branch)
+            x += self.norm3.forward(branch).float()
+
+    @dataclass(frozen=True)
+    class Cfg:
+        architectures: tuple = ("ToySandwichLM",)
+
+    def describe(cfg):
+        norm = lambda name: PartSpec("rms_norm", {"size": D, "eps": 1e-5, "name": name})  # noqa: E731
+        layers = tuple(LayerSpec(f"l{i}.", arrangement="toy_sandwich", parts=dict(
+            mixer=PartSpec("toy_wide_values", {"hidden_size": D, "dk": DK, "dv": DV}),
+            ffn=PartSpec("gated_mlp", {"hidden_size": D, "intermediate_size": F}),
+            norm1=norm("n1"), norm2=norm("n2"), norm3=norm("n3"))) for i in range(2))
+        return ModelSpec(name="ToySandwichLM", hidden_size=D, vocab_size=V,
+                         embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": D, "name": "emb"}),
+                         layers=layers, schedule=(ScheduleEntry(0, 0), ScheduleEntry(1, 1)), final_norm=norm("fn"),
+                         head=PartSpec("linear_head", {"vocab_size": V, "hidden_size": D, "name": "head",
+                                                       "tied_to": "emb", "tied": True}),
+                         max_positions=128)
+
+    register_architecture("ToySandwichLM", lambda d: Cfg(), describe)
+    eng = Engine.from_config({"architectures": ["ToySandwichLM"]}, seed=5, dtype="float32", max_tokens=512,
+                             std=0.3, gain_std=0.1, weight_dtype=torch.float32)
+    group = eng.cache.groups[0]
+    assert isinstance(group, DenseRows) and group.entries == [0, 1] and eng.cache.kv_groups == []
+    assert list(eng.stepper.needs) == ["toy_row_ranges"] and not eng.stepper.use_graphs
+
+    # the same computation, whole sequences in float64
+    w = {}
+    for prefix, part in eng.model._named_parts():
+        for owner in (part.parts() if hasattr(part, "parts") else (part,)):
+            for key, value in vars(owner).items():
+                if key == "t":
+                    w.update({prefix + k: v.double().cpu() for k, v in value.items()})
+    blocks = eng.model.blocks
+    emb = eng.model.embedding.table.double().cpu()
+
+    def rms(x, gain):
+        return x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-5) * gain.double().cpu()
+
+    def reference(tokens):
+        x = emb[torch.tensor(tokens)]
+        T = len(tokens)
+        for i, blk in enumerate(blocks):
+            p = f"l{i}."
+            n = rms(x, blk.norm1.gain)
+            q, k, v = n @ w[p + "wq"].T, n @ w[p + "wk"].T, n @ w[p + "wv"].T
+            s = (q @ k.T / DK ** 0.5).masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+            x = x + torch.softmax(s, -1) @ v @ w[p + "wo"].T
+            n = rms(x, blk.norm2.gain)
+            gu = n @ blk.ffn.w_gu.tensor.double().cpu().T
+            g, u = gu[:, :F], gu[:, F:]
+            y = (u * (g / (1 + torch.exp(-g)))) @ blk.ffn.w_down.tensor.double().cpu().T
+            x = x + rms(y, blk.norm3.gain)
+        return (rms(x, eng.model.final_norm.gain) @ emb.T).numpy()
+
+    rng = np.random.default_rng(9)
+    seqs = [rng.integers(0, V, n).tolist() for n in (23, 1, 9)]
+    refs = [reference(t) for t in seqs]
+    for round_ in range(2):                                  # the second round runs in slots that were used before
+        slots = [eng.new_sequence() for _ in seqs]
+        cut = [10, 1, 4]
+        got = eng.step([(s, t[:c]) for s, t, c in zip(slots, seqs, cut)], want=[list(range(c)) for c in cut]).cpu().numpy()
+        row = 0
+        for r, c in zip(refs, cut):
+            assert rel_err(got[row:row + c], r[:c]) < TOL["float32"]
+            row += c
+        done = list(cut)
+        # a continuation of several tokens beside single tokens, then single tokens until each sequence ends
+        live = [b for b in range(3) if done[b] < len(seqs[b])]
+        step_new = {0: 5, 2: 1}
+        while live:
+            entries = [(slots[b], seqs[b][done[b]:done[b] + step_new.get(b, 1)]) for b in live]
+            got = eng.step(entries, want=[list(range(len(t))) for _, t in entries]).cpu().numpy()
+            row = 0
+            for b, (_, t) in zip(live, entries):
+                r = refs[b][done[b]:done[b] + len(t)]
+                assert rel_err(got[row:row + len(t)], r) < TOL["float32"], (round_, b, done[b])
+                row += len(t)
+                done[b] += len(t)
+            step_new = {}
+            live = [b for b in live if done[b] < len(seqs[b])]
+        for s in slots:
+            eng.end_sequence(s)
+    assert group.started == group.released and len(group.started) == 6
+    assert torch.isnan(group.k).all()                        # nothing of an ended sequence is left readable

@@ -4,9 +4,15 @@ in 32-bit and in bfloat16, all against the plain implementation."""
 import pytest
 
 from helpers import TINY, TOL, make_model_folder, plain_logits, random_tokens, rel_err
-from trace_tools import run_trace, trace_batches, trace_last_one_by_one, trace_whole
+from trace_tools import Trace, run_trace, split, trace_batches, trace_last_one_by_one, trace_whole
 
 pytestmark = pytest.mark.gpu
+
+# Two cuts in bfloat16 come from other kernels, which sum in another order; a difference far below a rounding
+# step becomes a whole step where it tips a rounding, so after a few operations two correct paths are as far
+# apart as rounding noise itself (tests/helpers.py: storage_noise): half the bound against the plain
+# implementation.  In float32 the cuts are equal bit by bit.
+CUT_TOL_BF16 = 3e-2
 
 LENGTHS = {"r0": 40, "r1": 33, "r2": 100, "r3": 57, "r4": 71, "r5": 34, "r6": 90}
 PROMPTS = {"r0": 7, "r1": 33, "r2": 12, "r3": 1, "r4": 64, "r5": 20, "r6": 65}
@@ -30,24 +36,27 @@ def _compare(got, requests, folder, tol, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_replay_all_cuts_match_plain(tmp_path, name, dtype):
     folder = make_model_folder(tmp_path, name, seed=11)
     requests = _requests(name)
-    whole = run_trace(folder, dtype, trace_whole(requests), tmp_path / "whole")
+    # One call of the replay program serves the three cuts, one after the other: each starts in the slots
+    # and pages that the one before it gave back.
+    tr = Trace()
+    tr.extend(trace_whole(requests), "whole:")
+    tr.extend(trace_last_one_by_one(requests), "tail:")
+    tr.extend(trace_batches(requests, PROMPTS, width=3), "batched:")
+    got = run_trace(folder, dtype, tr, tmp_path / "out")
+    whole, tail, batched = split(got, "whole:"), split(got, "tail:"), split(got, "batched:")
     assert len(whole) == sum(LENGTHS.values())
     _compare(whole, requests, folder, TOL[dtype], "whole")
-
-    tail = run_trace(folder, dtype, trace_last_one_by_one(requests), tmp_path / "tail")
     assert len(tail) == 33 * len(requests)
     _compare(tail, requests, folder, TOL[dtype], "last 32 one by one")
-
-    batched = run_trace(folder, dtype, trace_batches(requests, PROMPTS, width=3), tmp_path / "batched")
     assert len(batched) == sum(LENGTHS.values())
     _compare(batched, requests, folder, TOL[dtype], "unequal batches")
 
     # The cuts agree with one another far more closely than with the plain implementation.
-    cut_tol = 2e-5 if dtype == "float32" else TOL[dtype]
+    cut_tol = 2e-5 if dtype == "float32" else CUT_TOL_BF16
     for key, row in tail.items():
         assert rel_err(row, whole[key]) < cut_tol, ("tail vs whole", key)
     for key, row in batched.items():

@@ -8,13 +8,13 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_whole_sequence_matches_plain(tmp_path, name, dtype):
     from longbow_quarrel_b200.engine import Engine
     folder = make_model_folder(tmp_path, name, seed=3)
     eng = Engine.from_pretrained(folder, dtype=dtype, max_tokens=512)
     vocab = TINY[name]["vocab_size"]
-    for n, seed in ((1, 1), (7, 2), (100, 3)):
+    for n, seed in ((1, 1), (7, 2), (100, 3)) + (((300, 4),) if name in "DE" else ()):
         tokens = random_tokens(n, vocab, seed)
         slot = eng.new_sequence()
         got = eng.step([(slot, tokens)], want=[list(range(n))]).cpu().numpy()
@@ -31,6 +31,12 @@ UNUSUAL = {
     # a head size between the templates of the tensor-core attention kernels
     "head 96": dict(hidden_size=192, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2, head_dim=96,
                     intermediate_size=344, vocab_size=1001),
+    # the survey's micro-case: heads * head_dim != hidden and a head of 8, below every tensor-core tile
+    "head 8": dict(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=8,
+                   intermediate_size=88, vocab_size=200),
+    # an even head size that is no multiple of 8: rotation pairs that no 16-byte access covers
+    "head 26": dict(hidden_size=104, num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=1, head_dim=26,
+                    intermediate_size=120, vocab_size=300, tie_word_embeddings=True),
     # a head size above 128: the plain attention kernel
     "head 160": dict(hidden_size=320, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1, head_dim=160,
                      intermediate_size=520, vocab_size=777, tie_word_embeddings=True),

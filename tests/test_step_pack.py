@@ -6,7 +6,8 @@ import numpy as np
 import pytest
 
 import longbow_quarrel_b200  # noqa: F401
-from longbow_quarrel_b200.engine.step import QUERY_BLOCK, StepError, check_entries, pack_step
+from longbow_quarrel_b200.engine.step import StepError, check_entries, pack_step
+from longbow_quarrel_b200.kernels.attention import PREFILL_LISTS, step_needs
 
 
 def _part(flat, info, name):
@@ -57,14 +58,17 @@ def test_without_want_the_last_row_of_every_sequence_is_asked_for():
     assert len(_part(flat, info, "want_rows")) == 0
 
 
-@pytest.mark.parametrize("prefix,size", [("qb", QUERY_BLOCK), ("qc", 2 * QUERY_BLOCK)])
-def test_query_blocks_cover_every_row_once_longest_first(prefix, size):
+@pytest.mark.parametrize("name,size", [("query_blocks64", 64), ("query_blocks128", 128)])
+def test_query_blocks_cover_every_row_once_longest_first(name, size):
+    """The work lists of the prompt attention kernels are no business of the step function: the attention
+    part names them (`step_needs`) and the step function packs what it is given."""
     rng = np.random.default_rng(3)
     new = [1, 64, 65, 200, 128, 129, 17]
     past = [0, 0, 100, 3, 64, 0, 700]
     entries = [(b, rng.integers(0, 50, n).tolist()) for b, n in enumerate(new)]
-    flat, info = pack_step(entries, None, past)
-    seq, row, rows, pos = (_part(flat, info, f"{prefix}_{k}") for k in ("seq", "row", "rows", "pos"))
+    flat, info = pack_step(entries, None, past, {name: PREFILL_LISTS[name]})
+    assert info["extra"] == [name]
+    seq, row, rows, pos = _part(flat, info, name).reshape(4, -1)
     tok_seq, tok_pos = _part(flat, info, "tok_seq"), _part(flat, info, "tok_pos")
     covered = np.zeros(sum(new), dtype=int)
     for s, r, n, p in zip(seq, row, rows, pos):
@@ -76,3 +80,18 @@ def test_query_blocks_cover_every_row_once_longest_first(prefix, size):
     assert (covered == 1).all()
     assert list(pos) == sorted(pos, reverse=True)                          # the blocks with the most keys come first
     assert len(seq) == sum(-(-n // size) for n in new)
+
+
+def test_parts_name_the_step_arrays_they_need():
+    import torch
+    assert list(step_needs(torch.bfloat16, 128)) == ["query_blocks128"]
+    assert list(step_needs(torch.bfloat16, 96)) == ["query_blocks64"]
+    assert step_needs(torch.bfloat16, 40) == {} and step_needs(torch.float32, 128) == {}
+    # a step of one token per sequence has no prompt work: the list is empty, whatever the batch
+    flat, info = pack_step([(0, [1]), (1, [2])], None, [5, 9], step_needs(torch.bfloat16, 128))
+    assert len(_part(flat, info, "query_blocks128")) == 0
+    # any part may add integers of its own; a name of the step context itself is refused
+    flat, info = pack_step([(0, [1, 2]), (1, [2])], None, [5, 9], {"twice_past": lambda st: [2 * p for p in st.past]})
+    assert _part(flat, info, "twice_past").tolist() == [10, 18]
+    with pytest.raises(StepError, match="named 'tokens'"):
+        pack_step([(0, [1])], None, [0], {"tokens": lambda st: [0]})
