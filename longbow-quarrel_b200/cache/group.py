@@ -41,6 +41,16 @@ class CacheGroup:
     def commit(self, slot: int, length: int) -> None:
         """The step is queued; the sequence now holds `length` tokens.  What no later token needs may go back."""
 
+    def reserve_one_each(self, slots, old_lens) -> None:
+        """reserve(slot, old, old + 1) for many sequences at once (numpy arrays): the step of one token per
+        sequence, which a group may do faster than one call per sequence."""
+        for slot, old in zip(slots.tolist(), old_lens.tolist()):
+            self.reserve(slot, old, old + 1)
+
+    def commit_one_each(self, slots, new_lens) -> None:
+        for slot, length in zip(slots.tolist(), new_lens.tolist()):
+            self.commit(slot, length)
+
     def release(self, slot: int) -> None:
         """The sequence in `slot` has ended: everything it holds goes back."""
 

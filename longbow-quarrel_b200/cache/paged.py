@@ -88,6 +88,21 @@ class PagedKVGroup(CacheGroup):
     def commit(self, slot: int, length: int) -> None:
         self.trim(slot, length)
 
+    def reserve_one_each(self, slots, old_lens) -> None:
+        # One more token needs a page only where it starts one.
+        starts = (old_lens % self.page_size) == 0
+        if starts.any():
+            for slot, old in zip(slots[starts].tolist(), old_lens[starts].tolist()):
+                self.reserve(slot, old, old + 1)
+
+    def commit_one_each(self, slots, new_lens) -> None:
+        if self.window is None:
+            return
+        # A page falls out of the window only when the window's lower end reaches the next page.
+        ends = (np.maximum(new_lens - self.window + 1, 0) % self.page_size) == 0
+        for slot, length in zip(slots[ends].tolist(), new_lens[ends].tolist()):
+            self.trim(slot, length)
+
     def release(self, slot: int) -> None:
         row = self.table[slot]
         for p in np.nonzero(row != NO_PAGE)[0]:

@@ -24,6 +24,12 @@ class StateGroup(CacheGroup):
 
     reset = start
 
+    def reserve_one_each(self, slots, old_lens) -> None:
+        pass
+
+    def commit_one_each(self, slots, new_lens) -> None:
+        pass
+
     def nbytes(self) -> int:
         return self.data.numel() * self.data.element_size()
 

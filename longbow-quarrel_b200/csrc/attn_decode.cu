@@ -382,6 +382,14 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
 // block that finishes a (token, kv head) last merges the slices itself, without them a second
 // kernel does.  head_dim must be a multiple of 8 and at most 128; page_size a multiple of 16;
 // at most 32 slices.
+namespace {
+// The sizes that the kernel takes (every entry point refuses the others before it touches anything).
+bool sizes_ok(int H, int Hkv, int hd, int page_size, int q_stride, int n_splits) {
+    return H > 0 && Hkv > 0 && hd > 0 && hd % 8 == 0 && hd <= 128 && H % Hkv == 0 && page_size > 0 &&
+           page_size % TILE == 0 && q_stride % 8 == 0 && n_splits >= 1 && n_splits <= MAX_SPLITS;
+}
+}  // namespace
+
 // next_w, next_bytes (or null): weights that are read next on this stream; their first next_bytes
 // are asked into L2 as the blocks finish.
 // early_loads: non-zero when, of all keys and values that a token reads, only those at its own
@@ -393,8 +401,7 @@ LQ_EXPORT int lq_attn_decode_next(const void* q, int q_stride, const void* k_pag
                                   int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
                                   const void* next_w, long next_bytes, int early_loads, cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
-    if (hd % 8 || hd > 128 || hd <= 0 || H % Hkv || page_size % TILE || n_splits < 1 || q_stride % 8) return LQ_BAD_SIZE;
-    if (n_splits > MAX_SPLITS) return LQ_BAD_SIZE;
+    if (!sizes_ok(H, Hkv, hd, page_size, q_stride, n_splits)) return LQ_BAD_SIZE;
     if (n_splits > 1 && (!part_o || !part_ml)) return LQ_BAD_SIZE;
 #define LQ_GO(HD) return launch<HD>(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, \
                                     part_o, part_ml, counters, out, T, H, Hkv, hd, page_size, scale, window, n_splits, \
@@ -460,7 +467,8 @@ LQ_EXPORT int lq_attn_decode_static(const void* q, int q_stride, const void* k_p
                                     const int* slots, void* out, int T, int H, int Hkv, int head_dim, int page_size,
                                     float scale, int window, int n_splits, cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
-    if (H <= 0 || Hkv <= 0 || head_dim <= 0 || n_splits < 1) return LQ_BAD_SIZE;
+    // Everything is checked before anything is queued: a refused call leaves the shared array alone.
+    if (!sizes_ok(H, Hkv, head_dim, page_size, q_stride, n_splits)) return LQ_BAD_SIZE;
     float* part_o = nullptr;
     float* part_ml = nullptr;
     int* counters = nullptr;

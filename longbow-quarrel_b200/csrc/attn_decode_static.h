@@ -20,10 +20,16 @@
  * lq_attn_decode_static_floats() gives the capacity.
  * With one slice (n_splits == 1) no scratch is used at all.
  *
+ * Sizes the kernel does not take (a head size that is no multiple of 8 or above 128, heads that are no
+ * multiple of the kv heads, a page size that is no multiple of 16, more than 32 slices, a q_stride that
+ * is no multiple of 8) are refused with -2, likewise before anything is queued.
+ *
  * Set-up.  The first call on a device asks the runtime for the array's device address
  * (cudaGetSymbolAddress, with that device current) and keeps it; the name of the array in
  * host code is only a handle, not an address the GPU can use.  Make that first call on each
  * device before any stream capture begins, like any other call that may initialise a module.
+ * The array is the current device's, so `stream` must be a stream of the device that is current
+ * when the call is made (the call does not check this).
  *
  * Sharing.  All calls on a device use the same array, and it keeps what the last call left in
  * it.  The partial outputs need no clearing: a call writes every element that it later reads

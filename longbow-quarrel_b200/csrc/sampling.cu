@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(SB)
 sample_kernel(const float* __restrict__ logits, float* __restrict__ scratch, int* __restrict__ out, int V,
               float temperature, int top_k, float top_p, float penalty, const int* __restrict__ history,
               int hist_stride, const int* __restrict__ hist_len, unsigned long long seed,
-              const int* __restrict__ rng_sequence, const int* __restrict__ rng_step) {
+              const int* __restrict__ rng_sequence, const int* __restrict__ rng_step, int step_offset) {
     __shared__ Shared sh;
     const int row = blockIdx.x, tid = threadIdx.x;
     const float* z_in = logits + (size_t)row * V;
@@ -267,7 +267,7 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ scratch, int
     if (tid == 0) {
         double run = 0.0;
         for (int t = 0; t < SB; ++t) { double c = sh.dscan[t]; sh.dscan[t] = run; run += c; }
-        double u = philox_uniform(seed, (uint32_t)rng_sequence[row], (uint32_t)rng_step[row]);
+        double u = philox_uniform(seed, (uint32_t)rng_sequence[row], (uint32_t)(rng_step[row] + step_offset));
         sh.bd = u * run;
         sh.bi = -1;
         // The chunk whose range holds r: the last one whose start is <= r and that has weight.
@@ -301,15 +301,17 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ scratch, int
 
 // logits [rows, V] float32; scratch [rows, V] float32 (overwritten); out [rows] int32.
 // history [rows, hist_stride] with hist_len[rows] valid ids each (null: no penalty).
-// rng_sequence / rng_step [rows]: the counter of each row's draw (unused for temperature 0).
+// rng_sequence / rng_step [rows]: the counter of each row's draw (unused for temperature 0); step_offset is added
+// to every row's step, so a caller whose rows all advance together keeps one array and passes the step here.
 LQ_EXPORT int lq_sample(const float* logits, float* scratch, int* out, int rows, int V, float temperature, int top_k,
                         float top_p, float penalty, const int* history, int hist_stride, const int* hist_len,
-                        unsigned long long seed, const int* rng_sequence, const int* rng_step, cudaStream_t stream) {
+                        unsigned long long seed, const int* rng_sequence, const int* rng_step, int step_offset,
+                        cudaStream_t stream) {
     if (rows <= 0) return LQ_OK;
     if (V <= 0 || temperature < 0.f) return LQ_BAD_SIZE;
     if (temperature > 0.f && (!rng_sequence || !rng_step)) return LQ_BAD_SIZE;
     if (hist_stride > SB) return LQ_BAD_SIZE;
     sample_kernel<<<rows, SB, 0, stream>>>(logits, scratch, out, V, temperature, top_k, top_p, penalty, history,
-                                           hist_stride, hist_len, seed, rng_sequence, rng_step);
+                                           hist_stride, hist_len, seed, rng_sequence, rng_step, step_offset);
     return lq_launch_status();
 }

@@ -42,6 +42,8 @@ class EngineBackend:
         self.engine, self.params = engine, params
         self.seed = params.resolved_seed()
         self.run_ahead = run_ahead and not params.uses_history
+        self.needs_history = params.uses_history        # the generation loop builds histories only for a penalty
+        self._draw_ids: dict = {}                        # requests of a step -> their ids on the device (and zeros)
         self._scratch = None
         self._ahead: _Sampled | None = None
         self._pinned: list[torch.Tensor] = []      # a small ring of pinned buffers for the sampled ids
@@ -57,16 +59,28 @@ class EngineBackend:
     def _sample(self, logits, requests, steps, histories):
         dev = logits.device
         seq_ids = step_ids = hist = hist_len = None
+        offset = 0
         if not self.params.greedy:
-            ids = torch.tensor([requests, steps], dtype=torch.int32).to(dev)
-            seq_ids, step_ids = ids[0], ids[1]
+            if len(set(steps)) == 1:
+                # The rows advance together (every step of a batch): their ids go to the device once, the step
+                # is passed by value.
+                key = tuple(requests)
+                if key not in self._draw_ids:
+                    if len(self._draw_ids) > 64:
+                        self._draw_ids.clear()
+                    self._draw_ids[key] = torch.tensor([requests, [0] * len(requests)], dtype=torch.int32).to(dev)
+                seq_ids, step_ids = self._draw_ids[key]
+                offset = int(steps[0])
+            else:
+                ids = torch.tensor([requests, steps], dtype=torch.int32).to(dev)
+                seq_ids, step_ids = ids[0], ids[1]
         if self.params.uses_history:
             h, n = history_window(histories)
             hist, hist_len = torch.from_numpy(h).to(dev), torch.from_numpy(n).to(dev)
         if self._scratch is None or self._scratch.shape[0] < logits.shape[0]:
             self._scratch = torch.empty_like(logits)
         tokens = sample(logits, self.params, self.seed, seq_ids, step_ids, hist, hist_len,
-                        scratch=self._scratch[:logits.shape[0]])
+                        scratch=self._scratch[:logits.shape[0]], step_offset=offset)
         n = tokens.numel()
         if len(self._pinned) < 4:
             self._pinned.append(torch.empty(max(n, self.engine.cache.max_slots), dtype=torch.int32).pin_memory())

@@ -67,12 +67,28 @@ class Engine:
 
     @classmethod
     def from_pretrained(cls, folder, dtype="bfloat16", max_tokens: int | None = None, max_batch: int | None = None,
-                        max_context: int | None = None, device="cuda:0", use_graphs: bool = True) -> "Engine":
-        """A model folder (config.json + model.safetensors); the class is chosen by config.json."""
+                        max_context: int | None = None, device="cuda:0", use_graphs: bool = True,
+                        convert_weights: bool = False, unexpected: str = "error") -> "Engine":
+        """A model folder (config.json + model.safetensors); the class is chosen by config.json.
+
+        Weights are kept as the file stores them.  A tensor stored in 32-bit therefore stays so under
+        dtype="bfloat16" too, and its products run on the CUDA cores instead of the tensor cores: right,
+        but several times slower, so a warning says it.  convert_weights=True rounds the weights to the
+        model's precision as they are loaded instead (what the reference does,
+        internal/engine/engine.go:787-802).  unexpected: see weights.load_weights."""
         folder = Path(folder)
         arch, config = load_config(folder)
-        return cls._build(arch, config, lambda table, dev: load_weights(folder, table, dev), dtype, max_tokens,
-                          max_batch, max_context, device, use_graphs)
+        run_dtype = _dtype(dtype)
+
+        def tensors(table, dev):
+            out = load_weights(folder, table, dev, convert_to=run_dtype if convert_weights else None, unexpected=unexpected)
+            wide = [n for n, t in out.items() if t.dtype == torch.float32 and t.dim() >= 2]
+            if wide and run_dtype == torch.bfloat16:
+                import warnings
+                warnings.warn(f"{folder}: {len(wide)} weight matrices are stored in 32-bit; with dtype='bfloat16' their "
+                              f"products run on the CUDA cores (pass convert_weights=True to round them to bfloat16 at load)")
+            return out
+        return cls._build(arch, config, tensors, dtype, max_tokens, max_batch, max_context, device, use_graphs)
 
     @classmethod
     def from_config(cls, config, seed: int = 0, dtype="bfloat16", max_tokens: int | None = None,

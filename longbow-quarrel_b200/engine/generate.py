@@ -15,6 +15,8 @@ from typing import Callable, Protocol, Sequence
 
 
 class Backend(Protocol):
+    # A backend whose sampling never looks at the tokens so far may set `needs_history = False`; `run` is then
+    # given None for `histories` (building them costs time in every step of a long generation).
     def start(self) -> int: ...
     def finish(self, handle: int) -> None: ...
     def run(self, entries: list[tuple[int, list[int]]], requests: list[int], steps: list[int],
@@ -49,6 +51,7 @@ def generate(backend: Backend, prompts: Sequence[Sequence[int]], max_new_tokens:
     if batch_size < 1:
         raise ValueError("batch_size must be at least 1")
     stops = set(int(s) for s in stop_ids)
+    with_history = getattr(backend, "needs_history", True)
     outputs: list[list[int]] = [[] for _ in prompts]
     stats = GenerationStats(finish_reasons=["" for _ in prompts])
     if max_new_tokens <= 0:
@@ -63,7 +66,7 @@ def generate(backend: Backend, prompts: Sequence[Sequence[int]], max_new_tokens:
         try:
             t0 = time.perf_counter()
             sampled = backend.run([(handles[i], list(prompts[i])) for i in live], live, [0] * len(live),
-                                  [list(prompts[i]) for i in live])
+                                  [list(prompts[i]) for i in live] if with_history else None)
             stats.prefill_seconds += time.perf_counter() - t0
             stats.prompt_tokens += sum(len(prompts[i]) for i in live)
             step = 0
@@ -96,7 +99,7 @@ def generate(backend: Backend, prompts: Sequence[Sequence[int]], max_new_tokens:
                 step += 1
                 t0 = time.perf_counter()
                 sampled = backend.run([(handles[i], [outputs[i][-1]]) for i in live], live, [step] * len(live),
-                                      [list(prompts[i]) + outputs[i] for i in live])
+                                      [list(prompts[i]) + outputs[i] for i in live] if with_history else None)
                 stats.decode_seconds += time.perf_counter() - t0
                 stats.decode_steps += 1
         finally:

@@ -114,11 +114,13 @@ class Stepper:
         """entries: [(slot, tokens)], want: [[places]] or None (= each sequence's last token).
         Returns logits [n_wanted, vocab] float32 in the order of entries and of want."""
         check_entries(entries, want, self.model.spec.vocab_size)
+        if all(len(t) == 1 for _, t in entries) and self._replays(len(entries)):
+            logits = self._replay_step([s for s, _ in entries], [int(t[0]) for _, t in entries], None)
+            return self._wanted(logits, want, len(entries))
         past = [self.cache.length(slot) for slot, _ in entries]
         for slot, tokens in entries:
             self.cache.reserve(slot, len(tokens))
         self.cache.upload()
-        B = len(entries)
         decode = all(len(t) == 1 for _, t in entries)
         if decode and self.use_graphs and self.model.probe is None:
             logits = self._decode_step(entries, want, past)
@@ -136,15 +138,17 @@ class Stepper:
         `source` (int32, e.g. what the sampler wrote for the step before): sequence b gets
         source[rows[b]] (source[b] without rows).  The host never sees these tokens before the
         step is launched, so the step can be queued while the one before it still runs."""
+        if rows is not None and rows != list(range(len(rows))):
+            source = source[torch.tensor(rows, dtype=torch.long, device=self.device)]
+        elif source.numel() != len(slots):
+            source = source[:len(slots)]
+        if self._replays(len(slots)):
+            return self._replay_step(slots, None, source)
         entries = [(s, [0]) for s in slots]
         past = [self.cache.length(s) for s in slots]
         for s in slots:
             self.cache.reserve(s, 1)
         self.cache.upload()
-        if rows is not None and rows != list(range(len(rows))):
-            source = source[torch.tensor(rows, dtype=torch.long, device=self.device)]
-        elif source.numel() != len(slots):
-            source = source[:len(slots)]
         if self.use_graphs and self.model.probe is None:
             logits = self._decode_step(entries, None, past, fed=source)
         else:
@@ -156,6 +160,32 @@ class Stepper:
         for s in slots:
             self.cache.commit(s, 1)
         return logits
+
+    # ------------------------------------------------------------------ steps of one token per sequence
+    def _replays(self, B: int) -> bool:
+        """Whether a step of one token for each of B sequences is a replay of a captured step."""
+        return self.use_graphs and self.model.probe is None and B in self._graphs
+
+    def _replay_step(self, slots: list[int], tokens: list[int] | None, fed: torch.Tensor | None) -> torch.Tensor:
+        """The step that generation repeats most, with as little host work as it needs: the cache's
+        bookkeeping for all sequences at once, the step's integers written into the captured step's layout
+        (what never changes between steps is there already), one copy, one replay."""
+        graph = self._graphs[len(slots)]
+        past = self.cache.reserve_one_each(slots)
+        self.cache.upload()
+        logits = graph.replay(graph.fill(slots, tokens, past, self.needs), fed)
+        self.cache.commit_one_each(slots)
+        return logits
+
+    def _wanted(self, logits, want, B: int):
+        if want is None:
+            return logits
+        rows = [b for b, ws in enumerate(want) for _ in ws]
+        if rows == list(range(B)):
+            return logits
+        if not rows:
+            return None
+        return logits[torch.tensor(rows, device=self.device)]
 
     def _decode_step(self, entries, want, past, fed: torch.Tensor | None = None):
         B = len(entries)
@@ -173,14 +203,7 @@ class Stepper:
             if graph is None:
                 graph = self._graphs[B] = _DecodeGraph(self.model, self.cache, self.device, flat, info)
             logits = graph.replay(flat, fed)
-        if want is None:
-            return logits
-        rows = [b for b, ws in enumerate(want) for _ in ws]
-        if rows == list(range(B)):
-            return logits
-        if not rows:
-            return None
-        return logits[torch.tensor(rows, device=self.device)]
+        return self._wanted(logits, want, B)
 
 
 class _DecodeGraph:
@@ -195,6 +218,7 @@ class _DecodeGraph:
         self.info = dict(info)
         # Kernels that size their work by the longest sequence are captured for the longest possible one.
         self.info["max_kv"] = cache.max_context
+        self.template = np.array(flat, dtype=np.int32)          # a step's integers in this layout, filled anew each step
         self.host.numpy()[:] = flat
         self.flat_dev.copy_(self.host, non_blocking=True)
         ctx = make_context(self.flat_dev, self.info, list(range(info["B"])))
@@ -209,6 +233,29 @@ class _DecodeGraph:
         ops.add_launches(-self.kernels, self.by_name, -1)      # recorded, not run
         torch.cuda.current_stream(device).wait_stream(stream)
         self.copied.record()
+
+    def fill(self, slots: list[int], tokens: list[int] | None, past: np.ndarray, needs: dict) -> np.ndarray:
+        """The integers of a step of one token per sequence, in this graph's layout.  Which row belongs to
+        which sequence, where the rows start and which rows are wanted is the same in every such step and stays
+        as the capture left it; tokens, slots, positions and lengths are written anew, and so are the arrays
+        that parts asked for, where they are not empty."""
+        flat, layout = self.template, self.info["layout"]
+        if tokens is not None:
+            o, n = layout["tokens"]
+            flat[o:o + n] = tokens
+        o, n = layout["slots"]
+        flat[o:o + n] = slots
+        o, n = layout["tok_pos"]
+        flat[o:o + n] = past
+        o, n = layout["kv_len"]
+        flat[o:o + n] = past + 1
+        for name in self.info["extra"]:
+            o, n = layout[name]
+            if n:
+                B = len(slots)
+                flat[o:o + n] = np.asarray(needs[name](StepShape(B=B, T=B, past=tuple(past.tolist()), new=(1,) * B,
+                                                                 cu=tuple(range(B + 1))))).reshape(-1)
+        return flat
 
     def replay(self, flat: np.ndarray, fed: torch.Tensor | None = None) -> torch.Tensor:
         self.copied.synchronize()

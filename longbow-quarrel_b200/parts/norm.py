@@ -20,7 +20,7 @@ class RMSNorm(Norm):
         self.gain: torch.Tensor | None = None
 
     def weights(self):
-        return {self.name: WeightSpec((self.size,), init="gain")}
+        return {self.name: WeightSpec((self.size,), init="gain", full_precision=True)}
 
     def load(self, tensors):
         self.gain = tensors[self.name].to(torch.float32).contiguous()

@@ -12,10 +12,11 @@ from .params import HISTORY_WINDOW, SamplingParams
 
 def sample(logits: torch.Tensor, params: SamplingParams, seed: int, sequence_ids=None, steps=None,
            history: torch.Tensor | None = None, history_len: torch.Tensor | None = None,
-           scratch: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+           scratch: torch.Tensor | None = None, out: torch.Tensor | None = None, step_offset: int = 0) -> torch.Tensor:
     """One token for each row of logits [rows, vocab] (float32).
 
-    sequence_ids, steps  int32 [rows]: the counter of each row's random draw
+    sequence_ids, steps  int32 [rows]: the counter of each row's random draw; step_offset is added to every
+                         row's step (rows that advance together keep one array and pass the step here)
     history, history_len int32 [rows, 64] and [rows]: the last tokens of each sequence
     """
     rows, V = logits.shape
@@ -29,12 +30,12 @@ def sample(logits: torch.Tensor, params: SamplingParams, seed: int, sequence_ids
         raise ops.KernelError("sample: a random draw needs sequence ids and steps")
     use_hist = params.uses_history and history is not None
     fn = ops._fn("sampling", "lq_sample", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_float, c_float,
-                                           c_void_p, c_int, c_void_p, c_ulonglong, c_void_p, c_void_p, c_void_p])
+                                           c_void_p, c_int, c_void_p, c_ulonglong, c_void_p, c_void_p, c_int, c_void_p])
     ops._check(fn(ops._p(logits), ops._p(scratch), ops._p(out), rows, V, float(params.temperature), int(params.top_k),
                   float(params.top_p), float(params.repetition_penalty),
                   ops._p(history if use_hist else None), history.stride(0) if use_hist else 0,
                   ops._p(history_len if use_hist else None), c_ulonglong(seed & 0xFFFF_FFFF_FFFF_FFFF),
-                  ops._p(sequence_ids), ops._p(steps), ops._stream()), "sample")
+                  ops._p(sequence_ids), ops._p(steps), int(step_offset), ops._stream()), "sample")
     return out
 
 

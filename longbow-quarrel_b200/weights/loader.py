@@ -6,11 +6,19 @@ when inference starts (engine.go:1316-1324).  Here the model says which names an
 shapes it needs, and one error lists everything that is wrong with the file.
 
 Kept as stored where possible: bfloat16 stays bfloat16, a tensor stored in 32-bit
-stays in 32-bit, float16 becomes bfloat16, integer tables become int32.
+stays in 32-bit, float16 becomes bfloat16, integer tables become int32.  The reference
+converts every tensor to the precision of its path as it loads
+(internal/engine/engine.go:787-802); `convert_to` asks for the same: floating-point
+tensors are rounded to that dtype at load, except those a part wants in full precision
+(norm gains, which the reference promotes to 32-bit, engine.go:788-792).  Tensors that
+the model does not name are an error by default, as missing ones are; `unexpected="warn"`
+lists them in a warning instead (the reference skips what it does not know,
+engine.go:867-870).
 """
 from __future__ import annotations
 
 import json
+import warnings
 from pathlib import Path
 
 import torch
@@ -51,9 +59,13 @@ def _open_files(folder: Path) -> list[SafetensorsFile]:
     raise SafetensorsError(f"{folder}: neither model.safetensors nor model.safetensors.index.json")
 
 
-def _keep_dtype(t: torch.Tensor, spec: WeightSpec) -> torch.Tensor:
+def _keep_dtype(t: torch.Tensor, spec: WeightSpec, convert_to: torch.dtype | None = None) -> torch.Tensor:
     if spec.integer:
         return t.to(torch.int32)
+    if convert_to is not None and t.dtype.is_floating_point and not spec.full_precision:
+        if convert_to == torch.float32 and t.dtype == torch.bfloat16:
+            return t                  # every bfloat16 value is a float32 value: the 32-bit kernels read it as it is
+        return t.to(convert_to)
     if t.dtype in (torch.float32, torch.bfloat16):
         return t
     if t.dtype in (torch.float16,):
@@ -63,9 +75,14 @@ def _keep_dtype(t: torch.Tensor, spec: WeightSpec) -> torch.Tensor:
     raise SafetensorsError(f"dtype {t.dtype} is not a weight dtype")
 
 
-def load_weights(folder, table: dict[str, WeightSpec], device) -> dict[str, torch.Tensor]:
+def load_weights(folder, table: dict[str, WeightSpec], device, convert_to: torch.dtype | None = None,
+                 unexpected: str = "error") -> dict[str, torch.Tensor]:
     """Every tensor of `table` on `device`.  A name with a `fallback` that is absent
-    from the file is left out of the result (the part then reads the fallback)."""
+    from the file is left out of the result (the part then reads the fallback).
+    convert_to: round floating-point tensors to this dtype at load (None: keep them as stored).
+    unexpected: "error" (tensors the model does not name are a fault like the others), "warn" or "ignore"."""
+    if unexpected not in ("error", "warn", "ignore"):
+        raise ValueError(f"unexpected must be 'error', 'warn' or 'ignore', found {unexpected!r}")
     folder = Path(folder)
     files = _open_files(folder)
     where: dict[str, SafetensorsFile] = {}
@@ -86,13 +103,15 @@ def load_weights(folder, table: dict[str, WeightSpec], device) -> dict[str, torc
         elif spec.integer == where[name].dtype(name).is_floating_point:
             other.append(f"tensor {name} has dtype {where[name].dtype(name)}, expected "
                          f"{'an integer' if spec.integer else 'a floating-point'} type")
-    unexpected = [n for n in where if n not in table]
-    if missing or wrong or unexpected or other:
-        raise WeightsError(folder, missing, unexpected, wrong, other)
+    extra = [n for n in where if n not in table]
+    if missing or wrong or other or (extra and unexpected == "error"):
+        raise WeightsError(folder, missing, extra, wrong, other)
+    if extra and unexpected == "warn":
+        warnings.warn(f"{folder}: {len(extra)} tensors that the model does not name are skipped: " + ", ".join(sorted(extra)))
     out = {}
     for name, spec in table.items():
         if name in where:
-            out[name] = _keep_dtype(where[name].tensor(name), spec).to(device, non_blocking=False).contiguous()
+            out[name] = _keep_dtype(where[name].tensor(name), spec, convert_to).to(device, non_blocking=False).contiguous()
     for f in files:
         f.close()
     return out

@@ -14,8 +14,11 @@ class WeightSpec:
     fallback  full name of another tensor that stands in when this one is absent
               (a tied output head reads the embedding table).
     integer   the tensor is an integer table (kept as int32).
+    full_precision  the part computes with this tensor in 32-bit whatever the model's precision (norm
+              gains): a loader that converts tensors to the model's precision leaves it as stored.
     """
     shape: tuple[int, ...]
     init: str = "normal"
     fallback: str | None = None
     integer: bool = False
+    full_precision: bool = False

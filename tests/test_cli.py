@@ -57,3 +57,37 @@ def test_options_reach_the_sampler_with_the_references_meanings():
         SamplingParams(temperature=-1.0)
     with pytest.raises(ValueError):
         SamplingParams(repetition_penalty=0.0)
+
+
+def test_prompts_from_a_file_and_synthetic_prompts(tmp_path):
+    p = cli.parser()
+    lines = tmp_path / "prompts.txt"
+    lines.write_text("# two prompts\n1 15043 3186\n\n7, 8,9\n")
+    a = p.parse_args(["-model", "D", "-prompt-file", str(lines)])
+    assert cli._prompts(a, 32000, None) == [[1, 15043, 3186], [7, 8, 9]]
+    assert cli._prompts(a, 32000, 2) == [[2, 1, 15043, 3186], [2, 7, 8, 9]]
+    as_json = tmp_path / "prompts.json"
+    as_json.write_text("[[4, 5], [6]]")
+    assert cli.read_prompt_file(as_json) == [[4, 5], [6]]
+    as_json.write_text("[4, 5, 6]")
+    assert cli.read_prompt_file(as_json) == [[4, 5, 6]]
+    lines.write_text("1 2\nthree\n")
+    with pytest.raises(SystemExit, match="prompts.txt:2"):
+        cli.read_prompt_file(lines)
+    # synthetic prompts: -batch of them, -prompt-len ids each, drawn from -seed
+    a = p.parse_args(["-model", "D", "-prompt-len", "12", "-batch", "3", "-seed", "5", "-no-bos"])
+    got = cli._prompts(a, 100, 2)
+    assert [len(q) for q in got] == [12, 12, 12] and all(0 <= t < 100 for q in got for t in q)
+    assert got == cli._prompts(a, 100, 2) and got[0] != got[1]
+    assert len(cli._prompts(p.parse_args(["-model", "D", "-prompt-len", "4"]), 100, None)) == 1
+
+
+def test_the_bench_command_has_the_references_flags(monkeypatch, capsys):
+    a = cli.bench_parser().parse_args(["-model", "DIR"])
+    assert (a.prompt, a.tokens, a.output, a.timeout) == ("Hello world", 20, "text", 60)     # cmd/benchmark_json/main.go:28-35
+    a = cli.bench_parser().parse_args(["--model", "DIR", "--tokens", "7", "--output", "json", "--timeout", "5",
+                                       "-prompt-len", "128", "-batch", "8"])
+    assert (a.tokens, a.output, a.timeout, a.prompt_len, a.batch) == (7, "json", 5, 128, 8)
+    monkeypatch.delenv("QUARREL_MODEL", raising=False)
+    assert cli.main(["bench"]) == 1
+    assert "--model is required" in capsys.readouterr().err

@@ -234,3 +234,29 @@ def test_command_line_generates_the_plain_implementations_tokens(tmp_path):
                            "-topp", "0.95", "-penalty", "1.1", "-seed", "7", "-stream"], capture_output=True, text=True,
                           timeout=300, env={**os.environ, "LQ_PYTHON": sys.executable})
     assert text.returncode == 0 and "3 tokens in" in text.stdout and "Longbow-Quarrel" in text.stdout
+
+
+def test_bench_command_with_a_prompt_file(tmp_path):
+    """`quarrel bench`: greedy, the reference's JSON fields, prompts from a file; and the timeout."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    folder = make_model_folder(tmp_path, "A", seed=26)
+    cfg, weights = plain_llama.load_folder(folder)
+    prompts = tmp_path / "prompts.txt"
+    prompts.write_text("3 1 4 1 5\n9,2,6\n")
+    exe = Path(__file__).resolve().parent.parent / "bin" / "quarrel"
+    env = {**os.environ, "LQ_PYTHON": sys.executable}
+    proc = subprocess.run([str(exe), "bench", "-model", str(folder), "-prompt-file", str(prompts), "-tokens", "5",
+                           "-dtype", "float32", "-output", "json"], capture_output=True, text=True, timeout=300, env=env)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    out = json.loads(proc.stdout.strip().splitlines()[-1])
+    assert out["tokens_generated"] == 10 and out["throughput_tokens_per_sec"] > 0
+    assert out["prefill_duration_seconds"] + out["generation_duration_seconds"] == pytest.approx(out["total_duration_seconds"])
+    for prompt, new in zip(([3, 1, 4, 1, 5], [9, 2, 6]), out["output"]):
+        assert new == plain_llama.greedy(cfg, weights, prompt, 5)
+    late = subprocess.run([str(exe), "bench", "-model", str(folder), "-prompt-len", "8", "-batch", "2", "-tokens", "50",
+                           "-timeout", "0"], capture_output=True, text=True, timeout=300, env=env)
+    assert late.returncode == 1 and "timed out after 0 seconds" in late.stderr

@@ -77,11 +77,28 @@ def test_weights_stored_in_32_bit_stay_32_bit(tmp_path):
     slot = eng.new_sequence()
     got = eng.step([(slot, tokens)], want=[list(range(50))]).cpu().numpy()
     assert rel_err(got, plain_logits(folder, tokens)) < TOL["float32"]
-    # the bfloat16 engine takes the same folder: 32-bit weights go through the plain product
-    eng16 = Engine.from_pretrained(folder, dtype="bfloat16", max_tokens=256)
+    # the bfloat16 engine takes the same folder: 32-bit weights go through the plain product, and it says so
+    from longbow_quarrel_b200.kernels import ops
+    with pytest.warns(UserWarning, match="stored in 32-bit.*convert_weights"):
+        eng16 = Engine.from_pretrained(folder, dtype="bfloat16", max_tokens=256)
+    assert eng16.model.blocks[0].mixer.w_qkv.tensor.dtype == torch.float32
     slot = eng16.new_sequence()
+    before = ops.launches_by_name()
     got = eng16.step([(slot, tokens)], want=[list(range(50))]).cpu().numpy()
     assert rel_err(got, plain_logits(folder, tokens)) < TOL["bfloat16"]
+    assert "gemm_tc" not in ops.launches_since(before) and ops.launches_since(before)["linear"] > 0
+    # asked to, the loader rounds the matrices to bfloat16 (norm gains stay in 32-bit): the tensor-core kernels run
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        conv = Engine.from_pretrained(folder, dtype="bfloat16", max_tokens=256, convert_weights=True)
+    assert conv.model.blocks[0].mixer.w_qkv.tensor.dtype == torch.bfloat16
+    assert conv.model.blocks[0].norm1.gain.dtype == torch.float32
+    slot = conv.new_sequence()
+    before = ops.launches_by_name()
+    got = conv.step([(slot, tokens)], want=[list(range(50))]).cpu().numpy()
+    assert rel_err(got, plain_logits(folder, tokens)) < TOL["bfloat16"]
+    assert ops.launches_since(before).get("gemm_tc", 0) > 0 and "linear" not in ops.launches_since(before)
 
 
 def test_step_errors_are_raised_before_anything_runs(tmp_path):

@@ -87,6 +87,54 @@ def test_a_tied_model_refuses_a_head_tensor(tmp_path):
         load_weights(folder, _table("B"), "cpu")
 
 
+def test_unexpected_tensors_may_be_a_warning_instead(tmp_path):
+    """Alone they need not stop a load (`unexpected="warn"` names them in a warning, "ignore" says nothing);
+    beside another fault they are listed in the one error all the same."""
+    folder = make_model_folder(tmp_path, "B", seed=2)
+    weights = plain_llama.read_safetensors(folder / "model.safetensors")
+    weights["lm_head.weight"] = torch.zeros(384, 96, dtype=torch.bfloat16)
+    weights["rotary.inv_freq"] = torch.zeros(16)
+    write_safetensors(folder / "model.safetensors", weights)
+    with pytest.warns(UserWarning, match="2 tensors.*lm_head.weight, rotary.inv_freq"):
+        out = load_weights(folder, _table("B"), "cpu", unexpected="warn")
+    assert sorted(out) == sorted(_table("B"))
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        load_weights(folder, _table("B"), "cpu", unexpected="ignore")
+    del weights["model.norm.weight"]
+    write_safetensors(folder / "model.safetensors", weights)
+    with pytest.raises(WeightsError) as exc:
+        load_weights(folder, _table("B"), "cpu", unexpected="warn")
+    assert exc.value.missing == ["model.norm.weight"] and len(exc.value.unexpected) == 2
+    with pytest.raises(ValueError, match="'error', 'warn' or 'ignore'"):
+        load_weights(folder, _table("B"), "cpu", unexpected="no")
+
+
+def test_converting_to_the_models_precision_at_load(tmp_path):
+    """Kept as stored by default; `convert_to` rounds matrices to the model's precision and leaves what a
+    part computes with in 32-bit (norm gains) as it is stored."""
+    folder = make_model_folder(tmp_path, "A", seed=3, dtype=torch.float32)
+    table = _table("A")
+    stored = load_weights(folder, table, "cpu")
+    assert all(t.dtype == torch.float32 for t in stored.values())
+    half = load_weights(folder, table, "cpu", convert_to=torch.bfloat16)
+    gains = [n for n, spec in table.items() if spec.full_precision]
+    assert len(gains) == 2 * 2 + 1
+    for name, t in half.items():
+        if name in gains:
+            assert t.dtype == torch.float32 and torch.equal(t, stored[name])
+        else:
+            assert t.dtype == torch.bfloat16 and torch.equal(t, stored[name].to(torch.bfloat16))
+    # to 32-bit: bfloat16 tensors stay (each of their values is a float32 value), float16 ones are widened
+    mixed = {"a": torch.randn(4, 4).to(torch.bfloat16), "b": torch.randn(4, 4).to(torch.float16)}
+    write_safetensors(tmp_path / "model.safetensors", mixed)
+    from longbow_quarrel_b200.weights import WeightSpec
+    out = load_weights(tmp_path, {"a": WeightSpec((4, 4)), "b": WeightSpec((4, 4))}, "cpu", convert_to=torch.float32)
+    assert out["a"].dtype == torch.bfloat16 and out["b"].dtype == torch.float32
+    assert torch.equal(out["b"], mixed["b"].float())
+
+
 def test_broken_files_are_refused(tmp_path):
     folder = make_model_folder(tmp_path, "A", seed=3)
     path = folder / "model.safetensors"

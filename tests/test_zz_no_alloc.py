@@ -6,8 +6,11 @@ cudaMalloc's device synchronisation, a host that forbids allocator calls in call
 them the scratch of the split-KV attention lives in a static device array inside the library.
 This test calls that entry point through its exported C symbol, twice in a row with different
 inputs and slice counts (the array keeps the first call's contents), and compares with the
-ordinary entry point, whose scratch the caller allocates.  It also checks that a call too large
-for the array is refused before anything runs.
+ordinary entry point, whose scratch the caller allocates.  It checks what the entry point is for --
+the calls leave the device's free memory and torch's allocation count where they were -- and that a
+call too large for the array is refused before anything runs, to the token: the largest call that
+fits runs and is right, one token more is refused, and so is a call whose partial results alone
+would fit but not together with its counters.
 
 The file's name makes pytest collect it last, so a run that stops at the first failure has
 already run every other test.  It passes alone in a fresh process and after the other tests.
@@ -34,8 +37,9 @@ def _symbol():
     return fn, int(cap())
 
 
-def _call(fn, q, case, tok_pos, tok_seq, H, Hkv, hd, scale, window, n_splits):
-    out = torch.full((q.shape[0], H * hd), float("nan"), dtype=torch.bfloat16, device=q.device)
+def _call(fn, q, case, tok_pos, tok_seq, H, Hkv, hd, scale, window, n_splits, out=None):
+    if out is None:
+        out = torch.full((q.shape[0], H * hd), float("nan"), dtype=torch.bfloat16, device=q.device)
     p = lambda t: c_void_p(t.data_ptr())  # noqa: E731
     rc = fn(p(q), q.stride(0), p(case.k_pages), p(case.v_pages), p(case.table), case.table.stride(0), p(tok_pos),
             p(tok_seq), p(case.slots), p(out), q.shape[0], H, Hkv, hd, case.page_size, float(scale), int(window or 0),
@@ -58,8 +62,14 @@ def test_static_scratch_entry_point_matches_the_allocating_one():
         q = _rand((6, (H + 2 * Hkv) * hd), torch.bfloat16, seed)
         want = ops.attn_decode(q, case.k_pages, case.v_pages, case.table, tok_pos, tok_seq, case.slots, H, Hkv, hd,
                                case.page_size, scale, window, n_splits)
-        rc, got = _call(fn, q, case, tok_pos, tok_seq, H, Hkv, hd, scale, window, n_splits)
+        out = torch.full((6, H * hd), float("nan"), dtype=torch.bfloat16, device=q.device)
         torch.cuda.synchronize()
+        # What the entry point exists for: the call itself allocates nothing, on the device or through torch.
+        free_before, count_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_stats()["allocation.all.allocated"]
+        rc, got = _call(fn, q, case, tok_pos, tok_seq, H, Hkv, hd, scale, window, n_splits, out=out)
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before
+        assert torch.cuda.memory_stats()["allocation.all.allocated"] == count_before
         assert rc == 0
         ref = case.reference(q[:, :H * hd].reshape(-1, H, hd).float(), tok_seq.tolist(), tok_pos.tolist(), H, scale,
                              window)
@@ -86,3 +96,37 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     torch.cuda.synchronize()
     assert rc == -4
     assert bool(out.isnan().all())            # nothing ran
+
+
+def test_static_scratch_capacity_is_exact_to_the_token():
+    """16 heads over 2 kv heads of 16, 16 slices: a token needs 16 * 16 * 18 floats of partial results and 2
+    counters.  454 tokens fit the 2 Mi floats and run; with 455 the partial results alone would still fit
+    (2,096,640) but not with the counters (2,097,550): refused.  Sizes that the kernel does not take are
+    refused with -2 and leave the array alone."""
+    from longbow_quarrel_b200.kernels import ops
+    from test_gpu_kernels import PagedCase, _ints, _rand
+    fn, capacity = _symbol()
+    H, Hkv, hd, n_splits = 16, 2, 16, 16
+    per_token = H * n_splits * (hd + 2) + Hkv
+    assert 454 * per_token <= capacity < 455 * per_token and 455 * (per_token - Hkv) <= capacity
+    case = PagedCase([200, 90], Hkv, hd, torch.bfloat16, seed=11)
+    for T, want_rc in ((454, 0), (455, -4)):
+        q = _rand((T, (H + 2 * Hkv) * hd), torch.bfloat16, 94)
+        tok_seq = _ints([i % 2 for i in range(T)])
+        tok_pos = _ints([(i * 7) % (200 if i % 2 == 0 else 90) for i in range(T)])
+        rc, got = _call(fn, q, case, tok_pos, tok_seq, H, Hkv, hd, 0.25, None, n_splits)
+        torch.cuda.synchronize()
+        assert rc == want_rc
+        if rc == 0:
+            want = ops.attn_decode(q, case.k_pages, case.v_pages, case.table, tok_pos, tok_seq, case.slots, H, Hkv, hd,
+                                   case.page_size, 0.25, None, n_splits)
+            assert torch.equal(got, want)
+        else:
+            assert bool(got.isnan().all())
+    q = _rand((4, (H + 2 * Hkv) * hd), torch.bfloat16, 95)
+    for bad in (dict(H=15), dict(n_splits=33), dict(hd=12)):
+        args = {**dict(H=H, Hkv=Hkv, hd=hd, n_splits=4), **bad}
+        rc, got = _call(fn, q, case, _ints([5, 6, 7, 8]), _ints([0, 1, 0, 1]), args["H"], args["Hkv"], args["hd"], 0.25, None,
+                        args["n_splits"])
+        torch.cuda.synchronize()
+        assert rc == -2 and bool(got.isnan().all()), bad
