@@ -43,7 +43,7 @@ MODEL_1B = llama(2048, 16, 32, 8, 64, 8192, 32.0, True)          # Llama 3.2 1B
 CONTEXT = 4096
 BATCH = 8
 PREFILL_TOKENS = 2048
-E2E_WARM = 48          # decode steps after a prompt step before the end-to-end figure is timed
+E2E_WARM = 48          # decode steps after a prompt step before a decode figure is timed (device-timed or end to end)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 REFERENCE_UNAVAILABLE = ("the reference is a Go program for Apple Metal with no Python package: pip reports "
@@ -171,14 +171,18 @@ def events(torch):
     return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
 
-def decode_run(torch, engine, rng, V, batch: int, steps: int, warm: int, prompt_len: int, params, sampler=None):
+def decode_run(torch, engine, rng, V, batch: int, steps: int, warm: int, prompt_len: int, params, sampler=None,
+               settle: int = 0):
     """One prompt step, then decode steps fed with token ids that were drawn beforehand (no host read in the
-    loop), each followed by the sampler on its logits: what the device does in a step, timed on the device."""
+    loop), each followed by the sampler on its logits: what the device does in a step, timed on the device.
+    settle: untimed decode steps before the `warm` warm-up steps, for the clocks to come back from the prompt
+    step (a long prompt step runs at the power cap, and the steps right after it at about half the clock)."""
     from longbow_quarrel_b200.kernels import ops
     from longbow_quarrel_b200.sampling import sample
     slots = [engine.new_sequence() for _ in range(batch)]
     prompts = [rng.integers(0, V, prompt_len).tolist() for _ in range(batch)]
     logits = engine.step(list(zip(slots, prompts)))
+    warm += settle
     feed = rng.integers(0, V, (warm + steps, batch))
     scratch = torch.empty_like(logits)
     seq_ids = torch.arange(batch, dtype=torch.int32, device=logits.device)
@@ -246,7 +250,7 @@ def other_workload(torch, np, peaks, name, cfg, prompt_lengths, n_steps, params,
     if device_steps:
         # The same decode steps without the host in the loop (tokens drawn beforehand, nothing read back): what is
         # left of a step when the host costs nothing.  1 - device / end-to-end is the host's share of a step.
-        ms, _, _, _ = decode_run(torch, engine, rng, V, B, device_steps, 8, prompt_lengths[0], params)
+        ms, _, _, _ = decode_run(torch, engine, rng, V, B, device_steps, 8, prompt_lengths[0], params, settle=E2E_WARM)
         out[f"{name}_device_ms_per_step"] = ms / device_steps
         out[f"{name}_host_share"] = max(0.0, 1.0 - (ms / device_steps) / ms_step)
     engine.close()
@@ -341,7 +345,8 @@ def main() -> int:
                "frac": pf_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)}
 
     # ------------------------------------------------------------------ decode, timed on the device
-    ms, mean_ctx, launches, clocks = decode_run(torch, engine, rng, V, BATCH, K, W, CONTEXT - (W + K), greedy, ClockSampler())
+    ms, mean_ctx, launches, clocks = decode_run(torch, engine, rng, V, BATCH, K, W, CONTEXT - (W + K + E2E_WARM), greedy,
+                                                ClockSampler(), settle=E2E_WARM)
     ms_per_step = ms / K
     value = BATCH * K / (ms / 1e3)
     bytes_step = decode_bytes(cfg, L, BATCH, mean_ctx)
@@ -352,12 +357,10 @@ def main() -> int:
     # ------------------------------------------------------------------ end to end through generate()
     # K steps through the public entry point: host token ids in, one copy of the step's integers to the device and
     # one read of the sampled ids a step.  Timed on the host from the arrival of one step's tokens to that of the
-    # K-th step after it.  The device-timed figure above starts after an idle moment (the clock sampler's start);
-    # generation does not pause between its prompt step and its first decode steps, and those run at the reduced
-    # clocks that a long prompt step under the power cap leaves behind (about a dozen steps; reported below with
-    # the clock they ran at).  So that both figures time the same kind of steps, this one begins E2E_WARM steps
-    # after the prompt.
-    W_dev, W = W, max(W, E2E_WARM)
+    # K-th step after it.  The decode steps right after a long prompt step run at the reduced clocks that the
+    # prompt step under the power cap leaves behind (about a dozen steps; reported below with the clock they ran
+    # at), so this figure, like the device-timed one above, begins E2E_WARM + W steps after the prompt.
+    W_dev, W = W, W + E2E_WARM
     prompt_len = CONTEXT - (W + K) - 1
     prompts = [rng.integers(0, V, prompt_len).tolist() for _ in range(BATCH)]
     engine.generate(prompts[:BATCH], max_new_tokens=3, sampling=greedy, stop_ids=[])       # warm-up
@@ -384,7 +387,7 @@ def main() -> int:
     if not args.no_points:
         for b in (1, 64):
             k = max(16, K // 2)
-            ms_b, ctx_b, _, _ = decode_run(torch, engine, rng, V, b, k, W, CONTEXT - (W + k), greedy)
+            ms_b, ctx_b, _, _ = decode_run(torch, engine, rng, V, b, k, W, CONTEXT - (W + k + E2E_WARM), greedy, settle=E2E_WARM)
             points[f"decode_b{b}"] = b * k / (ms_b / 1e3)
             points[f"decode_b{b}_frac"] = decode_bytes(cfg, L, b, ctx_b) / (ms_b / k / 1e3) / 1e9 / peaks["hbm_gbs"]
     engine.close()
@@ -410,7 +413,7 @@ def main() -> int:
                    "head_dim": cfg["head_dim"], "intermediate_size": cfg["intermediate_size"],
                    "vocab_size": V, "rope_theta": cfg["rope_theta"], "rope_scaling": "llama3 factor 8 low 1 high 4 orig 8192",
                    "rms_norm_eps": cfg["rms_norm_eps"], "tied_embeddings": False,
-                   "decode_context_mean": mean_ctx, "prefill_tokens": PREFILL_TOKENS,
+                   "decode_context_mean": mean_ctx, "prefill_tokens": PREFILL_TOKENS, "settle_steps_after_prompt": E2E_WARM,
                    "l2": "every step reads 15 GB of weights, far more than L2; no flush"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "prefill": prefill, "roofline": roofline,
         "points": points, "impl": "ours",

@@ -83,7 +83,10 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
     const int kvh = blockIdx.y / gtiles, gt = blockIdx.y % gtiles;
     // No pdl_launch_dependents() here: released early, the blocks of the product that follows moved
     // onto the SMs this kernel leaves free and fetched weights against it (measured: the step ran
-    // 50 % slower).  The kernel after this one starts when this one ends.
+    // 50 % slower).  Released late instead (once a block's keys and values have all arrived) it still lost 40 %:
+    // the product after this one releases its own successor at its start, and that one (the gate and up
+    // product, six waves of blocks) then takes the places that the product before it still needs.
+    // The kernel after this one starts when this one ends.
     // Positions, slots and page table are written before the step starts, never by a kernel of the
     // step, so they may be read before the kernel ahead is known to have finished.
     const int pos = tok_pos[tok], len = pos + 1;

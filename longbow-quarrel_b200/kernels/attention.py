@@ -10,15 +10,9 @@ USE_TC_PREFILL = True        # head_dim 64 and 128: prefill attention on tcgen05
 MAX_SPLITS = 32
 KEYS_PER_SPLIT = 128         # a slice shorter than this is not worth a block of its own
 
-_sm_count: dict = {}
-
-
 def resident_blocks(device) -> int:
     """Blocks of the decode kernel that run at a time: one (8 warps, ~200 KB of key/value rings) per SM."""
-    key = torch.device(device).index or 0
-    if key not in _sm_count:
-        _sm_count[key] = torch.cuda.get_device_properties(key).multi_processor_count
-    return _sm_count[key]
+    return ops.sm_count(device)
 
 
 def decode_splits(n_tokens: int, Hkv: int, group_tiles: int, max_kv: int, resident: int) -> int:

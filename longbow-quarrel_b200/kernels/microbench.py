@@ -7,6 +7,7 @@
     python -m longbow_quarrel_b200.kernels.microbench step --batch 8 --context 4096 --layers 4
     python -m longbow_quarrel_b200.kernels.microbench prefill --tokens 2048 --layers 4
     python -m longbow_quarrel_b200.kernels.microbench timeline --batch 8 --layers 6
+    python -m longbow_quarrel_b200.kernels.microbench timeline --prompt --tokens 2048 --layers 4
 
 Each kernel is timed with CUDA events over `--iters` launches after `--warmup`, captured
 into one CUDA graph so that no host time lies between the launches (`--no-graph` launches
@@ -101,13 +102,17 @@ def bench_chain(args) -> dict:
     x = torch.randn(M, D, device=dev, dtype=torch.bfloat16)
     res = torch.zeros(M, D, device=dev, dtype=torch.float32)
 
+    gain = torch.ones(D, device=dev, dtype=torch.float32)
+    attn = torch.randn(M, D, device=dev, dtype=torch.bfloat16)
+
     def run(i):
+        rows = x
         for j, w in enumerate(layers):
             nxt = layers[(j + 1) % L]
-            q = ops.gemm_skinny(x, w["qkv"], ops.EPI_BF16, next_w=w["o"])
-            ops.gemm_skinny(q[:, :D].contiguous() if False else x, w["o"], ops.EPI_RESID, res, next_w=w["gu"])
-            act = ops.gemm_skinny(x, w["gu"], ops.EPI_SWIGLU, next_w=w["down"])
-            ops.gemm_skinny(act, w["down"], ops.EPI_RESID, res, next_w=nxt["qkv"])
+            ops.gemm_skinny(rows, w["qkv"], ops.EPI_BF16, next_w=w["o"])
+            _, h2 = ops.gemm_skinny(attn, w["o"], ops.EPI_RESID, res, emit=(gain, 1e-5), next_w=w["gu"])
+            act = ops.gemm_skinny(h2, w["gu"], ops.EPI_SWIGLU, next_w=w["down"])
+            _, rows = ops.gemm_skinny(act, w["down"], ops.EPI_RESID, res, emit=(gain, 1e-5), next_w=nxt["qkv"])
     ms = _time(run, args.iters, args.warmup)
     nbytes = L * (6144 * D + D * D + 2 * F * D + D * F) * 2
     return {"kernel": "chain of a layer's products", "M": M, "layers": L, "ms_per_layer": ms / L, "gbs": nbytes / ms / 1e6,
@@ -173,17 +178,27 @@ def bench_attn_prefill(args) -> dict:
             "tflops": flops / ms / 1e9}
 
 
+# Layer sizes of the three Llama 3 shapes that the measurements name: hidden, heads, kv heads, head_dim, intermediate, tied.
+SHAPES = {"8b": (4096, 32, 8, 128, 14336, False), "3b": (3072, 24, 8, 128, 8192, True), "1b": (2048, 32, 8, 64, 8192, True)}
+
+
+def _config(args) -> dict:
+    D, H, Hkv, hd, F, tied = SHAPES[args.shape]
+    return dict(architectures=["LlamaForCausalLM"], hidden_size=D, num_hidden_layers=args.layers,
+                num_attention_heads=H, num_key_value_heads=Hkv, head_dim=hd, intermediate_size=F,
+                vocab_size=128256, rope_theta=500000.0, rms_norm_eps=1e-5, max_position_embeddings=131072,
+                tie_word_embeddings=tied,
+                rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                  original_max_position_embeddings=8192))
+
+
 def _decode_setup(args, use_graphs: bool):
-    """A model of Llama-3.1-8B layer sizes whose cache holds random keys and values, and a
+    """A model of the layer sizes that --shape names whose cache holds random keys and values, and a
     function that runs decode step i."""
     import numpy as np
 
     from ..engine import Engine
-    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, num_hidden_layers=args.layers,
-               num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336,
-               vocab_size=128256, rope_theta=500000.0, rms_norm_eps=1e-5, max_position_embeddings=131072,
-               rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
-                                 original_max_position_embeddings=8192))
+    cfg = _config(args)
     B, C = args.batch, args.context
     eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=B * (C + 64), max_batch=B,
                              max_context=C + 64, use_graphs=use_graphs)
@@ -217,7 +232,7 @@ def bench_timeline(args) -> dict:
     import re
 
     from torch.profiler import ProfilerActivity, profile
-    run = _decode_setup(args, True)
+    run = _prefill_setup(args) if args.prompt else _decode_setup(args, True)
     for i in range(args.warmup):
         run(i)
     torch.cuda.synchronize()
@@ -245,19 +260,16 @@ def bench_timeline(args) -> dict:
     for k in kinds.values():
         k["run_us"] = round(k["run_us"] / k["launches"], 2)
         k["adds_us"] = round(k["adds_us"] / k["launches"], 2)
-    return {"kernel": "decode step, kernel by kernel", "batch": args.batch, "context": args.context, "layers": args.layers,
+    return {"kernel": ("prompt" if args.prompt else "decode") + " step, kernel by kernel", "shape": args.shape, "batch": args.batch, "context": args.context, "layers": args.layers,
             "step_us": round(prev_end - t0, 1), "kinds": kinds}
 
 
-def bench_prefill(args) -> dict:
+def _prefill_setup(args):
+    """A model of the layer sizes that --shape names and a function that runs a prompt of --tokens tokens."""
     import numpy as np
 
     from ..engine import Engine
-    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, num_hidden_layers=args.layers,
-               num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336,
-               vocab_size=128256, rope_theta=500000.0, rms_norm_eps=1e-5, max_position_embeddings=131072,
-               rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
-                                 original_max_position_embeddings=8192))
+    cfg = _config(args)
     T = args.tokens
     eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=T + 64, max_batch=1, max_context=T + 64)
     rng = np.random.default_rng(0)
@@ -266,6 +278,12 @@ def bench_prefill(args) -> dict:
         slot = eng.new_sequence()
         eng.step([(slot, rng.integers(0, cfg["vocab_size"], T).tolist())])
         eng.end_sequence(slot)
+    return run
+
+
+def bench_prefill(args) -> dict:
+    T = args.tokens
+    run = _prefill_setup(args)
     ms = _time(run, args.iters, args.warmup, graph=False)
     return {"kernel": "prefill step", "tokens": T, "layers": args.layers, "ms": ms, "tokens_per_s": T / ms * 1e3}
 
@@ -286,7 +304,9 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="layer sizes for step, timeline and prefill")
     ap.add_argument("--eager", action="store_true")
+    ap.add_argument("--prompt", action="store_true", help="timeline: a prompt step of --tokens tokens instead of a decode step")
     ap.add_argument("--no-graph", action="store_true", help="time single kernels launch by launch from the host")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)

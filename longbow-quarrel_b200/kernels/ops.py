@@ -279,7 +279,29 @@ def clear_page_tails(k_pages: torch.Tensor, v_pages: torch.Tensor, items: list[t
 # ------------------------------------------------------------------ bfloat16 tensor-core kernels
 EPI_BF16, EPI_F32, EPI_RESID, EPI_SWIGLU = 0, 1, 2, 3
 SKINNY_MAX_ROWS = 64          # most rows gemm_skinny takes
-SKINNY_BEST_ROWS = 16         # up to here streaming W through registers beats the TMA-fed tcgen05 kernel
+SKINNY_BEST_ROWS = 16         # up to here streaming W through registers can beat the TMA-fed tcgen05 kernel
+SKINNY_SURE_ROWS = 8          # up to here it always does (one group of 8 rows: x stays in registers beside W)
+
+_sm_counts: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """Multiprocessors of the device (the current one by default)."""
+    index = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    if index not in _sm_counts:
+        _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _sm_counts[index]
+
+
+def streams_through_registers(M: int, N: int) -> bool:
+    """Whether a product of M rows with a weight of N rows goes to gemm_skinny rather than gemm_tc.  Up to 8
+    rows always.  From 9 to 16 rows only where its blocks of 16 weight rows fit the GPU at once (two a
+    multiprocessor): measured on B200 at 16 rows, weights of [4096, 4096] take 10.5 us there against 12.6 us in
+    gemm_tc, but [6144, 4096] 17.2 against 14.6, [28672, 4096] 60 against 48 and the head [128256, 4096]
+    225 against 167."""
+    if M <= SKINNY_SURE_ROWS:
+        return True
+    return M <= SKINNY_BEST_ROWS and -(-N // 16) <= 2 * sm_count()
 
 
 class NormedRows:

@@ -1,7 +1,8 @@
 """Tensor-core paths of the bfloat16 matrix products: which kernel takes which shape.
 
-rows <= 16   gemm_skinny: W streamed through registers into mma.sync (the fastest stream of W
+rows <= 8    gemm_skinny: W streamed through registers into mma.sync (the fastest stream of W
              measured: 6.4-6.9 TB/s on the LM head)
+9..16 rows   gemm_skinny where its blocks fit the GPU at once, else gemm_tc (ops.streams_through_registers)
 more rows    gemm_tc: 128 x 256 tiles, TMA ring, tcgen05 with two accumulators in tensor memory;
              with few tiles (few rows, narrow weight) it cuts the contraction into ranges so that
              every SM streams a share of W
@@ -17,7 +18,7 @@ from . import ops
 
 
 def _decode_kernel(M: int, N: int, K: int):
-    return ops.gemm_skinny if M <= ops.SKINNY_BEST_ROWS else ops.gemm_tc
+    return ops.gemm_skinny if ops.streams_through_registers(M, N) else ops.gemm_tc
 
 
 def _rows_for(fn, a):
