@@ -18,6 +18,7 @@ import torch
 from ..cache import CacheError
 from ..kernels import ops
 from ..sampling import SamplingParams, history_window, sample
+from ..sampling.sampler import needs_scratch
 
 
 @dataclass
@@ -77,10 +78,13 @@ class EngineBackend:
         if self.params.uses_history:
             h, n = history_window(histories)
             hist, hist_len = torch.from_numpy(h).to(dev), torch.from_numpy(n).to(dev)
-        if self._scratch is None or self._scratch.shape[0] < logits.shape[0]:
-            self._scratch = torch.empty_like(logits)
-        tokens = sample(logits, self.params, self.seed, seq_ids, step_ids, hist, hist_len,
-                        scratch=self._scratch[:logits.shape[0]], step_offset=offset)
+        scratch = None
+        if needs_scratch(logits.shape[1]):
+            if self._scratch is None or self._scratch.shape[0] < logits.shape[0]:
+                self._scratch = torch.empty_like(logits)
+            scratch = self._scratch[:logits.shape[0]]
+        tokens = sample(logits, self.params, self.seed, seq_ids, step_ids, hist, hist_len, scratch=scratch,
+                        step_offset=offset)
         n = tokens.numel()
         if len(self._pinned) < 4:
             self._pinned.append(torch.empty(max(n, self.engine.cache.max_slots), dtype=torch.int32).pin_memory())

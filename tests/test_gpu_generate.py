@@ -161,6 +161,40 @@ def test_sampler_top_k_one_is_greedy_and_filters_hold():
     assert ((counts - expect) ** 2 / expect).sum() < 16.3      # chi-square, 3 degrees of freedom, p = 0.001
 
 
+@pytest.mark.parametrize("V", [2048, 5001, 128256, 300000, 500000])
+def test_the_cluster_sampler_and_the_one_block_sampler_choose_the_same_tokens(V):
+    """A row spread over the shared memory of a cluster of eight blocks, or in one block's scratch row in global
+    memory (500,000 logits fit no cluster and take that kernel by themselves): the same rules, the same draws."""
+    from longbow_quarrel_b200.sampling import SamplingParams, history_window, sample
+    from longbow_quarrel_b200.sampling.sampler import needs_scratch
+    assert needs_scratch(V) == (V == 500000)
+    rng = np.random.default_rng(V)
+    rows = 5
+    logits = (rng.standard_normal((rows, V)) * 4).astype(np.float32)
+    logits[0, V - 1] = logits[0].max() + 1.0        # the maximum in the last block's part
+    logits[2, 700:720] = logits[2].max()            # twenty equal weights at the top: ties at a top-k cut-off
+    dev = torch.from_numpy(logits).cuda()
+    seq = torch.arange(rows, dtype=torch.int32, device="cuda")
+    step = torch.full((rows,), 7, dtype=torch.int32, device="cuda")
+    hist, n = history_window([list(range(i, i + 40)) + [V - 1] for i in range(rows)])
+    hist, n = torch.from_numpy(hist).cuda(), torch.from_numpy(n).cuda()
+    for params in (SamplingParams(), SamplingParams(temperature=1.0, seed=4), SamplingParams(temperature=0.6, top_k=40, seed=5),
+                   SamplingParams(temperature=0.6, top_k=7, seed=5), SamplingParams(temperature=1.2, top_p=0.9, seed=6),
+                   SamplingParams(temperature=0.7, top_k=40, top_p=0.95, repetition_penalty=1.3, seed=7),
+                   SamplingParams(repetition_penalty=5.0)):
+        kw = dict(history=hist, history_len=n) if params.uses_history else {}
+        for offset in (0, 3):
+            a = sample(dev, params, params.seed or 1, seq, step, step_offset=offset, **kw).cpu().numpy()
+            b = sample(dev, params, params.seed or 1, seq, step, step_offset=offset, one_block=True, **kw).cpu().numpy()
+            assert list(a) == list(b), (params, offset)
+    bad = logits.copy()
+    bad[1, :V // 2] = np.nan
+    bad[3, 5] = np.inf
+    for one_block in (False, True):
+        out = sample(torch.from_numpy(bad).cuda(), SamplingParams(temperature=0.9, seed=2), 2, seq, step, one_block=one_block)
+        assert list(out.cpu().numpy()[[1, 3]]) == [V // 2, 0]
+
+
 def test_sampler_penalty_and_bad_logits():
     from longbow_quarrel_b200.sampling import SamplingParams, history_window, sample
     logits = np.array([[1.0, 3.0, 2.9, -1.0], [1.0, -0.5, -0.6, -2.0]], dtype=np.float32)
