@@ -8,6 +8,7 @@
     python -m longbow_quarrel_b200.kernels.microbench prefill --tokens 2048 --layers 4
     python -m longbow_quarrel_b200.kernels.microbench timeline --batch 8 --layers 6
     python -m longbow_quarrel_b200.kernels.microbench timeline --prompt --tokens 2048 --layers 4
+    python -m longbow_quarrel_b200.kernels.microbench sample --batch 64 --temperature 0.7 --top-k 40 --top-p 0.95
 
 Each kernel is timed with CUDA events over `--iters` launches after `--warmup`, captured
 into one CUDA graph so that no host time lies between the launches (`--no-graph` launches
@@ -117,6 +118,27 @@ def bench_chain(args) -> dict:
     nbytes = L * (6144 * D + D * D + 2 * F * D + D * F) * 2
     return {"kernel": "chain of a layer's products", "M": M, "layers": L, "ms_per_layer": ms / L, "gbs": nbytes / ms / 1e6,
             "prefetch_bytes": ops.PREFETCH_BYTES}
+
+
+def bench_sample(args) -> dict:
+    """The sampler on --batch rows of --vocab logits (rotated through copies larger than L2)."""
+    from ..sampling import SamplingParams, sample
+    rows, V, dev = args.batch, args.vocab, "cuda"
+    n = min(_copies(rows * V * 4), 64)
+    logits = [torch.randn(rows, V, device=dev) * 3 for _ in range(n)]
+    params = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, seed=3)
+    seq = torch.arange(rows, dtype=torch.int32, device=dev)
+    step = torch.zeros(rows, dtype=torch.int32, device=dev)
+    scratch = torch.empty_like(logits[0]) if args.one_block else None
+    out = torch.empty(rows, dtype=torch.int32, device=dev)
+
+    def run(i):
+        sample(logits[i % n], params, 3, seq, step, scratch=scratch, out=out, step_offset=i, one_block=args.one_block)
+    ms = _time(run, args.iters, args.warmup)
+    nbytes = rows * V * 4
+    return {"kernel": "sample (one block a row)" if args.one_block else "sample (a cluster a row)", "rows": rows, "vocab": V,
+            "temperature": args.temperature, "top_k": args.top_k, "top_p": args.top_p, "ms": ms, "bytes": nbytes,
+            "gbs": nbytes / ms / 1e6}
 
 
 def _paged(batch: int, context: int, Hkv: int, hd: int, dev):
@@ -291,7 +313,7 @@ def bench_prefill(args) -> dict:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("what", choices=["gemm_skinny", "gemm_tc", "attn_decode", "attn_prefill", "attn_prefill_tc", "chain", "step",
-                                     "prefill", "timeline"])
+                                     "prefill", "timeline", "sample"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -305,6 +327,11 @@ def main(argv=None) -> int:
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="layer sizes for step, timeline and prefill")
+    ap.add_argument("--vocab", type=int, default=128256)
+    ap.add_argument("--temperature", type=float, default=0.0)
+    ap.add_argument("--top-k", type=int, default=0)
+    ap.add_argument("--top-p", type=float, default=1.0)
+    ap.add_argument("--one-block", action="store_true", help="sample: the kernel that takes a row per block")
     ap.add_argument("--eager", action="store_true")
     ap.add_argument("--prompt", action="store_true", help="timeline: a prompt step of --tokens tokens instead of a decode step")
     ap.add_argument("--no-graph", action="store_true", help="time single kernels launch by launch from the host")
@@ -317,6 +344,8 @@ def main(argv=None) -> int:
         out = bench_gemm(args.what, args)
     elif args.what == "chain":
         out = bench_chain(args)
+    elif args.what == "sample":
+        out = bench_sample(args)
     elif args.what == "attn_decode":
         out = bench_attn_decode(args)
     elif args.what in ("attn_prefill", "attn_prefill_tc"):
