@@ -26,8 +26,10 @@ namespace skinny {
 constexpr int WARPS = 8;
 constexpr int ROWS = 16;     // rows of W per unit
 constexpr int KC = 32;       // k per chunk
-constexpr int UNROLL = 4;    // chunks per warp and round
-constexpr int STEP = WARPS * UNROLL;
+// Chunks per warp and round.  With one group of 8 tokens a thread holds four chunks of W and of x; with two groups
+// it holds two chunks of W and of both groups' x (the same registers): x read inside the products instead, from
+// L1, made two groups 1.4 times slower than one.  More groups read x inside the products.
+template <int MT> struct Round { static constexpr int UNROLL = MT == 2 ? 2 : 4; static constexpr int XG = MT <= 2 ? MT : 0; };
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     uint4 v;
@@ -77,8 +79,9 @@ struct NormArgs {
 // few tokens) the tokens' x as B fragments, all loaded before any of it is used.
 template <int MT>
 struct Frags {
+    static constexpr int UNROLL = Round<MT>::UNROLL;
     uint4 a0[UNROLL], a1[UNROLL];
-    uint4 b[UNROLL];                    // x of the tokens, kept only when there is one group of 8 tokens
+    uint4 b[Round<MT>::XG > 0 ? Round<MT>::XG : 1][UNROLL];      // x of the tokens, kept for at most two groups of 8
 };
 
 template <int MT> struct Scratch {
@@ -91,6 +94,9 @@ template <int MT> struct Scratch {
 // have finished); `run` does the rest and needs x.
 template <int MT, int EPI, bool FRESH>
 struct Unit {
+    static constexpr int UNROLL = Round<MT>::UNROLL;
+    static constexpr int XG = Round<MT>::XG;
+    static constexpr int STEP = WARPS * UNROLL;
     const __nv_bfloat16 *X, *w0, *w1;
     int M, N, K, n0, n1, c_hi, warp, lane, g, t;
     bool r0ok, r1ok;
@@ -127,14 +133,16 @@ struct Unit {
         }
     }
     __device__ __forceinline__ void load_x(int c0, Frags<MT>& f) const {
-        if (MT == 1) {
+        if (XG > 0) {
             const uint4 zero = make_uint4(0, 0, 0, 0);
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
                 int c = c0 + u * WARPS;
                 int k = c * KC + t * 8;
                 bool ok = c < c_hi && k < K;
-                f.b[u] = (ok && g < M) ? ld_act16<FRESH>(X + (size_t)g * K + k) : zero;
+#pragma unroll
+                for (int j = 0; j < XG; ++j)
+                    f.b[j][u] = (ok && j * 8 + g < M) ? ld_act16<FRESH>(X + (size_t)(j * 8 + g) * K + k) : zero;
             }
         }
     }
@@ -148,8 +156,8 @@ struct Unit {
 #pragma unroll
             for (int j = 0; j < MT; ++j) {
                 uint4 b;
-                if (MT == 1) {
-                    b = f.b[u];
+                if (XG > 0) {
+                    b = f.b[j][u];
                 } else {
                     int m = j * 8 + g;
                     b = (ok && m < M) ? ld_act16<FRESH>(X + (size_t)m * K + k) : zero;

@@ -280,7 +280,7 @@ def clear_page_tails(k_pages: torch.Tensor, v_pages: torch.Tensor, items: list[t
 EPI_BF16, EPI_F32, EPI_RESID, EPI_SWIGLU = 0, 1, 2, 3
 SKINNY_MAX_ROWS = 64          # most rows gemm_skinny takes
 SKINNY_BEST_ROWS = 16         # up to here streaming W through registers can beat the TMA-fed tcgen05 kernel
-SKINNY_SURE_ROWS = 8          # up to here it always does (one group of 8 rows: x stays in registers beside W)
+SKINNY_SURE_ROWS = int(os.environ.get("LQ_SKINNY_SURE_ROWS", "8"))   # up to here it always does (one group of 8 rows, four chunks a round)
 
 _sm_counts: dict = {}
 

@@ -31,7 +31,7 @@ UNUSUAL = {
     # a head size between the templates of the tensor-core attention kernels
     "head 96": dict(hidden_size=192, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2, head_dim=96,
                     intermediate_size=344, vocab_size=1001),
-    # the survey's micro-case: heads * head_dim != hidden and a head of 8, below every tensor-core tile
+    # heads * head_dim != hidden and a head of 8, below every tensor-core tile
     "head 8": dict(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=8,
                    intermediate_size=88, vocab_size=200),
     # an even head size that is no multiple of 8: rotation pairs that no 16-byte access covers
