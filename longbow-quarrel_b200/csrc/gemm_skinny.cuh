@@ -219,7 +219,27 @@ struct Unit {
         for (int j = 0; j < MT; ++j)
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
-        if (MT <= 2) {
+        if (MT == 2) {
+            // Two groups of tokens: a round is two chunks, so two rounds are kept in flight beyond the one that is
+            // being multiplied (as many bytes of W on their way as with one group and rounds of four chunks).
+            Frags<MT> fb, fc;
+            int c0 = warp;
+            if (c0 < c_hi) load_x(c0, fa);
+            if (c0 + STEP < c_hi) { load_w(c0 + STEP, fb); load_x(c0 + STEP, fb); }
+            while (c0 < c_hi) {
+                if (c0 + 2 * STEP < c_hi) { load_w(c0 + 2 * STEP, fc); load_x(c0 + 2 * STEP, fc); }
+                compute(c0, fa, acc);
+                c0 += STEP;
+                if (c0 >= c_hi) break;
+                if (c0 + 2 * STEP < c_hi) { load_w(c0 + 2 * STEP, fa); load_x(c0 + 2 * STEP, fa); }
+                compute(c0, fb, acc);
+                c0 += STEP;
+                if (c0 >= c_hi) break;
+                if (c0 + 2 * STEP < c_hi) { load_w(c0 + 2 * STEP, fb); load_x(c0 + 2 * STEP, fb); }
+                compute(c0, fc, acc);
+                c0 += STEP;
+            }
+        } else if (MT <= 2) {
             // Few tokens: the loads of the next round are in flight while the current one is multiplied.
             Frags<MT> fb;
             int c0 = warp;

@@ -62,7 +62,7 @@ def note(weight: "LinearWeight") -> None:
 FOLD_NORMS = os.environ.get("LQ_FOLD_NORMS", "1") != "0"      # 0: every norm runs as a kernel of its own
 
 
-FOLD_MAX_ROWS = 8       # measured on B200: 3 % of a decode step at 1 row, 1.4 % at 8, a loss at 16
+FOLD_MAX_ROWS = int(os.environ.get("LQ_FOLD_MAX_ROWS", "8"))       # measured on B200: 3 % of a decode step at 1 row, 1.4 % at 8, a loss at 16
 
 
 def can_defer_norm(rows: int, width: int, dtype: torch.dtype) -> bool:

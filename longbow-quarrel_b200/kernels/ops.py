@@ -279,8 +279,7 @@ def clear_page_tails(k_pages: torch.Tensor, v_pages: torch.Tensor, items: list[t
 # ------------------------------------------------------------------ bfloat16 tensor-core kernels
 EPI_BF16, EPI_F32, EPI_RESID, EPI_SWIGLU = 0, 1, 2, 3
 SKINNY_MAX_ROWS = 64          # most rows gemm_skinny takes
-SKINNY_BEST_ROWS = 16         # up to here streaming W through registers can beat the TMA-fed tcgen05 kernel
-SKINNY_SURE_ROWS = int(os.environ.get("LQ_SKINNY_SURE_ROWS", "8"))   # up to here it always does (one group of 8 rows, four chunks a round)
+SKINNY_BEST_ROWS = int(os.environ.get("LQ_SKINNY_BEST_ROWS", "16"))         # up to here streaming W through registers beats the TMA-fed tcgen05 kernel in a step
 
 _sm_counts: dict = {}
 
@@ -294,14 +293,14 @@ def sm_count(device=None) -> int:
 
 
 def streams_through_registers(M: int, N: int) -> bool:
-    """Whether a product of M rows with a weight of N rows goes to gemm_skinny rather than gemm_tc.  Up to 8
-    rows always.  From 9 to 16 rows only where its blocks of 16 weight rows fit the GPU at once (two a
-    multiprocessor): measured on B200 at 16 rows, weights of [4096, 4096] take 10.5 us there against 12.6 us in
-    gemm_tc, but [6144, 4096] 17.2 against 14.6, [28672, 4096] 60 against 48 and the head [128256, 4096]
-    225 against 167."""
-    if M <= SKINNY_SURE_ROWS:
-        return True
-    return M <= SKINNY_BEST_ROWS and -(-N // 16) <= 2 * sm_count()
+    """Whether a product of M rows with a weight of N rows goes to gemm_skinny rather than gemm_tc: up to 16 rows.
+    Timed alone at 16 rows gemm_tc is the faster kernel for every weight but the square output projection
+    ([28672, 4096]: 48 us against 54; the head [128256, 4096]: 167 against 211), yet a whole model runs no
+    faster with it (8B shape, 16 rows, context 2,048: 4.47 ms a step with gemm_tc for every product, 4.40 with
+    gemm_skinny), and 15 % slower when only the products of more than one wave of blocks take it, as the single
+    timings suggest (6.11 against 5.43 ms at context 4,096): its blocks fill a multiprocessor, so nothing of the
+    kernel after it overlaps with it.  From 17 rows on gemm_tc wins (17 rows: 4.50 against 5.69 ms)."""
+    return M <= SKINNY_BEST_ROWS
 
 
 class NormedRows:

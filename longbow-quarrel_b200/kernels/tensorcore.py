@@ -1,8 +1,7 @@
 """Tensor-core paths of the bfloat16 matrix products: which kernel takes which shape.
 
-rows <= 8    gemm_skinny: W streamed through registers into mma.sync (the fastest stream of W
-             measured: 6.4-6.9 TB/s on the LM head)
-9..16 rows   gemm_skinny where its blocks fit the GPU at once, else gemm_tc (ops.streams_through_registers)
+rows <= 16   gemm_skinny: W streamed through registers into mma.sync (the fastest stream of W
+             measured: 6.9-7.0 TB/s on the LM head at 1 to 8 rows); see ops.streams_through_registers
 more rows    gemm_tc: 128 x 256 tiles, TMA ring, tcgen05 with two accumulators in tensor memory;
              with few tiles (few rows, narrow weight) it cuts the contraction into ranges so that
              every SM streams a share of W

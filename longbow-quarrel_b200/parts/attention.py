@@ -76,8 +76,7 @@ class Attention(Mixer):
         tables = self.position.tables() if self.position is not None else None
         fused = (store and h.dtype == torch.bfloat16 and self.w_qkv.tensor.dtype == torch.bfloat16 and self.D % 8 == 0
                  and self.hd % 16 == 0 and cache_view.k_pages.dtype == torch.bfloat16 and (self.position is None or tables is not None))
-        few = h.shape[0] <= ops.SKINNY_BEST_ROWS and (ops.streams_through_registers(h.shape[0], self.w_qkv.N)
-                                                     or self.hd not in (64, 128))
+        few = h.shape[0] <= 16 and ops.streams_through_registers(h.shape[0], self.w_qkv.N)
         if fused and (few or (self.hd in (64, 128) and not isinstance(h, ops.NormedRows))):
             # Projection, rotation and cache write are one kernel (for few tokens the one that streams the
             # weights through registers, else the tcgen05 one).
