@@ -39,10 +39,15 @@ class _Sampled:
 
 
 class EngineBackend:
-    def __init__(self, engine, params: SamplingParams, run_ahead: bool = True):
+    def __init__(self, engine, params: SamplingParams, run_ahead: bool = True, logits_callback=None):
+        """logits_callback(request, step, logits): called with the float32 logits (a host tensor [vocab]) from
+        which each token was sampled, before the token is handed back; asking for them costs a copy of every
+        step's logits to the host and switches running ahead off (the step queued ahead would overwrite the
+        captured step's logits before they are read)."""
         self.engine, self.params = engine, params
         self.seed = params.resolved_seed()
-        self.run_ahead = run_ahead and not params.uses_history
+        self.logits_callback = logits_callback
+        self.run_ahead = run_ahead and not params.uses_history and logits_callback is None
         self.needs_history = params.uses_history        # the generation loop builds histories only for a penalty
         self._draw_ids: dict = {}                        # requests of a step -> their ids on the device (and zeros)
         self._scratch = None
@@ -118,6 +123,10 @@ class EngineBackend:
             logits = self.engine.stepper.step(entries, None)
             current = _Sampled(handles, asked, *self._sample(logits, requests, steps, histories))
             rows = list(range(len(handles)))
+            if self.logits_callback is not None:
+                host = logits.to("cpu")
+                for row, (request, step) in enumerate(zip(requests, steps)):
+                    self.logits_callback(request, step, host[row])
         if self.run_ahead:
             try:
                 logits = self.engine.stepper.step_fed(list(handles), current.device, rows)

@@ -128,17 +128,21 @@ class Engine:
 
     # ------------------------------------------------------------------ generation
     def generate(self, prompts, max_new_tokens: int = 20, sampling: SamplingParams | None = None, stop_ids=None,
-                 callback=None, include_stop: bool = False, batch_size: int | None = None) -> list[list[int]]:
+                 callback=None, include_stop: bool = False, batch_size: int | None = None,
+                 logits_callback=None) -> list[list[int]]:
         """New tokens for each prompt (lists of token ids).  Prompts are run in batches of
         at most batch_size that start together; a sequence ends at a stop token (by default
         the model's eos ids; the stop token is not returned), after max_new_tokens, or when
-        the context is full.  callback(prompt index, token id) is called for every token.
-        Counterpart of Infer / InferWithCallback (internal/engine/engine.go:1277-1290)."""
+        the context is full.  callback(prompt index, token id) is called for every token;
+        logits_callback(prompt index, step, logits) with the float32 logits (on the host) from which the
+        token of that step was sampled, before the token's own callback (it costs a copy of every step's
+        logits and the overlap of steps with the host's work).
+        Counterpart of Infer / InferWithCallback / InferWithCallbackLogits (internal/engine/engine.go:1277-1290)."""
         from .backend import EngineBackend
         sampling = sampling or SamplingParams()
         stops = tuple(self.model.spec.stop_tokens) if stop_ids is None else tuple(stop_ids)
         with torch.cuda.device(self.device):
-            outputs, stats = generate(EngineBackend(self, sampling), prompts, max_new_tokens, stops, callback,
+            outputs, stats = generate(EngineBackend(self, sampling, logits_callback=logits_callback), prompts, max_new_tokens, stops, callback,
                                       include_stop, batch_size or self.cache.max_slots,
                                       self.runtime.max_context)
         self.last_stats = stats

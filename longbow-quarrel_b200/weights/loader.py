@@ -75,6 +75,43 @@ def _keep_dtype(t: torch.Tensor, spec: WeightSpec, convert_to: torch.dtype | Non
     raise SafetensorsError(f"dtype {t.dtype} is not a weight dtype")
 
 
+class _Uploader:
+    """Host memory that is mapped from a file goes to the device through two pinned buffers in turn: while one
+    buffer's copy to the device runs (asynchronously, on a stream of its own), the next piece of the file is read
+    into the other.  The reference maps its file and hands each tensor to the device as it walks the table
+    (internal/gguf/reader.go:16-35, internal/engine/engine.go:736-806)."""
+
+    CHUNK = 64 << 20
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.stream = torch.cuda.Stream(device=self.device)
+        self.buffers = [torch.empty(self.CHUNK, dtype=torch.uint8).pin_memory() for _ in range(2)]
+        self.free = [torch.cuda.Event(), torch.cuda.Event()]
+        self.turn = 0
+
+    def upload(self, src: torch.Tensor) -> torch.Tensor:
+        src = src.contiguous()
+        dst = torch.empty(src.shape, dtype=src.dtype, device=self.device)
+        if src.numel() == 0:
+            return dst
+        src_bytes, dst_bytes = src.reshape(-1).view(torch.uint8), dst.reshape(-1).view(torch.uint8)
+        for lo in range(0, src_bytes.numel(), self.CHUNK):
+            n = min(self.CHUNK, src_bytes.numel() - lo)
+            buf = self.buffers[self.turn]
+            self.free[self.turn].synchronize()                  # the copy that last used this buffer has left it
+            buf[:n].copy_(src_bytes[lo:lo + n])
+            with torch.cuda.stream(self.stream):
+                dst_bytes[lo:lo + n].copy_(buf[:n], non_blocking=True)
+                self.free[self.turn].record(self.stream)
+            self.turn ^= 1
+        return dst
+
+    def finish(self) -> None:
+        self.stream.synchronize()
+        torch.cuda.current_stream(self.device).wait_stream(self.stream)
+
+
 def load_weights(folder, table: dict[str, WeightSpec], device, convert_to: torch.dtype | None = None,
                  unexpected: str = "error") -> dict[str, torch.Tensor]:
     """Every tensor of `table` on `device`.  A name with a `fallback` that is absent
@@ -109,9 +146,18 @@ def load_weights(folder, table: dict[str, WeightSpec], device, convert_to: torch
     if extra and unexpected == "warn":
         warnings.warn(f"{folder}: {len(extra)} tensors that the model does not name are skipped: " + ", ".join(sorted(extra)))
     out = {}
+    uploader = _Uploader(device) if torch.device(device).type == "cuda" else None
     for name, spec in table.items():
         if name in where:
-            out[name] = _keep_dtype(where[name].tensor(name), spec, convert_to).to(device, non_blocking=False).contiguous()
+            stored = where[name].tensor(name)
+            if uploader is None:
+                out[name] = _keep_dtype(stored, spec, convert_to).to(device).contiguous()
+            else:
+                out[name] = uploader.upload(stored)       # as stored; converted on the device below
+    if uploader is not None:
+        uploader.finish()
+        for name in list(out):
+            out[name] = _keep_dtype(out[name], table[name], convert_to).contiguous()
     for f in files:
         f.close()
     return out

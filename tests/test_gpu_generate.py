@@ -68,6 +68,31 @@ def test_one_token_prompts_in_reused_slots_do_not_take_the_step_queued_for_the_b
     assert eng.cache.pages_in_use() == 0 and eng.cache.slots.n_live == 0
 
 
+def test_logits_callback_gives_the_logits_each_token_was_chosen_from(tmp_path):
+    """The counterpart of the reference's InferWithCallbackLogits: per token the logits it was sampled from, the
+    plain implementation's for that position; greedy tokens are their maxima; asking for them changes no token."""
+    from longbow_quarrel_b200.sampling import SamplingParams
+    folder = make_model_folder(tmp_path, "B", seed=27)
+    eng = _engine(folder, "float32")
+    prompts = [random_tokens(n, 384, 90 + i) for i, n in enumerate([6, 1, 11])]
+    seen, order = {}, []
+
+    def on_logits(i, step, logits):
+        assert logits.device.type == "cpu" and logits.dtype == torch.float32 and logits.shape == (384,)
+        seen[(i, step)] = logits.numpy().copy()
+        order.append(("logits", i, step))
+    out = eng.generate(prompts, 5, SamplingParams(), stop_ids=[], logits_callback=on_logits, batch_size=2,
+                       callback=lambda i, t: order.append(("token", i, t)))
+    assert out == eng.generate(prompts, 5, SamplingParams(), stop_ids=[], batch_size=2)
+    assert sorted(seen) == sorted((i, s) for i in range(3) for s in range(5))
+    for i, (p, o) in enumerate(zip(prompts, out)):
+        ref = plain_logits(folder, p + o)
+        for s, tok in enumerate(o):
+            assert rel_err(seen[(i, s)], ref[len(p) + s - 1]) < TOL["float32"]
+            assert int(np.argmax(seen[(i, s)])) == tok
+    assert order.index(("logits", 0, 0)) < order.index(("token", 0, out[0][0]))
+
+
 def test_stop_tokens_end_sequences_early(tmp_path):
     from longbow_quarrel_b200.sampling import SamplingParams
     folder = make_model_folder(tmp_path, "A", seed=22)
