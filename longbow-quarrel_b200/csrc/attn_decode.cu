@@ -16,6 +16,11 @@
 // (max, sum) to scratch memory; the block that parks its slice last for a (token, kv head)
 // merges them (a counter per pair; without counters a second kernel merges).
 //
+// With a work list (lq_attn_decode_work) the blocks form teams of one block per (kv head, row tile);
+// a team walks a list of segments (token, range of key tiles) that the host has cut so that every
+// team reads the same number of tiles, however unequal the sequences are: a long sequence is
+// shared by several teams, short ones share a team, and all blocks run as one wave.
+//
 // Reference counterpart: att_fused_f16 (internal/device/kernels.metal:657-813), one
 // threadgroup per query head, scores in threadgroup memory.
 #include "common.cuh"
@@ -56,14 +61,16 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // HD: head_dim rounded up to 32, 64 or 128; the real head_dim hd is a multiple of 8.
+// Two blocks share an SM where their rings allow it (head_dim up to 64), so the registers are held to half the file.
 template <int HD>
-__global__ void __launch_bounds__(DW * 32, 1)
+__global__ void __launch_bounds__(DW * 32, HD <= 64 ? 2 : 1)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_pages,
                    const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ page_table, int pt_stride,
                    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                    __nv_bfloat16* __restrict__ out, int H, int Hkv, int hd, int page_size, float scale, int window,
-                   int n_splits, const char* next_w, unsigned next_piece, int early_loads) {
+                   int n_splits, int part_stride, const int* __restrict__ work, const char* next_w, unsigned next_piece,
+                   int early_loads) {
     constexpr int LD = HD + PAD;                   // shared-memory row length in elements
     constexpr int KD = HD / 16;                    // k16 steps over the head dimension
     constexpr int STAGE = 2 * TILE * LD;           // elements of one tile: K rows, then V rows
@@ -78,15 +85,38 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
     __shared__ int sm_last;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int split = blockIdx.x, tok = blockIdx.z;
     const int G = H / Hkv, gtiles = (G + 15) / 16;
-    const int kvh = blockIdx.y / gtiles, gt = blockIdx.y % gtiles;
+    // Without a work list: grid (slices, kv heads x row tiles, tokens), one segment per block.
+    // With one: grid (kv heads x row tiles, teams); the list starts with teams + 1 offsets into its
+    // segments, five integers each: token, first and last + 1 key tile (counted from the first
+    // tile the token sees), which part of the token this is, and how many parts the token has.
+    const int head_tile = work ? blockIdx.x : blockIdx.y;
+    const int kvh = head_tile / gtiles, gt = head_tile % gtiles;
+    int seg = 0, seg_end = 1;
+    const int* segments = nullptr;
+    if (work) {
+        seg = work[blockIdx.y];
+        seg_end = work[blockIdx.y + 1];
+        segments = work + gridDim.y + 1;
+    }
+    const size_t head_off = (size_t)kvh * page_size * hd;
+    __nv_bfloat16* my_ring = ring + (size_t)warp * RING * STAGE;
     // No pdl_launch_dependents() here: released early, the blocks of the product that follows moved
     // onto the SMs this kernel leaves free and fetched weights against it (measured: the step ran
     // 50 % slower).  Released late instead (once a block's keys and values have all arrived) it still lost 40 %:
     // the product after this one releases its own successor at its start, and that one (the gate and up
     // product, six waves of blocks) then takes the places that the product before it still needs.
     // The kernel after this one starts when this one ends.
+    bool waited = false;
+    for (; seg < seg_end; ++seg) {
+    if (waited) __syncthreads();        // the merge of the segment before has read the shared memory that the ring refills
+    int tok, split, parts, seg_lo, seg_hi;
+    if (work) {
+        const int* s = segments + 5 * seg;
+        tok = s[0]; seg_lo = s[1]; seg_hi = s[2]; split = s[3]; parts = s[4];
+    } else {
+        tok = blockIdx.z; split = blockIdx.x; parts = n_splits; seg_lo = seg_hi = 0;
+    }
     // Positions, slots and page table are written before the step starts, never by a kernel of the
     // step, so they may be read before the kernel ahead is known to have finished.
     const int pos = tok_pos[tok], len = pos + 1;
@@ -95,11 +125,15 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
 
     const int first_tile = start / TILE;
     const int n_tiles = (len + TILE - 1) / TILE - first_tile;
-    const int per_split = (n_tiles + n_splits - 1) / n_splits;
-    const int tile_lo = first_tile + split * per_split;
-    const int tile_hi = min(first_tile + n_tiles, tile_lo + per_split);
-    const size_t head_off = (size_t)kvh * page_size * hd;
-    __nv_bfloat16* my_ring = ring + (size_t)warp * RING * STAGE;
+    int tile_lo, tile_hi;
+    if (work) {
+        tile_lo = first_tile + seg_lo;
+        tile_hi = min(first_tile + n_tiles, first_tile + seg_hi);
+    } else {
+        const int per_split = (n_tiles + parts - 1) / parts;
+        tile_lo = first_tile + split * per_split;
+        tile_hi = min(first_tile + n_tiles, tile_lo + per_split);
+    }
 
     // This warp's tiles are tile_lo + warp, + DW, ...; `n` counts them.
     auto issue = [&](int n) {
@@ -123,14 +157,17 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
     // The keys and values of earlier positions were stored by earlier steps: a warp whose first tiles
     // do not hold the token's own position (which the kernel ahead is writing) asks for them at once.
     const int own_tile = pos / TILE;
-    bool early = early_loads != 0;
+    bool early = waited || early_loads != 0;       // after the wait nothing of the step is still being written
+    if (!waited) {
 #pragma unroll
-    for (int n = 0; n < RING - 1; ++n) early = early && (tile_lo + warp + n * DW != own_tile);
+        for (int n = 0; n < RING - 1; ++n) early = early && (tile_lo + warp + n * DW != own_tile);
+    }
     if (early) {
 #pragma unroll
         for (int n = 0; n < RING - 1; ++n) issue(n);
     }
-    pdl_wait();
+    if (!waited) pdl_wait();
+    waited = true;
     if (!early) {
 #pragma unroll
         for (int n = 0; n < RING - 1; ++n) issue(n);
@@ -234,7 +271,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
         __syncwarp();       // every lane is done with the slot before a later copy refills it
     }
     cp_async_wait<0>();
-    if (next_w && threadIdx.x == 0) {
+    if (next_w && threadIdx.x == 0 && seg == seg_end - 1) {
         // The weights that the stream reads after this kernel: each block asks for one piece of their
         // first bytes to be brought into L2 now that its own keys and values have arrived.
         const size_t b = ((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
@@ -275,49 +312,50 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
             }
         }
         int h = kvh * G + gt * 16 + r;
-        if (n_splits == 1) {
+        if (parts == 1) {
             out[((size_t)tok * H + h) * hd + d] = __float2bfloat16_rn(acc / l);
         } else {
-            size_t base = ((size_t)tok * H + h) * n_splits + split;
+            size_t base = ((size_t)tok * H + h) * part_stride + split;
             part_o[base * hd + d] = acc;
             if (d == 0) { part_ml[base * 2] = mx; part_ml[base * 2 + 1] = l; }
         }
     }
-    if (n_splits == 1 || counters == nullptr) return;
+    if (parts == 1 || counters == nullptr) continue;
     // The block that parks its slice last merges all slices of its (token, kv head, row tile):
     // out = sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M), slices in their order.
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-        int* counter = counters + (size_t)tok * gridDim.y + blockIdx.y;
+        int* counter = counters + (size_t)tok * Hkv * gtiles + head_tile;
         int old = atomicAdd(counter, 1);
-        sm_last = (old == n_splits - 1);
+        sm_last = (old == parts - 1);
         if (sm_last) *counter = 0;                  // ready for the next call
     }
     __syncthreads();
-    if (!sm_last) return;
+    if (!sm_last) continue;
     __threadfence();
     // Weights of the slices, one warp per row and one lane per slice (at most 32 slices).
     for (int r = warp; r < rows; r += DW) {
-        const float* ml = part_ml + ((size_t)tok * H + kvh * G + gt * 16 + r) * n_splits * 2;
-        const float m = lane < n_splits ? __ldcg(ml + 2 * lane) : -CUDART_INF_F;
-        const float ls = lane < n_splits ? __ldcg(ml + 2 * lane + 1) : 0.f;
+        const float* ml = part_ml + ((size_t)tok * H + kvh * G + gt * 16 + r) * part_stride * 2;
+        const float m = lane < parts ? __ldcg(ml + 2 * lane) : -CUDART_INF_F;
+        const float ls = lane < parts ? __ldcg(ml + 2 * lane + 1) : 0.f;
         const float mx = warp_max(m);
         const float w = m > -CUDART_INF_F ? expf(m - mx) : 0.f;
         const float l = warp_sum(ls * w);        // the same order of additions whichever block merges
-        if (lane < n_splits) sm_w[r][lane] = w;
+        if (lane < parts) sm_w[r][lane] = w;
         if (lane == 0) sm_inv[r] = 1.0f / l;
     }
     __syncthreads();
     for (int i = threadIdx.x; i < rows * hd; i += DW * 32) {
         const int r = i / hd, d = i % hd;
         const int h = kvh * G + gt * 16 + r;
-        const float* po = part_o + ((size_t)tok * H + h) * n_splits * hd + d;
+        const float* po = part_o + ((size_t)tok * H + h) * part_stride * hd + d;
         float acc = 0.f;
 #pragma unroll 8
-        for (int s2 = 0; s2 < n_splits; ++s2) acc += __ldcg(po + (size_t)s2 * hd) * sm_w[r][s2];
+        for (int s2 = 0; s2 < parts; ++s2) acc += __ldcg(po + (size_t)s2 * hd) * sm_w[r][s2];
         out[((size_t)tok * H + h) * hd + d] = __float2bfloat16_rn(acc * sm_inv[r]);
     }
+    }   // segments
 }
 
 // Merge the slices of one (token, head): out = sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M).
@@ -352,9 +390,10 @@ template <int HD>
 int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages, const int* page_table, int pt_stride,
            const int* tok_pos, const int* tok_seq, const int* slots, float* part_o, float* part_ml, int* counters,
            void* out, int T, int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
-           const void* next_w, long next_bytes, int early_loads, cudaStream_t stream) {
+           const int* work, int teams, const void* next_w, long next_bytes, int early_loads, cudaStream_t stream) {
     int G = H / Hkv, gtiles = (G + 15) / 16;
     dim3 grid(n_splits, Hkv * gtiles, T);
+    if (work) grid = dim3(Hkv * gtiles, teams, 1);      // n_splits is then the room for parts per token in the scratch
     const long n_blocks = (long)grid.x * grid.y * grid.z;
     long piece = (next_w && !((uintptr_t)next_w & 15)) ? next_bytes / n_blocks / 16 * 16 : 0;
     if (piece > (1 << 20)) piece = 1 << 20;
@@ -370,7 +409,7 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
     }
     int rc = launch_pdl(attn_decode_kernel<HD>, grid, dim3(DW * 32), smem, stream, (const __nv_bfloat16*)q, q_stride,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots,
-        part_o, part_ml, counters, (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, n_splits,
+        part_o, part_ml, counters, (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, n_splits, n_splits, work,
         (const char*)next_w, (unsigned)piece, early_loads);
     if (rc != LQ_OK || n_splits == 1 || counters != nullptr) return rc;
     return launch_pdl(attn_merge_kernel, dim3(T * H), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml,
@@ -398,21 +437,38 @@ bool sizes_ok(int H, int Hkv, int hd, int page_size, int q_stride, int n_splits)
 // early_loads: non-zero when, of all keys and values that a token reads, only those at its own
 // position can have been written by the kernel ahead on the stream (one new token per sequence):
 // the others are then requested before that kernel is known to have finished.
+//
+// work, teams (or null, 0): the list of segments described in the kernel, teams + 1 offsets and then
+// five integers a segment; the grid is then one block per (kv head, row tile, team), n_splits is the
+// room for one token's parts in the scratch (part_o: T*H*n_splits*hd floats), no token may have more
+// parts than that, and the counters are required when any token has more than one part.
+LQ_EXPORT int lq_attn_decode_work(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+                                  const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
+                                  const int* slots, float* part_o, float* part_ml, int* counters, void* out, int T,
+                                  int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
+                                  const int* work, int teams, const void* next_w, long next_bytes, int early_loads,
+                                  cudaStream_t stream) {
+    if (T <= 0) return LQ_OK;
+    if (!sizes_ok(H, Hkv, hd, page_size, q_stride, n_splits)) return LQ_BAD_SIZE;
+    if (n_splits > 1 && (!part_o || !part_ml)) return LQ_BAD_SIZE;
+    if (work && (teams < 1 || teams > 65535 || (n_splits > 1 && !counters))) return LQ_BAD_SIZE;
+#define LQ_GO(HD) return launch<HD>(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, \
+                                    part_o, part_ml, counters, out, T, H, Hkv, hd, page_size, scale, window, n_splits, \
+                                    work, teams, next_w, next_bytes, early_loads, stream)
+    if (hd <= 32) LQ_GO(32);
+    if (hd <= 64) LQ_GO(64);
+    LQ_GO(128);
+#undef LQ_GO
+}
+
 LQ_EXPORT int lq_attn_decode_next(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                                   const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
                                   const int* slots, float* part_o, float* part_ml, int* counters, void* out, int T,
                                   int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
                                   const void* next_w, long next_bytes, int early_loads, cudaStream_t stream) {
-    if (T <= 0) return LQ_OK;
-    if (!sizes_ok(H, Hkv, hd, page_size, q_stride, n_splits)) return LQ_BAD_SIZE;
-    if (n_splits > 1 && (!part_o || !part_ml)) return LQ_BAD_SIZE;
-#define LQ_GO(HD) return launch<HD>(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, \
-                                    part_o, part_ml, counters, out, T, H, Hkv, hd, page_size, scale, window, n_splits, \
-                                    next_w, next_bytes, early_loads, stream)
-    if (hd <= 32) LQ_GO(32);
-    if (hd <= 64) LQ_GO(64);
-    LQ_GO(128);
-#undef LQ_GO
+    return lq_attn_decode_work(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, part_o,
+                               part_ml, counters, out, T, H, Hkv, hd, page_size, scale, window, n_splits, nullptr, 0,
+                               next_w, next_bytes, early_loads, stream);
 }
 
 LQ_EXPORT int lq_attn_decode_merged(const void* q, int q_stride, const void* k_pages, const void* v_pages,

@@ -222,16 +222,19 @@ def _decode_setup(args, use_graphs: bool):
     from ..engine import Engine
     cfg = _config(args)
     B, C = args.batch, args.context
-    eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=B * (C + 64), max_batch=B,
-                             max_context=C + 64, use_graphs=use_graphs)
+    longest = 2 * C if args.unequal else C
+    eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=B * (longest + 64), max_batch=B,
+                             max_context=longest + 64, use_graphs=use_graphs)
     for g in eng.cache.kv_groups:
         g.k_pages.normal_()
         g.v_pages.normal_()
     slots = [eng.new_sequence() for _ in range(B)]
     start = C - args.iters - args.warmup
-    for s in slots:                       # the cache holds `start` tokens of random keys and values
-        eng.cache.reserve(s, start)
-        eng.cache.commit(s, start)
+    for i, s in enumerate(slots):         # the cache holds `start` tokens of random keys and values
+        # --unequal: lengths from a twentieth of the context to almost twice it, the same mean
+        n = start if not args.unequal or B == 1 else max(1, int(start * (0.05 + 1.9 * i / (B - 1))))
+        eng.cache.reserve(s, n)
+        eng.cache.commit(s, n)
     rng = np.random.default_rng(0)
     feed = rng.integers(0, cfg["vocab_size"], (args.iters + args.warmup, B))
 
@@ -332,6 +335,11 @@ def main(argv=None) -> int:
     ap.add_argument("--top-k", type=int, default=0)
     ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--one-block", action="store_true", help="sample: the kernel that takes a row per block")
+    ap.add_argument("--unequal", action="store_true",
+                    help="step, timeline: sequences of unequal lengths (a twentieth to twice --context, the same mean)")
+    ap.add_argument("--equal-slices", action="store_true",
+                    help="step, timeline: decode attention cuts every sequence into the same number of slices "
+                         "instead of giving every team of blocks an equal share of all keys")
     ap.add_argument("--eager", action="store_true")
     ap.add_argument("--prompt", action="store_true", help="timeline: a prompt step of --tokens tokens instead of a decode step")
     ap.add_argument("--no-graph", action="store_true", help="time single kernels launch by launch from the host")
@@ -340,6 +348,9 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
     global GRAPH
     GRAPH = not args.no_graph
+    if args.equal_slices:
+        from . import attention
+        attention.BALANCED_DECODE = False
     if args.what in ("gemm_skinny", "gemm_tc"):
         out = bench_gemm(args.what, args)
     elif args.what == "chain":

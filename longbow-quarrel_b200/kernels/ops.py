@@ -544,9 +544,13 @@ def attn_prefill_tc_status() -> int:
 def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq, slots, H: int, Hkv: int, hd: int,
                 page_size: int, scale: float, window: int | None, n_splits: int,
                 out: torch.Tensor | None = None, scratch: tuple | None = None,
-                next_w: torch.Tensor | None = None, early_loads: bool = False) -> torch.Tensor:
+                next_w: torch.Tensor | None = None, early_loads: bool = False,
+                work: torch.Tensor | None = None, teams: int = 0) -> torch.Tensor:
     """Attention of single query rows over the paged bfloat16 cache, the keys of each
-    sequence cut into n_splits slices that are merged afterwards.  next_w: the weights that the
+    sequence cut into n_splits slices that are merged afterwards.  With `work` (int32: teams + 1 offsets,
+    then (token, first tile, last tile + 1, part, parts) per segment) the grid is `teams` blocks per kv
+    head and row tile, each walking the segments between its offset and the next, and n_splits is the most
+    parts any token has; the list must cover every tile of every token once (the kernel trusts it).  next_w: the weights that the
     stream reads after this; their first bytes are asked into L2 as the blocks finish.
     early_loads: of the keys and values a row reads, only those at its own position can have been
     written by the kernel ahead on the stream (a decode step: one new token per sequence); the kernel
@@ -571,16 +575,22 @@ def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq,
         n_counters = T * Hkv * -(-(H // Hkv) // 16)
         counters = _attn_counters(q.device)
         if n_counters > counters.numel():
+            if work is not None:
+                raise KernelError("attn_decode: more (token, kv head) pairs than counters for a work list")
             counters = None          # more (token, kv head) pairs than counters: merge with the second kernel
-    fn = _fn("attn_decode", "lq_attn_decode_next", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+    if work is not None and (work.dtype != torch.int32 or not work.is_contiguous() or teams < 1
+                             or work.numel() < teams + 1 + 5 * T):
+        raise KernelError("attn_decode: the work list must be int32 with teams + 1 offsets and at least a segment per token")
+    fn = _fn("attn_decode", "lq_attn_decode_work", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                                    c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_long,
-                                                    c_int, c_void_p])
+                                                    c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int,
+                                                    c_void_p, c_long, c_int, c_void_p])
     next_p, next_n = _next(next_w, PREFETCH_BYTES_ATTN)
     _check(fn(_p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0), _p(tok_pos),
               _p(tok_seq), _p(slots), _p(part_o), _p(part_ml), _p(counters), _p(out), T, H, Hkv, hd, page_size,
-              float(scale), int(window or 0), n_splits, next_p, next_n, int(early_loads), _stream()), "attn_decode",
-           2 if n_splits > 1 and counters is None else 1, "attn_decode:one_slice" if n_splits == 1 else "attn_decode:slices")
+              float(scale), int(window or 0), n_splits, _p(work), int(teams), next_p, next_n, int(early_loads), _stream()),
+           "attn_decode", 2 if n_splits > 1 and counters is None else 1,
+           "attn_decode:teams" if work is not None else "attn_decode:one_slice" if n_splits == 1 else "attn_decode:slices")
     return out
 
 

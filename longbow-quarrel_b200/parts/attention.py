@@ -51,7 +51,8 @@ class Attention(Mixer):
         return KVNeed(self.Hkv, self.hd, self.window)
 
     def step_needs(self):
-        return attention_kernels.step_needs(self.runtime.act_dtype, self.hd)
+        return attention_kernels.step_needs(self.runtime.act_dtype, self.hd, self.H, self.Hkv, self.window,
+                                            self.runtime.device)
 
     def weights(self):
         n = self.names

@@ -430,6 +430,45 @@ def test_attn_decode(H, Hkv, hd, window, n_splits):
         _close(out.reshape(-1, H, hd), ref, _attn_tol(case, ref), BF16_ULP)
 
 
+@pytest.mark.parametrize("H,Hkv,hd,window", [(8, 2, 128, None), (6, 2, 48, None), (4, 4, 16, 37), (3, 1, 32, None),
+                                             (40, 2, 64, 100), (8, 8, 80, None)])
+@pytest.mark.parametrize("teams", [7, 12, 40, "by hand"])
+def test_attn_decode_with_a_work_list(H, Hkv, hd, window, teams):
+    """The keys of a long sequence are cut into more parts than those of a short one (the parts merged by
+    the block that finishes last); a team of blocks may also be given several segments, one after another."""
+    ops = _ops()
+    from longbow_quarrel_b200.kernels.attention import cut_decode_work, MAX_SPLITS
+    lens = [300, 1, 77, 64, 17, 1500, 33]
+    case = PagedCase(lens, Hkv, hd, torch.bfloat16, seed=3)
+    tok_seq = list(range(len(lens)))
+    tok_pos = [n - 1 for n in lens]
+    q = _rand((len(tok_seq), (H + 2 * Hkv) * hd), torch.bfloat16, 78)
+    scale = hd ** -0.5
+    ref = case.reference(q[:, :H * hd].reshape(-1, H, hd).float(), tok_seq, tok_pos, H, scale, window)
+    if teams == "by hand":
+        # three teams: whole short tokens one after another; a token shared by two teams, one of which goes on
+        first = [max(0, p - window + 1) // 16 if window and p >= window else 0 for p in tok_pos]
+        tiles = [p // 16 + 1 - f for p, f in zip(tok_pos, first)]
+        half = tiles[5] // 2
+        shared = [(5, 0, half, 0, 2), (5, half, tiles[5], 1, 2)] if half else [(5, 0, tiles[5], 0, 1)]
+        segments = [[(b, 0, tiles[b], 0, 1) for b in (0, 1, 2)], shared[:1], shared[1:] + [(b, 0, tiles[b], 0, 1) for b in (3, 4, 6)]]
+        teams, offsets = 3, [0, 3, 4, 4 + len(segments[2])]
+        work = np.asarray(offsets + [x for team in segments for seg in team for x in seg], dtype=np.int32)
+    else:
+        work = cut_decode_work(tok_pos, int(window or 0), teams)
+        if teams > len(lens) and not window:
+            assert work[teams + 1:].reshape(-1, 5)[:work[teams], 4].max() > 1      # the long token has several parts
+    for early in (False, True):
+        out = ops.attn_decode(q, case.k_pages, case.v_pages, case.table, _ints(tok_pos), _ints(tok_seq), case.slots,
+                              H, Hkv, hd, case.page_size, scale, window, min(MAX_SPLITS, teams), early_loads=early,
+                              work=_ints(work.tolist()), teams=teams)
+        _close(out.reshape(-1, H, hd), ref, _attn_tol(case, ref), BF16_ULP)
+        again = ops.attn_decode(q, case.k_pages, case.v_pages, case.table, _ints(tok_pos), _ints(tok_seq), case.slots,
+                                H, Hkv, hd, case.page_size, scale, window, min(MAX_SPLITS, teams), early_loads=early,
+                                work=_ints(work.tolist()), teams=teams)
+        assert torch.equal(out, again)                       # the counters are back at zero; the merge has a fixed order
+
+
 @pytest.mark.parametrize("far_key", [0, 5, 250, 511, 700])
 def test_attn_decode_finds_a_far_key(far_key):
     """One key among hundreds is made to stand out; the output must be its value."""
@@ -449,9 +488,15 @@ def test_attn_decode_finds_a_far_key(far_key):
         case.k_pages[page, kvh, far_key % 64] = key
         case.k[0][far_key, kvh] = key
     scale = 1.0
-    for n_splits in (1, 4):
-        out = ops.attn_decode(q, case.k_pages, case.v_pages, case.table, _ints([n - 1]), _ints([0]), case.slots,
-                              H, Hkv, hd, 64, scale, None, n_splits).reshape(H, hd)
+    from longbow_quarrel_b200.kernels.attention import cut_decode_work
+    for n_splits in (1, 4, "teams"):
+        if n_splits == "teams":
+            out = ops.attn_decode(q, case.k_pages, case.v_pages, case.table, _ints([n - 1]), _ints([0]), case.slots,
+                                  H, Hkv, hd, 64, scale, None, 5, work=_ints(cut_decode_work([n - 1], 0, 5).tolist()),
+                                  teams=5).reshape(H, hd)
+        else:
+            out = ops.attn_decode(q, case.k_pages, case.v_pages, case.table, _ints([n - 1]), _ints([0]), case.slots,
+                                  H, Hkv, hd, 64, scale, None, n_splits).reshape(H, hd)
         for kvh in range(Hkv):
             _close(out[kvh * G], case.v[0][far_key, kvh], 2e-2)
 

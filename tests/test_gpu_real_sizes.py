@@ -109,7 +109,7 @@ def test_real_layer_sizes_in_every_cut(tmp_path_factory, tmp_path, shape, dtype)
     counts = kernel_counts(out)
     if dtype == "bfloat16":
         for name in ("gemm_tc_qkv", "attn_prefill_tc", "gemm_skinny_qkv", "attn_decode", "gemm_tc", "gemm_skinny",
-                     "gemm_skinny:rows8:norm_in", "attn_decode:slices"):
+                     "gemm_skinny:rows8:norm_in", "attn_decode:teams"):
             assert counts.get(name, 0) > 0, (name, counts)
         assert "attention" not in counts and "linear" not in counts, counts       # no plain kernel took a product
     else:
@@ -160,5 +160,5 @@ def test_wide_batches_at_real_layer_sizes(tmp_path_factory, tmp_path, dtype):
     if dtype == "bfloat16":
         counts = kernel_counts(out)
         for name in ("gemm_skinny:rows16", "gemm_skinny_qkv:rows16", "gemm_tc:split_k", "gemm_tc_qkv:split_k",
-                     "attn_decode:one_slice", "attn_decode:slices", "attn_prefill_tc"):
+                     "attn_decode:teams", "attn_prefill_tc"):
             assert counts.get(name, 0) > 0, (name, counts)

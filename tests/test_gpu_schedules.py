@@ -61,7 +61,7 @@ def test_prompts_in_portions_mixed_steps_and_wide_batches(tmp_path, dtype):
     if dtype == "bfloat16":
         counts = kernel_counts(out)
         for name in ("attn_prefill_tc", "gemm_tc_qkv", "gemm_skinny_qkv:rows16", "gemm_skinny:rows16", "gemm_tc:few_rows",
-                     "gemm_tc_qkv:few_rows", "attn_decode:one_slice", "attn_decode:slices"):
+                     "gemm_tc_qkv:few_rows", "attn_decode:teams"):
             assert counts.get(name, 0) > 0, (name, counts)
 
 

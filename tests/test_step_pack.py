@@ -95,3 +95,71 @@ def test_parts_name_the_step_arrays_they_need():
     assert _part(flat, info, "twice_past").tolist() == [10, 18]
     with pytest.raises(StepError, match="named 'tokens'"):
         pack_step([(0, [1])], None, [0], {"tokens": lambda st: [0]})
+
+
+def _check_decode_work(positions, window, teams):
+    """Every key tile of every token lies in exactly one segment, the parts of a token are numbered in
+    order, every team has at most one segment and the longest come first.  Returns the segments' lengths."""
+    from longbow_quarrel_b200.kernels.attention import cut_decode_work, decode_work_size, MAX_SPLITS, MIN_PART_TILES
+    work = cut_decode_work(positions, window, teams)
+    assert work.dtype == np.int32 and len(work) == decode_work_size(len(positions), teams)
+    offsets, n = work[:teams + 1], int(work[teams])
+    assert offsets.tolist() == [min(i, n) for i in range(teams + 1)] and len(positions) <= n <= teams
+    segments = work[teams + 1:].reshape(-1, 5)[:n]
+    pos = np.asarray(positions)
+    first = np.where((window > 0) & (pos >= window), pos - window + 1, 0) // 16
+    tiles = pos // 16 + 1 - first
+    seen = {b: [] for b in range(len(pos))}
+    for tok, lo, hi, part, parts in segments.tolist():
+        seen[tok].append((lo, hi, part, parts))
+    for b, segs in seen.items():
+        segs.sort()
+        assert segs[0][0] == 0 and segs[-1][1] == tiles[b] and len(segs) <= MAX_SPLITS, (b, segs)
+        for i, (lo, hi, part, parts) in enumerate(segs):
+            assert lo < hi and part == i and parts == len(segs) and (i == 0 or segs[i - 1][1] == lo), (b, segs)
+            assert parts == 1 or hi - lo >= MIN_PART_TILES, (b, segs)
+    lengths = (segments[:, 2] - segments[:, 1]).tolist()
+    assert lengths == sorted(lengths, reverse=True)
+    return lengths
+
+
+def test_decode_work_covers_every_tile_once():
+    rng = np.random.default_rng(5)
+    for _ in range(1500):
+        B = int(rng.integers(1, 80))
+        teams = B + int(rng.integers(0, 150))
+        window = int(rng.choice([0, 0, 7, 64, 1000]))
+        _check_decode_work(rng.integers(0, int(rng.choice([5, 60, 700, 9000])), size=B), window, teams)
+    _check_decode_work([0], 0, 1)
+    assert len(_check_decode_work([100000], 0, 148)) == 32       # one token has no more parts than the merge takes
+    with pytest.raises(ValueError, match="at least as many teams"):
+        _check_decode_work([5, 6, 7], 0, 2)
+
+
+def test_decode_work_gives_long_sequences_more_parts():
+    # unequal sequences (7 ... 250 tiles) and 18 teams: the longest part is far shorter than half the
+    # longest sequence, which the same two slices for everyone would leave
+    lengths = _check_decode_work([int(2048 * (0.05 + 1.9 * i / 7)) for i in range(8)], 0, 18)
+    assert len(lengths) == 18 and lengths[0] <= 76, lengths
+    # equal sequences: the same number of slices each, as many as fit
+    assert _check_decode_work([2047] * 8, 0, 18) == [64] * 16
+    assert _check_decode_work([1199] * 16, 0, 18) == [75] * 16
+    # short sequences are not cut at all
+    assert _check_decode_work([40] * 8, 0, 18) == [3] * 8
+    # one sequence alone is shared by all teams
+    lengths = _check_decode_work([4095], 0, 18)
+    assert len(lengths) == 18 and lengths[0] - lengths[-1] <= 1, lengths
+    # more tokens than teams that run at a time: one part each, the longest first
+    assert _check_decode_work([16 * i for i in range(64)], 0, 64) == list(range(64, 0, -1))
+
+
+def test_attention_asks_for_decode_work_by_its_head_counts():
+    import torch
+    from longbow_quarrel_b200.kernels.attention import decode_work_name
+    needs = step_needs(torch.bfloat16, 128, 32, 8, None, "cpu")
+    assert list(needs) == ["query_blocks128", decode_work_name(32, 8, None)]
+    assert list(step_needs(torch.float32, 128, 32, 8, None, "cpu")) == []
+    assert list(step_needs(torch.bfloat16, 40, 8, 8, None, "cpu")) == []
+    # in a step with prompts the decode list is empty
+    flat, info = pack_step([(0, [1, 2]), (1, [2])], None, [5, 9], {"w": needs[decode_work_name(32, 8, None)]})
+    assert len(_part(flat, info, "w")) == 0
