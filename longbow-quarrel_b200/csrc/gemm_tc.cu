@@ -61,9 +61,12 @@ struct Smem {
 
 // ------------------------------------------------------------------ epilogue of 32 columns of one row
 // n_lim: the tile's columns end there (at most N); columns from n_lim on are not stored.
+// pre (EPI_RESID, or null): the residual of these 32 columns, loaded beforehand (only asked for whole chunks
+// of a matrix whose rows are 16-byte aligned, the case in which this function would load float4s itself).
 template <int EPI>
 __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], void* Cout,
-                                            const float* residual, int m, int n, int M, int N, int n_lim) {
+                                            const float* residual, int m, int n, int M, int N, int n_lim,
+                                            const float4* pre = nullptr) {
     if (m >= M || n >= n_lim) return;
     if (EPI == EPI_SWIGLU) {
         // 32 columns = [8 gate, 8 up, 8 gate, 8 up] -> 16 outputs at column n / 2 of [M, N / 2].
@@ -113,7 +116,7 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], void* Cout,
                 float4 v = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
                                        __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
                 if (EPI == EPI_RESID) {
-                    float4 q = reinterpret_cast<const float4*>(res)[i];
+                    float4 q = pre ? pre[i] : reinterpret_cast<const float4*>(res)[i];
                     v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
                 }
                 reinterpret_cast<float4*>(dst)[i] = v;
@@ -279,11 +282,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
             void* dst = splits > 1 ? (void*)((float*)Cout + (size_t)range * M * N) : Cout;
             const uint32_t acc = t & 1;
+            const int m = m0 + quarter * 32 + lane;
+            const int n_lim = n0 + BN < N ? n0 + BN : N;
+            // The residual that the tile is added to is known before the products are done: its first 32 columns
+            // are requested now and each further chunk while the one before it is added and stored.
+            float4 pre[8];
+            auto fetch = [&](int c) -> bool {
+                if constexpr (EPI == EPI_RESID) {
+                    const int n = n0 + c * 32;
+                    if (m >= M || n + 32 > n_lim || (N & 3)) return false;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) pre[i] = reinterpret_cast<const float4*>(residual + (size_t)m * N + n)[i];
+                    return true;
+                } else {
+                    return false;
+                }
+            };
+            bool fetched = fetch(0);
             if (!mbar_wait(smem_u32(&sm.acc_full[acc]), (t >> 1) & 1)) { give_up(4); ok = false; break; }
             fence_after();
-            const int m = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
-            const int n_lim = n0 + BN < N ? n0 + BN : N;
             if (EPI == EPI_QKV) {
                 // The tile holds whole heads (BN is a multiple of hd); a head's halves are hd / 2 = 32 or 64 columns.
                 const int hd = qkv.hd, half = hd >> 1;
@@ -310,7 +328,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     uint32_t r[32];
                     ld32(taddr + c * 32, r);
                     wait_ld();
-                    store_chunk<EPI>(r, dst, residual, m, n0 + c * 32, M, N, n_lim);
+                    if (EPI == EPI_RESID) {
+                        float4 now[8];
+                        const bool have = fetched;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) now[i] = pre[i];
+                        fetched = c + 1 < (BN + 31) / 32 && fetch(c + 1);
+                        store_chunk<EPI>(r, dst, residual, m, n0 + c * 32, M, N, n_lim, have ? now : nullptr);
+                    } else {
+                        store_chunk<EPI>(r, dst, residual, m, n0 + c * 32, M, N, n_lim);
+                    }
                 }
             }
             fence_before();
