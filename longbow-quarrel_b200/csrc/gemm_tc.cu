@@ -7,7 +7,9 @@
 //   warp 1      one lane issues tcgen05.mma (M 128, N BN, K 16; four per stage) into one of
 //               two accumulators in tensor memory, and frees a stage with tcgen05.commit;
 //   warps 2..5  read a finished accumulator with tcgen05.ld (each thread one row) and store
-//               it, while the next tile's products already run into the other accumulator.
+//               it, while the next tile's products already run into the other accumulator; with
+//               many rows the stores go through shared memory and leave as TMA stores of whole
+//               lines (for the residual as TMA adds into it).
 // Stages and accumulators are handed over through mbarriers.  Every wait is bounded: after
 // about two seconds a role records a code in the status word, leaves its loop, and the
 // block still waits (bounded) for its copies in flight, frees its tensor memory and ends.
@@ -48,10 +50,13 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 // AROWS: rows of x that a stage holds, 128 or (for at most 64 rows of x) 64.  With 64 the products still
 // read 128 rows: the upper 64 are whatever follows in shared memory, and give rows of the accumulator
 // that are never stored -- the stage is 8 KB smaller, so more stages of W are on their way.
-template <int BN, int STAGES, int AROWS>
+// STAGED: the epilogue warps have two buffers of 32 rows x 128 bytes each, from which their stores go out as
+// whole lines (TMA); without them a thread stores its own row, 16 bytes at a time.
+template <int BN, int STAGES, int AROWS, bool STAGED>
 struct Smem {
     alignas(1024) uint8_t a[STAGES][AROWS * BK * 2];
     alignas(1024) uint8_t b[STAGES][BN * BK * 2];
+    alignas(1024) uint8_t stage[STAGED ? 4 : 1][STAGED ? 2 : 1][STAGED ? 4096 : 16];
     alignas(8) uint64_t full[STAGES];
     uint64_t empty[STAGES];
     uint64_t acc_full[2];
@@ -184,12 +189,25 @@ __device__ __forceinline__ void store_qkv_pair(const uint32_t (&a)[32], const ui
 }
 
 // ------------------------------------------------------------------ the kernel
+// Whether the epilogue of a kernel with these parameters can go through shared memory and TMA stores:
+// many rows (whole 128-row tiles of x in a stage), tiles of 128 or 256 columns, and not the q/k/v epilogue,
+// whose rows go to cache pages of their own.
+template <int BN, int EPI, int AROWS> struct StagedEpilogue {
+    static constexpr bool value = AROWS == BM && (BN == 128 || BN == 256) && EPI != EPI_QKV;
+};
+
+// 16-byte piece `piece` (0..7) of row `row` in a buffer of 128-byte rows with the 128-byte swizzle of the tensor maps.
+__device__ __forceinline__ uint4* staged_at(uint8_t* buf, int row, int piece) {
+    return reinterpret_cast<uint4*>(buf + row * 128 + ((piece ^ (row & 7)) << 4));
+}
+
 template <int BN, int STAGES, int EPI, int AROWS>
 __global__ void __launch_bounds__(N_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               void* Cout, const float* residual, int M, int N, int K, int splits, const QkvArgs qkv) {
+               const __grid_constant__ CUtensorMap map_c, int staged, void* Cout, const float* residual, int M, int N, int K, int splits, const QkvArgs qkv) {
     extern __shared__ uint8_t smem_raw[];
-    using S = Smem<BN, STAGES, AROWS>;
+    constexpr bool STAGED = StagedEpilogue<BN, EPI, AROWS>::value;
+    using S = Smem<BN, STAGES, AROWS, STAGED>;
     S& sm = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
@@ -207,6 +225,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         mbar_fence_init();
         prefetch_map(&map_a);
         prefetch_map(&map_b);
+        if (STAGED && staged) prefetch_map(&map_c);
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(&sm.tmem_base), TMEM_COLS);
@@ -276,6 +295,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ---------------------------------------------------------------- epilogue (warps 2..5)
         const int quarter = warp & 3;                     // the 32 lanes of tensor memory this warp may read
         uint32_t t = 0;
+        int stage_buf = 0;
         bool ok = true;
         for (int piece = blockIdx.x; piece < total && ok; piece += gridDim.x, ++t) {
             const int tile = piece / splits, range = piece % splits;
@@ -298,7 +318,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     return false;
                 }
             };
-            bool fetched = fetch(0);
+            bool fetched = !(STAGED && staged) && fetch(0);
             if (!mbar_wait(smem_u32(&sm.acc_full[acc]), (t >> 1) & 1)) { give_up(4); ok = false; break; }
             fence_after();
             const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
@@ -322,6 +342,59 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                            rotate ? qkv.sin_t + (size_t)pos * half : nullptr, j0, half);
                     }
                 }
+            } else if (STAGED && staged) {
+                // Through shared memory: a thread puts its row's 128 bytes into the warp's buffer (swizzled, so the
+                // 32 rows do not collide), and one TMA store (for the residual: one TMA add into it, which reads
+                // nothing here) sends the 32 rows as whole lines.  Two buffers per warp: one fills while the other
+                // drains.  Thread-per-row stores of 16 bytes touch 32 lines per instruction: a 128 x 256 float32 tile
+                // with its residual then took 16 us, against 26 us for the tile's products at K = 4096.
+                constexpr int COLS = (EPI == EPI_F32 || EPI == EPI_RESID) ? 32 : (EPI == EPI_BF16 ? 64 : 128);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN && n0 + c0 < N; c0 += COLS) {
+                    uint8_t* buf = sm.stage[quarter][stage_buf];
+                    if (lane == 0) bulk_wait_read<1>();            // the store before the last has read this buffer
+                    __syncwarp();
+#pragma unroll
+                    for (int sub = 0; sub < COLS / 32; ++sub) {
+                        uint32_t r[32];
+                        ld32(taddr + c0 + sub * 32, r);
+                        wait_ld();
+                        if (EPI == EPI_F32 || EPI == EPI_RESID) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                *staged_at(buf, lane, i) = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+                        } else if (EPI == EPI_BF16) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                *staged_at(buf, lane, sub * 4 + i) =
+                                    make_uint4(pack2(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
+                                               pack2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
+                                               pack2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
+                                               pack2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7])));
+                        } else {
+                            // 32 columns = [8 gate, 8 up, 8 gate, 8 up] -> 16 outputs
+                            float o[16];
+#pragma unroll
+                            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {
+                                    const float gt = __uint_as_float(r[h * 16 + i]), up = __uint_as_float(r[h * 16 + 8 + i]);
+                                    o[h * 8 + i] = up * (gt / (1.0f + __expf(-gt)));
+                                }
+                            *staged_at(buf, lane, sub * 2) = make_uint4(pack2(o[0], o[1]), pack2(o[2], o[3]), pack2(o[4], o[5]), pack2(o[6], o[7]));
+                            *staged_at(buf, lane, sub * 2 + 1) = make_uint4(pack2(o[8], o[9]), pack2(o[10], o[11]), pack2(o[12], o[13]), pack2(o[14], o[15]));
+                        }
+                    }
+                    fence_async_shared();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int x = EPI == EPI_SWIGLU ? (n0 + c0) >> 1 : n0 + c0, y = m0 + quarter * 32;
+                        if (EPI == EPI_RESID) tma_add_2d(&map_c, smem_u32(buf), x, y);
+                        else tma_store_2d(&map_c, smem_u32(buf), x, y);
+                        bulk_commit();
+                    }
+                    stage_buf ^= 1;
+                }
             } else {
 #pragma unroll 1
                 for (int c = 0; c < (BN + 31) / 32; ++c) {      // a last half chunk reads columns that are not stored
@@ -344,6 +417,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sm.acc_empty[acc]));
         }
+        if (STAGED && staged && lane == 0) bulk_wait<0>();      // this warp's stores are done before the block ends
     }
     fence_before();
     __syncthreads();
@@ -449,7 +523,8 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) 
 template <int BN, int STAGES, int EPI, int AROWS>
 int launch_epi(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const float* residual, int M, int N, int K,
                int n_sms, int splits, const QkvArgs& qkv, cudaStream_t stream) {
-    constexpr size_t smem = sizeof(Smem<BN, STAGES, AROWS>) + 1024;
+    constexpr bool STAGED = StagedEpilogue<BN, EPI, AROWS>::value;
+    constexpr size_t smem = sizeof(Smem<BN, STAGES, AROWS, STAGED>) + 1024;
     static_assert(smem <= 232448, "more shared memory than a block may have");
     static bool configured = false;
     if (!configured) {
@@ -459,8 +534,18 @@ int launch_epi(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const floa
     }
     int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * splits;
     int grid = tiles < n_sms ? tiles : n_sms;
-    return launch_pdl(gemm_tc_kernel<BN, STAGES, EPI, AROWS>, dim3(grid), dim3(N_THREADS), smem, stream, ma, mb, C, residual, M, N, K,
-                      splits, qkv);
+    // The epilogue goes through shared memory and TMA stores when the output's rows are 16-byte aligned
+    // (and, for the residual, when the sums are added in place).
+    CUtensorMap mc{};
+    int staged = 0;
+    if (STAGED) {
+        const int elt = (EPI == EPI_F32 || EPI == EPI_RESID) ? 4 : 2;
+        const long cols = EPI == EPI_SWIGLU ? N / 2 : N;
+        if (splits == 1 && !((uintptr_t)C & 15) && (cols * elt) % 16 == 0 && (EPI != EPI_RESID || C == (void*)residual))
+            staged = make_map_out(&mc, C, elt, M, cols, cols, 32) == LQ_OK;
+    }
+    return launch_pdl(gemm_tc_kernel<BN, STAGES, EPI, AROWS>, dim3(grid), dim3(N_THREADS), smem, stream, ma, mb, mc, staged, C, residual,
+                      M, N, K, splits, qkv);
 }
 
 // ALL: every epilogue; otherwise only the two that products with many columns have (SwiGLU, float32 store).

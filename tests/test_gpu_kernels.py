@@ -319,7 +319,7 @@ def test_gemm_skinny_qkv_finishes_a_folded_norm():
 
 
 @pytest.mark.parametrize("M", [65, 128, 300, 1111])
-@pytest.mark.parametrize("N,K", [(16, 64), (250, 80), (1000, 200), (4104, 1024), (520, 4096)])
+@pytest.mark.parametrize("N,K", [(16, 64), (250, 80), (1000, 200), (1004, 136), (4104, 1024), (520, 4096)])
 def test_gemm_tc(M, N, K):
     ops = _ops()
     a, w = _rand((M, K), torch.bfloat16, 20), _rand((N, K), torch.bfloat16, 21)
