@@ -26,13 +26,7 @@
 //
 // Reference counterpart: the per-row linear_f16 kernels and the library GEMM of
 // internal/device/metal.go:886-964; its CUDA path calls cublasSgemmEx (internal/device/cuda.go:293-318).
-#include "tcgen05.cuh"
-
-#define EPI_BF16 0
-#define EPI_F32 1
-#define EPI_RESID 2
-#define EPI_SWIGLU 3
-#define EPI_QKV 4       // q, k, v rows: rotate q and k, store k and v into the cache pages
+#include "gemm_tc_epilogue.cuh"
 
 namespace {
 
@@ -41,11 +35,6 @@ constexpr int BK = 64;                 // 64 bf16 = 128 bytes: one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int N_THREADS = 192;
 using namespace tc;       // mbarriers with bounded waits, TMA, tcgen05 wrappers, descriptors, status word
-
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
 
 // AROWS: rows of x that a stage holds, 128 or (for at most 64 rows of x) 64.  With 64 the products still
 // read 128 rows: the upper 64 are whatever follows in shared memory, and give rows of the accumulator
@@ -56,7 +45,7 @@ template <int BN, int STAGES, int AROWS, bool STAGED>
 struct Smem {
     alignas(1024) uint8_t a[STAGES][AROWS * BK * 2];
     alignas(1024) uint8_t b[STAGES][BN * BK * 2];
-    alignas(1024) uint8_t stage[STAGED ? 4 : 1][STAGED ? 2 : 1][STAGED ? 4096 : 16];
+    alignas(1024) uint8_t stage[STAGED ? 4 : 1][STAGED ? 2 * STAGE_BUF_BYTES : 16];
     alignas(8) uint64_t full[STAGES];
     uint64_t empty[STAGES];
     uint64_t acc_full[2];
@@ -134,60 +123,6 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], void* Cout,
     }
 }
 
-// What the q/k/v epilogue needs beside the product: where each row stands and where its cache page is.
-// W holds H query heads, then Hkv key heads, then Hkv value heads, hd rows each.
-struct QkvArgs {
-    const float* cos_t;       // [positions, hd / 2] or null (no rotation)
-    const float* sin_t;
-    const int* tok_pos;
-    const int* tok_seq;
-    const int* slots;
-    const int* page_table;
-    __nv_bfloat16* k_pages;
-    __nv_bfloat16* v_pages;
-    int pt_stride, H, Hkv, hd, page_size;
-};
-
-// Where elements j .. of head `head` of row m go: q_out, or the row's place in a cache page.
-__device__ __forceinline__ __nv_bfloat16* qkv_dest(const QkvArgs& q, __nv_bfloat16* q_out, int m, int head, int pos) {
-    if (head < q.H) return q_out + ((size_t)m * q.H + head) * q.hd;
-    const int kvh = (head - q.H) % q.Hkv;
-    __nv_bfloat16* pages = head < q.H + q.Hkv ? q.k_pages : q.v_pages;
-    const int page = q.page_table[(size_t)q.slots[q.tok_seq[m]] * q.pt_stride + pos / q.page_size];
-    return pages + (((size_t)page * q.Hkv + kvh) * q.page_size + pos % q.page_size) * q.hd;
-}
-
-// 32 elements j0 .. j0+31 of a head's first half (a) and their partners in the second half (b) of one row:
-// rotated (heads of q and k, when there are tables) and stored at dst + j0 and dst + half + j0.
-__device__ __forceinline__ void store_qkv_pair(const uint32_t (&a)[32], const uint32_t (&b)[32], __nv_bfloat16* dst,
-                                               const float* cos_row, const float* sin_row, int j0, int half) {
-    uint4* lo = reinterpret_cast<uint4*>(dst + j0);
-    uint4* hi = reinterpret_cast<uint4*>(dst + half + j0);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float x0[8], x1[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) { x0[e] = __uint_as_float(a[8 * i + e]); x1[e] = __uint_as_float(b[8 * i + e]); }
-        if (cos_row) {
-#pragma unroll
-            for (int e4 = 0; e4 < 2; ++e4) {
-                const float4 c = reinterpret_cast<const float4*>(cos_row + j0)[2 * i + e4];
-                const float4 sn = reinterpret_cast<const float4*>(sin_row + j0)[2 * i + e4];
-                const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float y0 = x0[4 * e4 + e] * cc[e] - x1[4 * e4 + e] * ss[e];
-                    const float y1 = x0[4 * e4 + e] * ss[e] + x1[4 * e4 + e] * cc[e];
-                    x0[4 * e4 + e] = y0;
-                    x1[4 * e4 + e] = y1;
-                }
-            }
-        }
-        lo[i] = make_uint4(pack2(x0[0], x0[1]), pack2(x0[2], x0[3]), pack2(x0[4], x0[5]), pack2(x0[6], x0[7]));
-        hi[i] = make_uint4(pack2(x1[0], x1[1]), pack2(x1[2], x1[3]), pack2(x1[4], x1[5]), pack2(x1[6], x1[7]));
-    }
-}
-
 // ------------------------------------------------------------------ the kernel
 // Whether the epilogue of a kernel with these parameters can go through shared memory and TMA stores:
 // many rows (whole 128-row tiles of x in a stage), tiles of 128 or 256 columns, and not the q/k/v epilogue,
@@ -195,11 +130,6 @@ __device__ __forceinline__ void store_qkv_pair(const uint32_t (&a)[32], const ui
 template <int BN, int EPI, int AROWS> struct StagedEpilogue {
     static constexpr bool value = AROWS == BM && (BN == 128 || BN == 256) && EPI != EPI_QKV;
 };
-
-// 16-byte piece `piece` (0..7) of row `row` in a buffer of 128-byte rows with the 128-byte swizzle of the tensor maps.
-__device__ __forceinline__ uint4* staged_at(uint8_t* buf, int row, int piece) {
-    return reinterpret_cast<uint4*>(buf + row * 128 + ((piece ^ (row & 7)) << 4));
-}
 
 template <int BN, int STAGES, int EPI, int AROWS>
 __global__ void __launch_bounds__(N_THREADS, 1)
@@ -323,78 +253,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             fence_after();
             const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
             if (EPI == EPI_QKV) {
-                // The tile holds whole heads (BN is a multiple of hd); a head's halves are hd / 2 = 32 or 64 columns.
-                const int hd = qkv.hd, half = hd >> 1;
-                const int pos = m < M ? qkv.tok_pos[m] : 0;
-#pragma unroll 1
-                for (int col = 0; col < BN && n0 + col < N; col += hd) {
-                    const int head = (n0 + col) / hd;
-                    const bool rotate = qkv.cos_t != nullptr && head < qkv.H + qkv.Hkv;
-                    __nv_bfloat16* row = m < M ? qkv_dest(qkv, (__nv_bfloat16*)Cout, m, head, pos) : nullptr;
-#pragma unroll 1
-                    for (int j0 = 0; j0 < half; j0 += 32) {
-                        uint32_t a[32], b[32];
-                        ld32(taddr + col + j0, a);
-                        ld32(taddr + col + half + j0, b);
-                        wait_ld();
-                        if (m < M)
-                            store_qkv_pair(a, b, row, rotate ? qkv.cos_t + (size_t)pos * half : nullptr,
-                                           rotate ? qkv.sin_t + (size_t)pos * half : nullptr, j0, half);
-                    }
-                }
+                qkv_epilogue(taddr, BN, qkv, (__nv_bfloat16*)Cout, m, M, n0, N);
             } else if (STAGED && staged) {
-                // Through shared memory: a thread puts its row's 128 bytes into the warp's buffer (swizzled, so the
-                // 32 rows do not collide), and one TMA store (for the residual: one TMA add into it, which reads
-                // nothing here) sends the 32 rows as whole lines.  Two buffers per warp: one fills while the other
-                // drains.  Thread-per-row stores of 16 bytes touch 32 lines per instruction: a 128 x 256 float32 tile
-                // with its residual then took 16 us, against 26 us for the tile's products at K = 4096.
-                constexpr int COLS = (EPI == EPI_F32 || EPI == EPI_RESID) ? 32 : (EPI == EPI_BF16 ? 64 : 128);
-#pragma unroll 1
-                for (int c0 = 0; c0 < BN && n0 + c0 < N; c0 += COLS) {
-                    uint8_t* buf = sm.stage[quarter][stage_buf];
-                    if (lane == 0) bulk_wait_read<1>();            // the store before the last has read this buffer
-                    __syncwarp();
-#pragma unroll
-                    for (int sub = 0; sub < COLS / 32; ++sub) {
-                        uint32_t r[32];
-                        ld32(taddr + c0 + sub * 32, r);
-                        wait_ld();
-                        if (EPI == EPI_F32 || EPI == EPI_RESID) {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                *staged_at(buf, lane, i) = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
-                        } else if (EPI == EPI_BF16) {
-#pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                *staged_at(buf, lane, sub * 4 + i) =
-                                    make_uint4(pack2(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
-                                               pack2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
-                                               pack2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
-                                               pack2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7])));
-                        } else {
-                            // 32 columns = [8 gate, 8 up, 8 gate, 8 up] -> 16 outputs
-                            float o[16];
-#pragma unroll
-                            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) {
-                                    const float gt = __uint_as_float(r[h * 16 + i]), up = __uint_as_float(r[h * 16 + 8 + i]);
-                                    o[h * 8 + i] = up * (gt / (1.0f + __expf(-gt)));
-                                }
-                            *staged_at(buf, lane, sub * 2) = make_uint4(pack2(o[0], o[1]), pack2(o[2], o[3]), pack2(o[4], o[5]), pack2(o[6], o[7]));
-                            *staged_at(buf, lane, sub * 2 + 1) = make_uint4(pack2(o[8], o[9]), pack2(o[10], o[11]), pack2(o[12], o[13]), pack2(o[14], o[15]));
-                        }
-                    }
-                    fence_async_shared();
-                    __syncwarp();
-                    if (lane == 0) {
-                        const int x = EPI == EPI_SWIGLU ? (n0 + c0) >> 1 : n0 + c0, y = m0 + quarter * 32;
-                        if (EPI == EPI_RESID) tma_add_2d(&map_c, smem_u32(buf), x, y);
-                        else tma_store_2d(&map_c, smem_u32(buf), x, y);
-                        bulk_commit();
-                    }
-                    stage_buf ^= 1;
-                }
+                if constexpr (STAGED)
+                    staged_epilogue<EPI>(taddr, BN, sm.stage[quarter], stage_buf, &map_c, m0 + quarter * 32, n0, N, lane);
             } else {
 #pragma unroll 1
                 for (int c = 0; c < (BN + 31) / 32; ++c) {      // a last half chunk reads columns that are not stored
@@ -538,12 +400,8 @@ int launch_epi(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const floa
     // (and, for the residual, when the sums are added in place).
     CUtensorMap mc{};
     int staged = 0;
-    if (STAGED) {
-        const int elt = (EPI == EPI_F32 || EPI == EPI_RESID) ? 4 : 2;
-        const long cols = EPI == EPI_SWIGLU ? N / 2 : N;
-        if (splits == 1 && !((uintptr_t)C & 15) && (cols * elt) % 16 == 0 && (EPI != EPI_RESID || C == (void*)residual))
-            staged = make_map_out(&mc, C, elt, M, cols, cols, 32) == LQ_OK;
-    }
+    if constexpr (STAGED)
+        staged = splits == 1 && staged_map<EPI>(&mc, C, residual, M, EPI == EPI_SWIGLU ? N / 2 : N);
     return launch_pdl(gemm_tc_kernel<BN, STAGES, EPI, AROWS>, dim3(grid), dim3(N_THREADS), smem, stream, ma, mb, mc, staged, C, residual,
                       M, N, K, splits, qkv);
 }

@@ -340,6 +340,8 @@ def main(argv=None) -> int:
     ap.add_argument("--equal-slices", action="store_true",
                     help="step, timeline: decode attention cuts every sequence into the same number of slices "
                          "instead of giving every team of blocks an equal share of all keys")
+    ap.add_argument("--single-sm", action="store_true",
+                    help="gemm_tc, prefill: every tile on one SM (no products on pairs of SMs)")
     ap.add_argument("--eager", action="store_true")
     ap.add_argument("--prompt", action="store_true", help="timeline: a prompt step of --tokens tokens instead of a decode step")
     ap.add_argument("--no-graph", action="store_true", help="time single kernels launch by launch from the host")
@@ -348,6 +350,9 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
     global GRAPH
     GRAPH = not args.no_graph
+    if args.single_sm:
+        from . import ops
+        ops.USE_PAIRS = False
     if args.equal_slices:
         from . import attention
         attention.BALANCED_DECODE = False

@@ -88,6 +88,8 @@ _declared: set[tuple[str, str]] = set()
 # Libraries whose kernels wait on barriers with a time limit, and what their status codes mean.
 _WATCHED = {"gemm_tc": {1: "the TMA producer waited for a free stage", 2: "the product issuer waited for a free accumulator",
                         3: "the product issuer waited for a stage's copies", 4: "the epilogue waited for an accumulator"},
+            "gemm_pair": {1: "a TMA producer waited for a free stage", 2: "the product issuer waited for a free accumulator",
+                          3: "the product issuer waited for a stage's copies", 4: "an epilogue waited for an accumulator"},
             "attn_prefill_tc": {}}
 _status_words: dict[str, object] = {}
 
@@ -426,6 +428,20 @@ def gemm_skinny_qkv(a, w: torch.Tensor, cos, sin, tok_pos, tok_seq, slots, page_
     return out
 
 
+USE_PAIRS = True        # many rows: products on pairs of SMs (tcgen05 cta_group::2) where gemm_pair takes the sizes
+
+
+def gemm_pair_takes(M: int, N: int, K: int) -> bool:
+    """Whether the product of these sizes runs on pairs of SMs (256 x 256 tiles fill the pairs at least once)."""
+    return USE_PAIRS and bool(_fn("gemm_pair", "lq_gemm_pair_takes", [c_int, c_int, c_int])(M, N, K))
+
+
+def gemm_pair_status() -> int:
+    fn = build.load("gemm_pair").lq_gemm_pair_status
+    fn.restype = c_int
+    return int(fn())
+
+
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, epi: int, residual: torch.Tensor | None = None,
             out: torch.Tensor | None = None) -> torch.Tensor:
     """a [M, K] . w [N, K]^T on the tcgen05 tensor cores (TMA-fed, float32 accumulation in
@@ -446,6 +462,13 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, epi: int, residual: torch.Tensor |
     elif out is None:
         shape = (M, N // 2) if epi == EPI_SWIGLU else (M, N)
         out = torch.empty(shape, dtype=torch.float32 if epi == EPI_F32 else torch.bfloat16, device=a.device)
+    out_cols = N // 2 if epi == EPI_SWIGLU else N
+    if (gemm_pair_takes(M, N, K) and out.is_contiguous() and out.data_ptr() % 16 == 0
+            and (out_cols * out.element_size()) % 16 == 0 and a.is_contiguous() and w.is_contiguous()):
+        # Many rows: tiles of 256 x 256 on pairs of SMs, the output leaving by TMA.
+        fn = _fn("gemm_pair", "lq_gemm_pair", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+        _check(fn(_p(a), _p(w), _p(out), _p(residual), M, N, K, epi, _stream()), "gemm_pair")
+        return out
     # Few tiles (few rows, narrow weight): the kernel cuts the contraction into ranges and adds them afterwards.
     splits = int(_fn("gemm_tc", "lq_gemm_tc_splits", [c_int, c_int, c_int])(M, N, K))
     scratch = torch.empty(splits * M * N, dtype=torch.float32, device=a.device) if splits > 1 else None
@@ -472,6 +495,13 @@ def gemm_tc_qkv(a: torch.Tensor, w: torch.Tensor, cos, sin, tok_pos, tok_seq, sl
     _check_tables("gemm_tc_qkv", cos, sin, hd)
     if out is None:
         out = torch.empty((M, H * hd), dtype=torch.bfloat16, device=a.device)
+    if gemm_pair_takes(M, N, K) and a.is_contiguous() and w.is_contiguous():
+        fn = _fn("gemm_pair", "lq_gemm_pair_qkv", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                                   c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                                   c_int, c_int, c_void_p])
+        _check(fn(_p(a), _p(w), _p(out), M, K, _p(cos), _p(sin), _p(tok_pos), _p(tok_seq), _p(slots), _p(page_table),
+                  page_table.stride(0), _p(k_pages), _p(v_pages), H, Hkv, hd, page_size, _stream()), "gemm_pair_qkv")
+        return out
     splits = int(_fn("gemm_tc", "lq_gemm_tc_splits", [c_int, c_int, c_int])(M, N, K))
     scratch = torch.empty(splits * M * N, dtype=torch.float32, device=a.device) if splits > 1 else None
     fn = _fn("gemm_tc", "lq_gemm_tc_qkv", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,

@@ -401,6 +401,61 @@ def test_gemm_tc_one_row_of_tiles_of_every_width(M, N):
     assert ops.gemm_tc_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(2048, 4096, 1536),      # 128 tiles of 256 x 256 on 74 pairs: both accumulators, two rounds
+                                   (2000, 5008, 520),       # partial tiles at both edges, K no multiple of 64
+                                   (256, 18944, 72),        # one row of tiles, two steps along K
+                                   (1111, 10000, 4096)])
+def test_gemm_pair(M, N, K):
+    """Products of many rows on pairs of SMs (tcgen05 with cta_group::2): every epilogue against a product in
+    double precision, the same result as the kernel that keeps a tile on one SM up to float32 rounding, and
+    the same bits when run again."""
+    ops = _ops()
+    from longbow_quarrel_b200.kernels.linear import interleave_gate_up
+    assert ops.gemm_pair_takes(M, N, K)
+    assert not ops.gemm_pair_takes(128, N, K) and not ops.gemm_pair_takes(512, 1024, K)     # too few tiles: gemm_tc's
+    a, w = _rand((M, K), torch.bfloat16, 126), _rand((N, K), torch.bfloat16, 127, 0.3)
+    ref = a.double() @ w.double().T
+    res = _rand((M, N), torch.float32, 128)
+    F = N // 2
+    wg, wu = w[:F].contiguous(), w[F:].contiguous()
+    g, u = a.double() @ wg.double().T, a.double() @ wu.double().T
+    inter = interleave_gate_up(wg, wu)
+    outs = {}
+    for pairs in (True, False, True):
+        ops.USE_PAIRS = pairs
+        try:
+            before = ops.launches_by_name()
+            f32 = ops.gemm_tc(a, w, ops.EPI_F32)
+            bf = ops.gemm_tc(a, w, ops.EPI_BF16)
+            added = ops.gemm_tc(a, w, ops.EPI_RESID, residual=res.clone())
+            act = ops.gemm_tc(a, inter, ops.EPI_SWIGLU)
+            names = ops.launches_since(before)
+        finally:
+            ops.USE_PAIRS = True
+        assert names.get("gemm_pair", 0) == (4 if pairs else 0), names
+        _close(f32, ref, _acc_tol(K) + 1e-6)
+        _close(bf, ref, _acc_tol(K) + 1e-6, BF16_ULP)
+        _close(added, res.double() + ref, _acc_tol(K) + 1e-6)
+        _close(act, u * (g / (1 + torch.exp(-g))), 1e-4, BF16_ULP)
+        if pairs in outs:
+            for x, y in zip(outs[pairs], (f32, bf, added, act)):
+                assert torch.equal(x, y)
+        outs[pairs] = (f32, bf, added, act)
+    torch.cuda.synchronize()
+    assert ops.gemm_pair_status() == 0 and ops.gemm_tc_status() == 0
+
+
+def test_gemm_pair_leaves_unaligned_outputs_to_gemm_tc():
+    """An output whose rows are not 16-byte aligned cannot leave by TMA: the product stays on gemm_tc."""
+    ops = _ops()
+    M, N, K = 2048, 4098, 128
+    a, w = _rand((M, K), torch.bfloat16, 131), _rand((N, K), torch.bfloat16, 132, 0.3)
+    before = ops.launches_by_name()
+    out = ops.gemm_tc(a, w, ops.EPI_F32)
+    assert "gemm_pair" not in ops.launches_since(before)
+    _close(out, a.double() @ w.double().T, _acc_tol(K) + 1e-6)
+
+
 def test_gemm_tc_large_many_tiles_per_block():
     """More tiles than SMs: blocks walk over several tiles and both accumulators are used."""
     ops = _ops()
@@ -603,6 +658,22 @@ def test_gemm_skinny_qkv_rotates_and_stores(M, H, Hkv, hd, rotate):
 def test_gemm_tc_qkv_rotates_and_stores(M, K, H, Hkv, hd, rotate):
     """The fused projection of many rows (tiles, or ranges of K added by the second kernel) against
     product, rotation and cache write done apart; rows of several sequences, some continuing."""
+    _check_gemm_tc_qkv(M, K, H, Hkv, hd, rotate)
+
+
+@pytest.mark.parametrize("M,K,H,Hkv,hd,rotate", [(2500, 1032, 32, 8, 128, True), (1111, 520, 52, 7, 64, True),
+                                                 (2048, 256, 24, 8, 128, False)])
+def test_gemm_pair_qkv_rotates_and_stores(M, K, H, Hkv, hd, rotate):
+    """The same on pairs of SMs (tiles of 256 x 256): enough rows and heads that the pair kernel takes the product."""
+    ops = _ops()
+    assert ops.gemm_pair_takes(M, (H + 2 * Hkv) * hd, K)
+    before = ops.launches_by_name()
+    _check_gemm_tc_qkv(M, K, H, Hkv, hd, rotate)
+    assert ops.launches_since(before).get("gemm_pair_qkv") == 1
+    assert ops.gemm_pair_status() == 0
+
+
+def _check_gemm_tc_qkv(M, K, H, Hkv, hd, rotate):
     ops = _ops()
     n_seq = 5
     new = [M // n_seq + (1 if b < M % n_seq else 0) for b in range(n_seq)]

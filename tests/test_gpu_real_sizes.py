@@ -108,7 +108,7 @@ def test_real_layer_sizes_in_every_cut(tmp_path_factory, tmp_path, shape, dtype)
 
     counts = kernel_counts(out)
     if dtype == "bfloat16":
-        for name in ("gemm_tc_qkv", "attn_prefill_tc", "gemm_skinny_qkv", "attn_decode", "gemm_tc", "gemm_skinny",
+        for name in ("gemm_tc_qkv", "gemm_pair_qkv", "gemm_pair", "attn_prefill_tc", "gemm_skinny_qkv", "attn_decode", "gemm_tc", "gemm_skinny",
                      "gemm_skinny:rows8:norm_in", "attn_decode:teams"):
             assert counts.get(name, 0) > 0, (name, counts)
         assert "attention" not in counts and "linear" not in counts, counts       # no plain kernel took a product
