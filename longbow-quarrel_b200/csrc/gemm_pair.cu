@@ -250,12 +250,14 @@ int launch(const void* A, const void* W, void* C, const float* residual, int M, 
 
 }  // namespace
 
-// Whether lq_gemm_pair takes a product of these sizes: enough rows and columns for tiles of 256 x 256 to fill
-// the pairs of SMs at least once (smaller products are gemm_tc's, with its narrower tiles and its cuts of K).
+// Whether lq_gemm_pair takes a product of these sizes: enough rows and columns for tiles of 256 x 256 to keep
+// five eighths of the pairs of SMs busy (smaller products are gemm_tc's, with its narrower tiles and its cuts
+// of K).  Measured, us pairs / gemm_tc at K = 4096: 1024 rows x 4096 columns (64 tiles) 28 / 46, with K = 14336
+// 89 / 142; 512 x 4096 (32 tiles) 27 / 30 but with K = 14336 74 / 64; 256 x 4096 (16 tiles) 26 / 23.
 LQ_EXPORT int lq_gemm_pair_takes(int M, int N, int K) {
     if (M < 2 * BM || N < BN || K < BK || K % 8 != 0) return 0;
     const long tiles = (long)((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
-    return tiles >= sm_count() / 2;
+    return tiles * 8 >= (long)(sm_count() / 2) * 5;
 }
 
 // A [M, K] and W [N, K] bfloat16, row-major, 16-byte aligned, K % 8 == 0; epi: EPI_BF16, EPI_F32, EPI_RESID

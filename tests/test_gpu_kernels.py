@@ -412,7 +412,7 @@ def test_gemm_pair(M, N, K):
     ops = _ops()
     from longbow_quarrel_b200.kernels.linear import interleave_gate_up
     assert ops.gemm_pair_takes(M, N, K)
-    assert not ops.gemm_pair_takes(128, N, K) and not ops.gemm_pair_takes(512, 1024, K)     # too few tiles: gemm_tc's
+    assert not ops.gemm_pair_takes(128, N, K) and not ops.gemm_pair_takes(512, 4096, K)     # too few tiles: gemm_tc's
     a, w = _rand((M, K), torch.bfloat16, 126), _rand((N, K), torch.bfloat16, 127, 0.3)
     ref = a.double() @ w.double().T
     res = _rand((M, N), torch.float32, 128)
