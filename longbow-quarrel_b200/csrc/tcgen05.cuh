@@ -99,7 +99,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
-// Writes of ordinary threads to shared memory become visible to the tensor cores and TMA.
 // Stores of a box from shared memory (written by threads, then fence_async_shared) to a tensor in global
 // memory: plain, or added to what is there (float32).  Elements of the box outside the tensor are not written.
 // The inner coordinate times the element size must be a multiple of 16 bytes.
@@ -115,6 +114,7 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 // Until at most N of this thread's groups of stores still read their shared memory / are still under way.
 template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 template <int N> __device__ __forceinline__ void bulk_wait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+// Writes of ordinary threads to shared memory become visible to the tensor cores and TMA.
 __device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
