@@ -20,7 +20,7 @@
 // uses the other's barriers and before either ends.
 //
 // Epilogues: bfloat16 store, float32 store, residual add in place, SwiGLU, and q/k/v with rotation and cache
-// write (a thread stores its own row there).  Outputs whose rows are not 16-byte aligned, and all other
+// write (q leaves by TMA too; rows of k and v go to their cache pages from the same buffers).  Outputs whose rows are not 16-byte aligned, and all other
 // shapes, are gemm_tc's.
 //
 // Reference counterpart: the library GEMM of internal/device/cuda.go:293-318 (cublasSgemmEx).
@@ -105,7 +105,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         mbar_fence_init();
         prefetch_map(&map_a);
         prefetch_map(&map_b);
-        if (EPI != EPI_QKV) prefetch_map(&map_c);
+        prefetch_map(&map_c);
     }
     if (warp == 1) tmem_alloc_pair(smem_u32(&sm.tmem_base), TMEM_COLS);      // the same warp in both blocks
     pdl_launch_dependents();
@@ -179,8 +179,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             fence_after();
             const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
             if (EPI == EPI_QKV) {
-                // Rows go to cache pages of their own: a thread rotates and stores its row (BN holds whole heads).
-                qkv_epilogue(taddr, BN, qkv, q_out, m0 + quarter * 32 + lane, M, n0, N);
+                // BN holds whole heads; q leaves by TMA, rows of k and v go to their cache pages.
+                qkv_epilogue_staged(taddr, BN, qkv, &map_c, sm.stage[quarter], which, m0 + quarter * 32, M, n0, N, lane);
             } else if (m0 + quarter * 32 < M) {
                 staged_epilogue<EPI>(taddr, BN, sm.stage[quarter], which, &map_c, m0 + quarter * 32, n0, N, lane);
             }
@@ -188,7 +188,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             __syncwarp();
             if (lane == 0) arrive_at_first(smem_u32(&sm.acc_empty[acc]));
         }
-        if (EPI != EPI_QKV && lane == 0) bulk_wait<0>();      // this warp's stores are done before the block ends
+        if (lane == 0) bulk_wait<0>();      // this warp's stores are done before the block ends
     }
     fence_before();
     __syncthreads();
@@ -217,8 +217,11 @@ int launch(const void* A, const void* W, void* C, const float* residual, int M, 
     if (rc != LQ_OK) return rc;
     rc = make_map_bf16(&mb, W, N, K, K, BN / 2);
     if (rc != LQ_OK) return rc;
-    if constexpr (EPI != EPI_QKV)
+    if constexpr (EPI == EPI_QKV) {
+        if (make_map_out(&mc, C, 2, M, (long)qkv.H * qkv.hd, (long)qkv.H * qkv.hd, 32) != LQ_OK) return LQ_BAD_SIZE;
+    } else {
         if (!staged_map<EPI>(&mc, C, residual, M, EPI == EPI_SWIGLU ? N / 2 : N)) return LQ_BAD_SIZE;
+    }
     constexpr size_t smem = sizeof(Smem) + 1024;
     static_assert(smem <= 232448, "more shared memory than a block may have");
     static bool configured = false;

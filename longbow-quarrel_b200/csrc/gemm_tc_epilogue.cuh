@@ -112,35 +112,40 @@ __device__ __forceinline__ __nv_bfloat16* qkv_dest(const QkvArgs& q, __nv_bfloat
     return pages + (((size_t)page * q.Hkv + kvh) * q.page_size + pos % q.page_size) * q.hd;
 }
 
+// Elements j0 + 8 i .. j0 + 8 i + 7 of a head's first half (from a) and their partners in the second half (from b)
+// of one row, rotated (heads of q and k, when there are tables) and packed as bfloat16.
+__device__ __forceinline__ void rotate_pack(const uint32_t (&a)[32], const uint32_t (&b)[32], const float* cos_row,
+                                            const float* sin_row, int j0, int i, uint4& lo, uint4& hi) {
+    float x0[8], x1[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { x0[e] = __uint_as_float(a[8 * i + e]); x1[e] = __uint_as_float(b[8 * i + e]); }
+    if (cos_row) {
+#pragma unroll
+        for (int e4 = 0; e4 < 2; ++e4) {
+            const float4 c = reinterpret_cast<const float4*>(cos_row + j0)[2 * i + e4];
+            const float4 sn = reinterpret_cast<const float4*>(sin_row + j0)[2 * i + e4];
+            const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float y0 = x0[4 * e4 + e] * cc[e] - x1[4 * e4 + e] * ss[e];
+                const float y1 = x0[4 * e4 + e] * ss[e] + x1[4 * e4 + e] * cc[e];
+                x0[4 * e4 + e] = y0;
+                x1[4 * e4 + e] = y1;
+            }
+        }
+    }
+    lo = make_uint4(pack2(x0[0], x0[1]), pack2(x0[2], x0[3]), pack2(x0[4], x0[5]), pack2(x0[6], x0[7]));
+    hi = make_uint4(pack2(x1[0], x1[1]), pack2(x1[2], x1[3]), pack2(x1[4], x1[5]), pack2(x1[6], x1[7]));
+}
+
 // 32 elements j0 .. j0+31 of a head's first half (a) and their partners in the second half (b) of one row:
-// rotated (heads of q and k, when there are tables) and stored at dst + j0 and dst + half + j0.
+// rotated and stored at dst + j0 and dst + half + j0.
 __device__ __forceinline__ void store_qkv_pair(const uint32_t (&a)[32], const uint32_t (&b)[32], __nv_bfloat16* dst,
                                                const float* cos_row, const float* sin_row, int j0, int half) {
     uint4* lo = reinterpret_cast<uint4*>(dst + j0);
     uint4* hi = reinterpret_cast<uint4*>(dst + half + j0);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float x0[8], x1[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) { x0[e] = __uint_as_float(a[8 * i + e]); x1[e] = __uint_as_float(b[8 * i + e]); }
-        if (cos_row) {
-#pragma unroll
-            for (int e4 = 0; e4 < 2; ++e4) {
-                const float4 c = reinterpret_cast<const float4*>(cos_row + j0)[2 * i + e4];
-                const float4 sn = reinterpret_cast<const float4*>(sin_row + j0)[2 * i + e4];
-                const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float y0 = x0[4 * e4 + e] * cc[e] - x1[4 * e4 + e] * ss[e];
-                    const float y1 = x0[4 * e4 + e] * ss[e] + x1[4 * e4 + e] * cc[e];
-                    x0[4 * e4 + e] = y0;
-                    x1[4 * e4 + e] = y1;
-                }
-            }
-        }
-        lo[i] = make_uint4(pack2(x0[0], x0[1]), pack2(x0[2], x0[3]), pack2(x0[4], x0[5]), pack2(x0[6], x0[7]));
-        hi[i] = make_uint4(pack2(x1[0], x1[1]), pack2(x1[2], x1[3]), pack2(x1[4], x1[5]), pack2(x1[6], x1[7]));
-    }
+    for (int i = 0; i < 4; ++i) rotate_pack(a, b, cos_row, sin_row, j0, i, lo[i], hi[i]);
 }
 
 // The q/k/v epilogue of one thread's row m: columns [0, bn) of its lane of the accumulator at `taddr` are whole
@@ -163,6 +168,71 @@ __device__ __forceinline__ void qkv_epilogue(uint32_t taddr, int bn, const QkvAr
             if (m < M)
                 store_qkv_pair(a, b, row, rotate ? qkv.cos_t + (size_t)pos * half : nullptr,
                                rotate ? qkv.sin_t + (size_t)pos * half : nullptr, j0, half);
+        }
+    }
+}
+
+// The same through shared memory, for a warp's 32 rows (this thread's row is m = y + lane): a head's rows are put
+// into the warp's buffers as 128-byte pieces (head size 128: elements 0..63 in one buffer, 64..127 in the other;
+// head size 64: a whole row in one buffer).  Query heads leave as TMA stores into q_out (map_q: [M, H hd]); rows
+// of k and v go to their cache pages four rows per instruction, eight lanes writing a row's 128 contiguous bytes.
+__device__ __forceinline__ void qkv_epilogue_staged(uint32_t taddr, int bn, const QkvArgs& qkv, const CUtensorMap* map_q,
+                                                    uint8_t* bufs, int& which, int y, int M, int n0, int N, int lane) {
+    const int hd = qkv.hd, half = hd >> 1;
+    const int m = y + lane;
+    const int pos = m < M ? qkv.tok_pos[m] : 0;
+    const float* cos_row = qkv.cos_t ? qkv.cos_t + (size_t)pos * half : nullptr;
+    const float* sin_row = qkv.cos_t ? qkv.sin_t + (size_t)pos * half : nullptr;
+#pragma unroll 1
+    for (int col = 0; col < bn && n0 + col < N; col += hd) {
+        const int head = (n0 + col) / hd;
+        const bool rotate = head < qkv.H + qkv.Hkv;
+        uint8_t *lo_buf, *hi_buf;
+        int hi_piece;                               // where the second half's pieces start in hi_buf
+        if (hd == 128) {
+            if (lane == 0) bulk_wait_read<0>();     // both buffers are used at once
+            lo_buf = bufs; hi_buf = bufs + STAGE_BUF_BYTES; hi_piece = 0;
+        } else {
+            if (lane == 0) bulk_wait_read<1>();
+            lo_buf = hi_buf = bufs + which * STAGE_BUF_BYTES; hi_piece = 4;
+            which ^= 1;
+        }
+        __syncwarp();
+#pragma unroll 1
+        for (int j0 = 0; j0 < half; j0 += 32) {
+            uint32_t a[32], b[32];
+            ld32(taddr + col + j0, a);
+            ld32(taddr + col + half + j0, b);
+            wait_ld();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint4 lo, hi;
+                rotate_pack(a, b, rotate ? cos_row : nullptr, rotate ? sin_row : nullptr, j0, i, lo, hi);
+                *staged_at(lo_buf, lane, (j0 >> 3) + i) = lo;
+                *staged_at(hi_buf, lane, hi_piece + (j0 >> 3) + i) = hi;
+            }
+        }
+        if (head < qkv.H) {
+            fence_async_shared();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(map_q, smem_u32(lo_buf), head * hd, y);
+                if (hd == 128) tma_store_2d(map_q, smem_u32(hi_buf), head * hd + 64, y);
+                bulk_commit();
+            }
+        } else {
+            __syncwarp();
+            const unsigned long long mine = m < M ? (unsigned long long)qkv_dest(qkv, nullptr, m, head, pos) : 0ull;
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const int r = it * 4 + (lane >> 3), piece = lane & 7;
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(__shfl_sync(0xffffffffu, mine, r));
+                if (dst) {
+                    *reinterpret_cast<uint4*>(dst + piece * 8) = *staged_at(lo_buf, r, piece);
+                    if (hd == 128) *reinterpret_cast<uint4*>(dst + 64 + piece * 8) = *staged_at(hi_buf, r, piece);
+                }
+            }
+            __syncwarp();           // all lanes have read the buffers before the next head fills them
         }
     }
 }
