@@ -6,13 +6,13 @@
 //   warp 0      one lane loads Q once and then K and V tiles by TMA into two stages of shared
 //               memory (128-byte swizzle; a page of one kv head is a [64, 128] box);
 //   warp 1      one lane issues tcgen05.mma: S = Q K^T into tensor memory, and, once the
-//               softmax warps have turned S into probabilities P in shared memory,
+//               softmax warps have turned S into probabilities P in tensor memory,
 //               O += P V into a second accumulator (V is the MN-major operand: its rows are
 //               keys).  S of the next tile is issued as soon as S of this one has been read,
 //               so the tensor cores work on it while the softmax of this tile runs;
 //   warps 2..9  two threads per query row (64 keys each): read the row of S from tensor
 //               memory, mask it, keep the running maximum and sum in 32-bit, write
-//               bfloat16 probabilities into shared memory in the layout the tensor cores read.  The
+//               bfloat16 probabilities into tensor memory, where the second product reads them.  The
 //               reference maximum of a row is only moved (and O rescaled in tensor memory)
 //               when the true maximum has grown by more than 2^8 since; the result is the
 //               same, as O and the sum always share one reference.  The probabilities are
@@ -54,7 +54,6 @@ struct Smem {
     alignas(1024) uint8_t q[HD / 64][PANEL];          // [d half][128 rows x 128 B]
     alignas(1024) uint8_t k[2][HD / 64][PANEL];       // [stage][d half][128 keys x 128 B]
     alignas(1024) uint8_t v[2][HD / 64][PANEL];       // [stage][d half][128 keys x 128 B]
-    alignas(1024) uint8_t p[2][PANEL];          // [key half][128 rows x 128 B]
     alignas(8) uint64_t q_full;
     uint64_t k_full[2], v_full[2], kv_empty[2];
     uint64_t s_full, s_empty, p_full, pv_done;
@@ -93,7 +92,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     constexpr int DH = HD / 64;                  // panels of 64 elements along the head dimension
     Smem<HD>& sm = *reinterpret_cast<Smem<HD>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr uint32_t TMEM_COLS = 256;          // S in columns 0..127, O in 128..255
+    constexpr uint32_t TMEM_COLS = 512;          // S in columns 0..127, O in 128..255, P (bfloat16 pairs) in 256..319
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&sm.q_full), 1);
@@ -115,7 +114,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     fence_before();
     __syncthreads();
     fence_after();
-    const uint32_t tmem_s = sm.tmem_base, tmem_o = sm.tmem_base + BN;
+    const uint32_t tmem_s = sm.tmem_base, tmem_o = sm.tmem_base + BN, tmem_p = sm.tmem_base + 2 * BN;
     pdl_wait();
 
     // Heads vary fastest: the work list has the blocks with the most keys first, so the launch order is
@@ -191,9 +190,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 fence_after();
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint64_t a = desc_k_major(smem_u32(sm.p[kk >> 2]) + (kk & 3) * 32);
                     const uint64_t b = desc_mn_major(smem_u32(sm.v[s][0]) + kk * 2048, PANEL);
-                    mma_f16(tmem_o, a, b, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    mma_f16_ts(tmem_o, tmem_p + kk * 8, b, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 commit(smem_u32(&sm.kv_empty[s]));
                 commit(smem_u32(&sm.pv_done));
@@ -288,15 +286,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 LQ_WAIT(sm.pv_done, (j - 1) & 1, 8);              // the last product has read P
                 if (!ok) break;
             }
-            // Row r of P: panels of 64 keys, 8 pieces of 8 keys each; piece q of a row lies at piece (q ^ (r % 8)).
-            uint8_t* prow = sm.p[(part * NC) / 64] + (r >> 3) * 1024 + (r & 7) * 128;
-            const int piece0 = ((part * NC) % 64) / 8;
+            // Row r of P goes to lane r of tensor memory, two probabilities per column: keys 2c and 2c + 1 of this
+            // thread's part in column part * NC / 2 + c.
 #pragma unroll
-            for (int c = 0; c < NC / 8; ++c)
-                *reinterpret_cast<uint4*>(prow + (((piece0 + c) ^ (r & 7)) << 4)) =
-                    make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            for (int c = 0; c < NC / 64; ++c) st32(tmem_p + lane_base + part * (NC / 2) + c * 32, pk + c * 32);
+            wait_st();
             l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
-            fence_async_shared();
             fence_before();
             mbar_arrive(smem_u32(&sm.p_full));
         }
