@@ -332,6 +332,249 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
 }
 
+// ------------------------------------------------------------------ two heads of a group per block
+// The same attention with two chains of work per block: the 128 query rows of two heads that share a kv head
+// (so each tile of keys and values is loaded once for both), each chain with an S and an O of its own in
+// tensor memory and four softmax warps (one thread per row: no exchange of maxima).  While the softmax of
+// one chain runs, the tensor cores make the other chain's products, so the chain of hand-overs of a tile
+// (scores ready, read, maxima, exponentials, probabilities stored, product issued) of one head hides behind
+// the other's.  P takes the place of S in tensor memory (the next S of a chain is issued after its P V, and
+// products run in the order of issue).  Twelve warps: 0 loads, 1 issues products, 2 and 3 idle, 4..7 and
+// 8..11 the two chains' softmax; the first four give registers up (setmaxnreg) so that a softmax thread can
+// hold its row's 128 scores.
+constexpr int N_THREADS2 = 384;
+
+template <int HD>
+struct Smem2 {
+    alignas(1024) uint8_t q[2][HD / 64][PANEL];       // [chain][d half][128 rows x 128 B]
+    alignas(1024) uint8_t k[2][HD / 64][PANEL];       // [stage][d half][128 keys x 128 B]
+    alignas(1024) uint8_t v[2][HD / 64][PANEL];
+    alignas(8) uint64_t q_full;
+    uint64_t k_full[2], v_full[2], kv_empty[2];
+    uint64_t s_full[2], p_full[2], pv_done[2];        // per chain
+    uint32_t tmem_base;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(N_THREADS2, 1)
+attn_prefill_two_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table, int pt_stride,
+                        const int* __restrict__ slots, const int* __restrict__ kv_len, const int* __restrict__ qb_seq,
+                        const int* __restrict__ qb_row, const int* __restrict__ qb_rows, const int* __restrict__ qb_pos,
+                        __nv_bfloat16* __restrict__ out, int H, int Hkv, int oob_row, float scale_log2, int window) {
+    extern __shared__ uint8_t smem_raw[];
+    constexpr int DH = HD / 64;
+    Smem2<HD>& sm = *reinterpret_cast<Smem2<HD>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr uint32_t TMEM_COLS = 512;          // S (then P) of the chains in columns 0..127 and 128..255, O from 256 on
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&sm.q_full), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&sm.k_full[s]), 1);
+            mbar_init(smem_u32(&sm.v_full[s]), 1);
+            mbar_init(smem_u32(&sm.kv_empty[s]), 1);
+            mbar_init(smem_u32(&sm.s_full[s]), 1);
+            mbar_init(smem_u32(&sm.p_full[s]), BM);
+            mbar_init(smem_u32(&sm.pv_done[s]), 1);
+        }
+        mbar_fence_init();
+        prefetch_map(&map_q);
+        prefetch_map(&map_k);
+        prefetch_map(&map_v);
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&sm.tmem_base), TMEM_COLS);
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem_base = sm.tmem_base;
+    pdl_wait();
+
+    // Pairs of heads vary fastest: the blocks with the most keys come first over all heads.
+    const int pairs = H >> 1;
+    const int blk = blockIdx.x / pairs, h0 = (blockIdx.x % pairs) * 2;
+    const int seq = qb_seq[blk], row0 = qb_row[blk], n_rows = qb_rows[blk], pos0 = qb_pos[blk];
+    const int kvh = h0 / (H / Hkv);
+    const int len = kv_len[seq];
+    const int* pt = page_table + (size_t)slots[seq] * pt_stride;
+    const int pos_last = pos0 + n_rows - 1;
+    const int key_first = (window > 0 && pos0 >= window) ? pos0 - window + 1 : 0;
+    const int tile_lo = key_first / BN, n_tiles = pos_last / BN - tile_lo + 1;
+    const int last_page = (len - 1) / PAGE;
+
+    if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        if (warp == 0 && lane == 0) {
+            // ------------------------------------------------------------ TMA producer
+            bool ok = true;
+            mbar_expect_tx(smem_u32(&sm.q_full), 2 * DH * PANEL);
+            for (int c = 0; c < 2; ++c)
+                for (int half = 0; half < DH; ++half)
+                    tma_load_2d(smem_u32(sm.q[c][half]), &map_q, (h0 + c) * HD + half * 64, row0, smem_u32(&sm.q_full));
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j & 1;
+                LQ_WAIT(sm.kv_empty[s], ((j >> 1) & 1) ^ 1, 1);
+                if (!ok) break;
+                int rows[2];
+                for (int i = 0; i < 2; ++i) {
+                    const int pg = (tile_lo + j) * 2 + i;
+                    const int page = pg <= last_page ? pt[pg] : -1;
+                    rows[i] = page >= 0 ? (page * Hkv + kvh) * PAGE : oob_row;   // out of range: TMA fills zeros
+                }
+                mbar_expect_tx(smem_u32(&sm.k_full[s]), DH * PANEL);
+                for (int half = 0; half < DH; ++half)
+                    for (int i = 0; i < 2; ++i)
+                        tma_load_2d(smem_u32(sm.k[s][half]) + i * (PANEL / 2), &map_k, half * 64, rows[i], smem_u32(&sm.k_full[s]));
+                mbar_expect_tx(smem_u32(&sm.v_full[s]), DH * PANEL);
+                for (int half = 0; half < DH; ++half)
+                    for (int i = 0; i < 2; ++i)
+                        tma_load_2d(smem_u32(sm.v[s][half]) + i * (PANEL / 2), &map_v, half * 64, rows[i], smem_u32(&sm.v_full[s]));
+            }
+        } else if (warp == 1 && lane == 0) {
+            // ------------------------------------------------------------ MMA issuer
+            constexpr uint32_t idesc_s = idesc_bf16(BM, BN, false);
+            constexpr uint32_t idesc_pv = idesc_bf16(BM, HD, true);
+            bool ok = true;
+            auto issue_s = [&](int c, int s) {          // S of chain c from the keys in stage s
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint64_t a = desc_k_major(smem_u32(sm.q[c][kk >> 2]) + (kk & 3) * 32);
+                    const uint64_t b = desc_k_major(smem_u32(sm.k[s][kk >> 2]) + (kk & 3) * 32);
+                    mma_f16(tmem_base + c * BN, a, b, idesc_s, kk > 0 ? 1u : 0u);
+                }
+                commit(smem_u32(&sm.s_full[c]));
+            };
+            LQ_WAIT(sm.q_full, 0, 2);
+            if (ok) LQ_WAIT(sm.k_full[0], 0, 3);
+            if (ok) { fence_after(); issue_s(0, 0); issue_s(1, 0); }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j & 1;
+                for (int c = 0; c < 2 && ok; ++c) {
+                    LQ_WAIT(sm.p_full[c], j & 1, 5);
+                    if (ok && c == 0) LQ_WAIT(sm.v_full[s], (j >> 1) & 1, 6);
+                    if (!ok) break;
+                    fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < BN / 16; ++kk) {
+                        const uint64_t b = desc_mn_major(smem_u32(sm.v[s][0]) + kk * 2048, PANEL);
+                        mma_f16_ts(tmem_base + 2 * BN + c * HD, tmem_base + c * BN + kk * 8, b, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    if (c == 1) commit(smem_u32(&sm.kv_empty[s]));      // every product that reads this stage has been issued
+                    commit(smem_u32(&sm.pv_done[c]));
+                    if (j + 1 < n_tiles) {
+                        // The chain's next S takes the place of its P: issued after P V, it runs after it.
+                        if (c == 0) LQ_WAIT(sm.k_full[s ^ 1], ((j + 1) >> 1) & 1, 3);
+                        if (!ok) break;
+                        fence_after();
+                        issue_s(c, s ^ 1);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------------------------------------------------------- softmax: one thread per query row and chain
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        const int chain = (warp - 4) >> 2, quarter = warp & 3;
+        const int h = h0 + chain;
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const uint32_t tmem_s = tmem_base + chain * BN + lane_base;              // S, then P in its first 64 columns
+        const uint32_t tmem_o = tmem_base + 2 * BN + chain * HD + lane_base;
+        const int pos_r = pos0 + r;
+        const bool row_ok = r < n_rows;
+        float m_ref = -CUDART_INF_F, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            LQ_WAIT(sm.s_full[chain], j & 1, 7);         // S of this tile is there, and so is the last tile's P V (issued before it)
+            if (!ok) break;
+            fence_after();
+            float t[BN];
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) ld32(tmem_s + c * 32, reinterpret_cast<uint32_t*>(t) + c * 32);
+            wait_ld();
+            const int kb = (tile_lo + j) * BN;
+            const bool whole = n_rows == BM && kb + BN - 1 <= pos0 && kb + BN <= len && (window <= 0 || kb > pos_last - window);
+            float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+            if (whole) {
+#pragma unroll
+                for (int c = 0; c < BN; ++c) mx[c & 3] = fmaxf(mx[c & 3], t[c]);
+            } else {
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                    const int key = kb + c;
+                    const bool vis = row_ok && key <= pos_r && key < len && (window <= 0 || key > pos_r - window);
+                    t[c] = vis ? t[c] : -CUDART_INF_F;
+                    mx[c & 3] = fmaxf(mx[c & 3], t[c]);
+                }
+            }
+            const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
+            // Move the reference only when the maximum has run ahead of it by more than the step.
+            const bool need = m_tile > m_ref + RESCALE_STEP;
+            const float corr = need ? ex2(m_ref - m_tile) : 1.0f;
+            if (need) { m_ref = m_tile; l *= corr; }
+            if (j > 0 && __any_sync(0xffffffffu, need)) {
+#pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    uint32_t o[32];
+                    ld32(tmem_o + c * 32, o);
+                    wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                    st32(tmem_o + c * 32, o);
+                }
+            }
+            const float base = m_ref == -CUDART_INF_F ? 0.f : m_ref;
+            float sums[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t pk[32];
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const uint32_t b0 = bf16_bits(ex2(fmaf(t[half * 64 + 2 * c], scale_log2, -base)));
+                    const uint32_t b1 = bf16_bits(ex2(fmaf(t[half * 64 + 2 * c + 1], scale_log2, -base)));
+                    sums[c & 3] += __uint_as_float(b0) + __uint_as_float(b1);
+                    pk[c] = __byte_perm(b0, b1, 0x7632);
+                }
+                st32(tmem_s + half * 32, pk);           // keys 64 half + 2c, + 1 in column 32 half + c
+            }
+            wait_st();
+            l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
+            fence_before();
+            mbar_arrive(smem_u32(&sm.p_full[chain]));
+        }
+        if (ok) {
+            LQ_WAIT(sm.pv_done[chain], (n_tiles - 1) & 1, 9);
+        }
+        if (ok) {
+            fence_after();
+            const float inv = 1.0f / l;
+            __nv_bfloat16* orow = out + ((size_t)(row0 + r) * H + h) * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t o[32];
+                ld32(tmem_o + c * 32, o);
+                wait_ld();
+                if (row_ok) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        reinterpret_cast<uint4*>(orow + c * 32)[i] =
+                            make_uint4(pack2(__uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv),
+                                       pack2(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv),
+                                       pack2(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv),
+                                       pack2(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv));
+                }
+            }
+        }
+    }
+    fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
 }  // namespace
 
 namespace {
@@ -352,6 +595,21 @@ int launch_hd(const void* q, int q_stride, int T, const void* k_pages, const voi
         if (cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return lq_launch_status();
         configured = true;
+    }
+    static const bool one_chain = [] { const char* v = getenv("LQ_ATTN_ONE_CHAIN"); return v && v[0] == '1'; }();
+    if ((H / Hkv) % 2 == 0 && !one_chain) {
+        // Two heads of a group per block: they share the block's tiles of keys and values.
+        constexpr size_t smem2 = sizeof(Smem2<HD>) + 1024;
+        static_assert(smem2 <= 232448, "more shared memory than a block may have");
+        static bool configured2 = false;
+        if (!configured2) {
+            if (cudaFuncSetAttribute(attn_prefill_two_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2) != cudaSuccess)
+                return lq_launch_status();
+            configured2 = true;
+        }
+        return launch_pdl(attn_prefill_two_kernel<HD>, dim3(n_blocks * (H / 2)), dim3(N_THREADS2), smem2, stream, mq, mk, mv,
+                          page_table, pt_stride, slots, kv_len, qb_seq, qb_row, qb_rows, qb_pos, (__nv_bfloat16*)out, H, Hkv,
+                          (int)kv_rows, scale * 1.4426950408889634f, window);
     }
     return launch_pdl(attn_prefill_tc_kernel<HD>, dim3(n_blocks * H), dim3(N_THREADS), smem, stream, mq, mk, mv, page_table,
                       pt_stride, slots, kv_len, qb_seq, qb_row, qb_rows, qb_pos, (__nv_bfloat16*)out, H, Hkv,
