@@ -66,10 +66,14 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
-// The bits of x rounded to bfloat16 precision (nearest, ties to even), low 16 bits zero; x finite, x >= 0.
-__device__ __forceinline__ uint32_t bf16_bits(float x) {
-    const uint32_t u = __float_as_uint(x);
-    return (u + 0x7FFFu + ((u >> 16) & 1u)) & 0xFFFF0000u;
+// x rounded to bfloat16 precision (nearest; the low 16 bits of the result are zero), x finite and at most 2^100 in
+// size: Veltkamp's splitting with 2^16 + 1, three operations of the multiply-add pipe.  The conversion
+// instructions share a pipe with the exponentials, and rounding by integer arithmetic took four operations of the
+// integer pipe, which with the maxima and the packing made that pipe the busiest of the kernel (60 % against 41 %
+// for the exponentials' and 40 % for the tensor cores').
+__device__ __forceinline__ float bf16_round(float x) {
+    const float p = __fmul_rn(x, 65537.0f);
+    return __fadd_rn(__fsub_rn(x, p), p);
 }
 // 2^x by the special-function unit (relative error about 2^-22; -inf gives 0).
 __device__ __forceinline__ float ex2(float x) {
@@ -271,16 +275,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const float base = m_ref == -CUDART_INF_F ? 0.f : m_ref;
             // The probabilities, rounded to bfloat16 and packed in pairs, while the last tile's product with V
             // still runs.  The sum runs over them as the product will see them.
-            // Rounded by integer arithmetic (nearest, ties to even): the values are finite and not negative,
-            // and the conversion instructions would share a pipe with the exponentials.
+            // Rounded on the multiply-add pipe (bf16_round): conversion instructions would share a pipe with the exponentials.
             float sums[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pk[NC / 2];
 #pragma unroll
             for (int c = 0; c < NC / 2; ++c) {
-                const uint32_t b0 = bf16_bits(ex2(fmaf(t[2 * c], scale_log2, -base)));
-                const uint32_t b1 = bf16_bits(ex2(fmaf(t[2 * c + 1], scale_log2, -base)));
-                sums[c & 3] += __uint_as_float(b0) + __uint_as_float(b1);
-                pk[c] = __byte_perm(b0, b1, 0x7632);              // low half: b0's upper 16 bits, high half: b1's
+                const float b0 = bf16_round(ex2(fmaf(t[2 * c], scale_log2, -base)));
+                const float b1 = bf16_round(ex2(fmaf(t[2 * c + 1], scale_log2, -base)));
+                sums[c & 3] += b0 + b1;
+                pk[c] = __byte_perm(__float_as_uint(b0), __float_as_uint(b1), 0x7632);      // low half: b0's upper 16 bits, high half: b1's
             }
             if (j > 0) {
                 LQ_WAIT(sm.pv_done, (j - 1) & 1, 8);              // the last product has read P
@@ -531,10 +534,10 @@ attn_prefill_two_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 uint32_t pk[32];
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
-                    const uint32_t b0 = bf16_bits(ex2(fmaf(t[half * 64 + 2 * c], scale_log2, -base)));
-                    const uint32_t b1 = bf16_bits(ex2(fmaf(t[half * 64 + 2 * c + 1], scale_log2, -base)));
-                    sums[c & 3] += __uint_as_float(b0) + __uint_as_float(b1);
-                    pk[c] = __byte_perm(b0, b1, 0x7632);
+                    const float b0 = bf16_round(ex2(fmaf(t[half * 64 + 2 * c], scale_log2, -base)));
+                    const float b1 = bf16_round(ex2(fmaf(t[half * 64 + 2 * c + 1], scale_log2, -base)));
+                    sums[c & 3] += b0 + b1;
+                    pk[c] = __byte_perm(__float_as_uint(b0), __float_as_uint(b1), 0x7632);
                 }
                 st32(tmem_s + half * 32, pk);           // keys 64 half + 2c, + 1 in column 32 half + c
             }

@@ -15,8 +15,9 @@ constexpr unsigned long long WAIT_NS = 2000000000ull;   // a wait gives up after
 __device__ int g_status = 0;
 __device__ volatile int* g_status_mapped = nullptr;
 
+// The first code stays: the waits that give up after it are its consequences.
 __device__ __forceinline__ void give_up(int code) {
-    atomicExch(&g_status, code);
+    if (atomicCAS(&g_status, 0, code) != 0) return;
     volatile int* p = g_status_mapped;
     if (p) { *p = code; __threadfence_system(); }
 }
