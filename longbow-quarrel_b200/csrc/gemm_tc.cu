@@ -45,7 +45,7 @@ template <int BN, int STAGES, int AROWS, bool STAGED>
 struct Smem {
     alignas(1024) uint8_t a[STAGES][AROWS * BK * 2];
     alignas(1024) uint8_t b[STAGES][BN * BK * 2];
-    alignas(1024) uint8_t stage[STAGED ? 4 : 1][STAGED ? 2 * STAGE_BUF_BYTES : 16];
+    alignas(1024) uint8_t stage[STAGED ? (AROWS == BM ? 4 : 2) : 1][STAGED ? 2 * STAGE_BUF_BYTES : 16];
     alignas(8) uint64_t full[STAGES];
     uint64_t empty[STAGES];
     uint64_t acc_full[2];
@@ -125,16 +125,18 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], void* Cout,
 
 // ------------------------------------------------------------------ the kernel
 // Whether the epilogue of a kernel with these parameters can go through shared memory and TMA stores:
-// many rows (whole 128-row tiles of x in a stage), tiles of 128 or 256 columns, and not the q/k/v epilogue,
-// whose rows go to cache pages of their own.
+// tiles of 128 or 256 columns and not the q/k/v epilogue, whose rows go to cache pages of their own; with
+// 64-row stages (at most 64 rows of x) only the float32 store of 256-column tiles, which the ranges of K use.
 template <int BN, int EPI, int AROWS> struct StagedEpilogue {
-    static constexpr bool value = AROWS == BM && (BN == 128 || BN == 256) && EPI != EPI_QKV;
+    static constexpr bool value = (AROWS == BM && (BN == 128 || BN == 256) && EPI != EPI_QKV) ||
+                                  (AROWS == 64 && BN == 256 && EPI == EPI_F32);
 };
 
 template <int BN, int STAGES, int EPI, int AROWS>
 __global__ void __launch_bounds__(N_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ CUtensorMap map_c, int staged, void* Cout, const float* residual, int M, int N, int K, int splits, const QkvArgs qkv) {
+               const __grid_constant__ CUtensorMap map_c, int staged, void* Cout, const float* residual, int M, int N, int K, int splits,
+               int plane_rows, const QkvArgs qkv) {
     extern __shared__ uint8_t smem_raw[];
     constexpr bool STAGED = StagedEpilogue<BN, EPI, AROWS>::value;
     using S = Smem<BN, STAGES, AROWS, STAGED>;
@@ -142,7 +144,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
     // A piece of work is (tile, range of K): piece = tile * splits + range.  With splits > 1 the kernel
-    // is the float32-store one and Cout the scratch [splits, M, N].
+    // is the float32-store one and Cout the scratch [splits, plane_rows, N] (plane_rows: M rounded up to 32, so
+    // that a warp's box of 32 rows stays inside its range's plane).
     const int total = m_tiles * n_tiles * splits;
     const int n_kb = (K + BK - 1) / BK;
     constexpr uint32_t STAGE_BYTES = (AROWS + BN) * BK * 2;
@@ -230,7 +233,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int piece = blockIdx.x; piece < total && ok; piece += gridDim.x, ++t) {
             const int tile = piece / splits, range = piece % splits;
             const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
-            void* dst = splits > 1 ? (void*)((float*)Cout + (size_t)range * M * N) : Cout;
+            void* dst = splits > 1 ? (void*)((float*)Cout + (size_t)range * plane_rows * N) : Cout;
             const uint32_t acc = t & 1;
             const int m = m0 + quarter * 32 + lane;
             const int n_lim = n0 + BN < N ? n0 + BN : N;
@@ -255,8 +258,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (EPI == EPI_QKV) {
                 qkv_epilogue(taddr, BN, qkv, (__nv_bfloat16*)Cout, m, M, n0, N);
             } else if (STAGED && staged) {
-                if constexpr (STAGED)
-                    staged_epilogue<EPI>(taddr, BN, sm.stage[quarter], stage_buf, &map_c, m0 + quarter * 32, n0, N, lane);
+                if constexpr (STAGED) {
+                    if (m0 + quarter * 32 < M)          // (with 64-row stages only the first two warps hold rows of x)
+                        staged_epilogue<EPI>(taddr, BN, sm.stage[quarter], stage_buf, &map_c,
+                                             (splits > 1 ? range * plane_rows : 0) + m0 + quarter * 32, n0, N, lane);
+                }
             } else {
 #pragma unroll 1
                 for (int c = 0; c < (BN + 31) / 32; ++c) {      // a last half chunk reads columns that are not stored
@@ -293,7 +299,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // part [splits, M, N] float32 -> the epilogue of their sum, the ranges added in their order.
 // One thread makes four neighbouring outputs.
 template <int EPI>
-__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int splits, void* Cout,
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int splits, int plane_rows, void* Cout,
                                                             const float* residual, int M, int N, const QkvArgs qkv) {
     pdl_launch_dependents();
     pdl_wait();
@@ -302,7 +308,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long)M * groups) return;
     const int m = (int)(idx / groups), c = (int)(idx % groups) * 4;
-    const size_t plane = (size_t)M * N;
+    const size_t plane = (size_t)plane_rows * N;
     auto sum4 = [&](int col, float (&v)[4]) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) v[i] = 0.f;
@@ -370,10 +376,11 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
 template <int EPI>
 int launch_reduce(const float* part, int splits, void* C, const float* residual, int M, int N, const QkvArgs& qkv,
                   cudaStream_t stream) {
+    const int plane_rows = (M + 31) / 32 * 32;
     const int NO = (EPI == EPI_SWIGLU || EPI == EPI_QKV) ? N >> 1 : N;
     const long threads = (long)M * ((NO + 3) >> 2);
     return launch_pdl(splitk_reduce_kernel<EPI>, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, stream, part, splits,
-                      C, residual, M, N, qkv);
+                      plane_rows, C, residual, M, N, qkv);
 }
 
 // ------------------------------------------------------------------ host side
@@ -400,10 +407,11 @@ int launch_epi(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const floa
     // (and, for the residual, when the sums are added in place).
     CUtensorMap mc{};
     int staged = 0;
+    const int plane_rows = (M + 31) / 32 * 32;          // rows of one range's plane of the scratch
     if constexpr (STAGED)
-        staged = splits == 1 && staged_map<EPI>(&mc, C, residual, M, EPI == EPI_SWIGLU ? N / 2 : N);
+        staged = staged_map<EPI>(&mc, C, residual, splits > 1 ? (long)splits * plane_rows : M, EPI == EPI_SWIGLU ? N / 2 : N);
     return launch_pdl(gemm_tc_kernel<BN, STAGES, EPI, AROWS>, dim3(grid), dim3(N_THREADS), smem, stream, ma, mb, mc, staged, C, residual,
-                      M, N, K, splits, qkv);
+                      M, N, K, splits, plane_rows, qkv);
 }
 
 // ALL: every epilogue; otherwise only the two that products with many columns have (SwiGLU, float32 store).
@@ -510,7 +518,7 @@ int gemm_tc_dispatch(const void* A, const void* W, void* C, const float* residua
 
 // A [M, K] and W [N, K] bfloat16, row-major, 16-byte aligned, K % 8 == 0.
 // For EPI_SWIGLU, N counts the interleaved gate and up rows (N % 16 == 0) and C is [M, N / 2].
-// scratch: lq_gemm_tc_splits(M, N, K) * M * N floats when that number is above 1 (else unused).
+// scratch: lq_gemm_tc_scratch_floats(M, N, K) floats (0: unused): a plane of M rounded up to 32 rows for each range of K.
 LQ_EXPORT int lq_gemm_tc(const void* A, const void* W, void* C, const float* residual, int M, int N, int K, int epi,
                          float* scratch, cudaStream_t stream) {
     if (epi < EPI_BF16 || epi > EPI_SWIGLU) return LQ_BAD_DTYPE;
@@ -519,7 +527,7 @@ LQ_EXPORT int lq_gemm_tc(const void* A, const void* W, void* C, const float* res
 
 // The q/k/v projection with its epilogue fused: X [M, K] . W^T for W [(H + 2 Hkv) hd, K]; q and k are rotated
 // by the cos/sin tables at each row's position (tables null: no rotation); q goes to q_out [M, H hd], k and v go
-// into the row's cache page.  hd is 64 or 128.  scratch: lq_gemm_tc_splits(M, (H + 2 Hkv) hd, K) * M * N floats
+// into the row's cache page.  hd is 64 or 128.  scratch: lq_gemm_tc_scratch_floats(M, (H + 2 Hkv) hd, K) floats
 // when that number is above 1.
 LQ_EXPORT int lq_gemm_tc_qkv(const void* X, const void* W, void* q_out, int M, int K, const float* cos_t,
                              const float* sin_t, const int* tok_pos, const int* tok_seq, const int* slots,
@@ -537,6 +545,13 @@ LQ_EXPORT int lq_gemm_tc_qkv(const void* X, const void* W, void* q_out, int M, i
 LQ_EXPORT int lq_gemm_tc_splits(int M, int N, int K) {
     if (M <= 0 || N <= 0 || K <= 0) return 1;
     return plan_splits(M, N, K);
+}
+
+// Floats of scratch that a product of these sizes needs (0 when the contraction is not cut).
+LQ_EXPORT long lq_gemm_tc_scratch_floats(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    const int splits = plan_splits(M, N, K);
+    return splits > 1 ? (long)splits * ((M + 31) / 32 * 32) * N : 0;
 }
 
 // The status word of the bounded waits: 0, or the code of the first wait that gave up

@@ -442,6 +442,12 @@ def gemm_pair_status() -> int:
     return int(fn())
 
 
+def _gemm_tc_scratch_floats(M: int, N: int, K: int) -> int:
+    fn = build.load("gemm_tc").lq_gemm_tc_scratch_floats
+    fn.argtypes, fn.restype = [c_int, c_int, c_int], c_long
+    return int(fn(M, N, K))
+
+
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, epi: int, residual: torch.Tensor | None = None,
             out: torch.Tensor | None = None) -> torch.Tensor:
     """a [M, K] . w [N, K]^T on the tcgen05 tensor cores (TMA-fed, float32 accumulation in
@@ -471,7 +477,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, epi: int, residual: torch.Tensor |
         return out
     # Few tiles (few rows, narrow weight): the kernel cuts the contraction into ranges and adds them afterwards.
     splits = int(_fn("gemm_tc", "lq_gemm_tc_splits", [c_int, c_int, c_int])(M, N, K))
-    scratch = torch.empty(splits * M * N, dtype=torch.float32, device=a.device) if splits > 1 else None
+    scratch = torch.empty(_gemm_tc_scratch_floats(M, N, K), dtype=torch.float32, device=a.device) if splits > 1 else None
     fn = _fn("gemm_tc", "lq_gemm_tc", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                        c_void_p])
     _check(fn(_p(_contig(a, "a")), _p(_contig(w, "w")), _p(out), _p(residual), M, N, K, epi, _p(scratch), _stream()),
@@ -503,7 +509,7 @@ def gemm_tc_qkv(a: torch.Tensor, w: torch.Tensor, cos, sin, tok_pos, tok_seq, sl
                   page_table.stride(0), _p(k_pages), _p(v_pages), H, Hkv, hd, page_size, _stream()), "gemm_pair_qkv")
         return out
     splits = int(_fn("gemm_tc", "lq_gemm_tc_splits", [c_int, c_int, c_int])(M, N, K))
-    scratch = torch.empty(splits * M * N, dtype=torch.float32, device=a.device) if splits > 1 else None
+    scratch = torch.empty(_gemm_tc_scratch_floats(M, N, K), dtype=torch.float32, device=a.device) if splits > 1 else None
     fn = _fn("gemm_tc", "lq_gemm_tc_qkv", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                            c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                            c_int, c_void_p, c_void_p])
