@@ -20,8 +20,8 @@
 // uses the other's barriers and before either ends.
 //
 // Epilogues: bfloat16 store, float32 store, residual add in place, SwiGLU, and q/k/v with rotation and cache
-// write (q leaves by TMA too; rows of k and v go to their cache pages from the same buffers).  Outputs whose rows are not 16-byte aligned, and all other
-// shapes, are gemm_tc's.
+// write (q leaves by TMA too; rows of k and v go to their cache pages from the same buffers).  Outputs whose
+// rows are not 16-byte aligned, and all other shapes, are gemm_tc's.
 //
 // Reference counterpart: the library GEMM of internal/device/cuda.go:293-318 (cublasSgemmEx).
 #include "gemm_tc_epilogue.cuh"
