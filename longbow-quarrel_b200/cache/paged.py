@@ -38,6 +38,18 @@ class PagedKVGroup(CacheGroup):
         self._dirty: set[int] = set()
         self._to_clear: list[tuple[int, int]] = []      # (page, first row that the step does not write)
 
+    def _snapshot(self) -> torch.Tensor:
+        """The next of four pinned copies of the table (its last upload, four uploads ago, has long been read)."""
+        if not hasattr(self, "_staged"):
+            self._staged, self._turn = [], 0
+        if len(self._staged) < 4:
+            self._staged.append((torch.empty(self.table.shape, dtype=torch.int32).pin_memory(), torch.cuda.Event()))
+            self._turn = len(self._staged) - 1
+        else:
+            self._turn = (self._turn + 1) % 4
+            self._staged[self._turn][1].synchronize()
+        return self._staged[self._turn][0]
+
     @property
     def n_free_pages(self) -> int:
         return len(self._free)
@@ -113,9 +125,19 @@ class PagedKVGroup(CacheGroup):
     def upload(self) -> None:
         """Copy the rows of the page table that changed to the device, and clear the unwritten ends of
         pages that were handed out since the last step."""
-        for slot in sorted(self._dirty):
-            self.table_dev[slot].copy_(torch.from_numpy(self.table[slot]), non_blocking=False)
-        self._dirty.clear()
+        if self._dirty:
+            lo, hi = min(self._dirty), max(self._dirty) + 1
+            if self.table_dev.is_cuda:
+                # Through a snapshot in pinned memory, so that the copy neither makes the host wait nor reads rows
+                # that the host changes afterwards (a step queued ahead may still be waiting for it when a finished
+                # sequence's row is wiped).  Rows between the changed ones are the same on both sides already.
+                stage = self._snapshot()
+                stage[lo:hi].copy_(torch.from_numpy(self.table[lo:hi]))
+                self.table_dev[lo:hi].copy_(stage[lo:hi], non_blocking=True)
+                self._staged[self._turn][1].record()
+            else:
+                self.table_dev[lo:hi].copy_(torch.from_numpy(self.table[lo:hi]))
+            self._dirty.clear()
         if self._to_clear:
             todo, self._to_clear = self._to_clear, []
             if self.k_pages.is_cuda:
