@@ -250,7 +250,9 @@ def other_workload(torch, np, peaks, name, cfg, prompt_lengths, n_steps, params,
     if device_steps:
         # The same decode steps without the host in the loop (tokens drawn beforehand, nothing read back): what is
         # left of a step when the host costs nothing.  1 - device / end-to-end is the host's share of a step.
-        ms, _, _, _ = decode_run(torch, engine, rng, V, B, device_steps, 8, prompt_lengths[0], params, settle=E2E_WARM)
+        # (at the same mean context as the steps above: the prompt is as much longer as those steps are more)
+        start = max(1, int(mean_ctx - E2E_WARM - 8 - device_steps / 2.0))
+        ms, _, _, _ = decode_run(torch, engine, rng, V, B, device_steps, 8, start, params, settle=E2E_WARM)
         out[f"{name}_device_ms_per_step"] = ms / device_steps
         out[f"{name}_host_share"] = max(0.0, 1.0 - (ms / device_steps) / ms_step)
     engine.close()
