@@ -37,6 +37,12 @@ UNUSUAL = {
     # an even head size that is no multiple of 8: rotation pairs that no 16-byte access covers
     "head 26": dict(hidden_size=104, num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=1, head_dim=26,
                     intermediate_size=120, vocab_size=300, tie_word_embeddings=True),
+    # three heads to a kv head (as the 3B shape has): the tensor-core prompt attention takes one head per block,
+    # where an even group shares a block between two heads
+    "group of 3, head 128": dict(hidden_size=256, num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=1,
+                                 head_dim=128, intermediate_size=352, vocab_size=640),
+    "group of 3, head 64": dict(hidden_size=192, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2,
+                                head_dim=64, intermediate_size=264, vocab_size=512, sliding_window=100),
     # a head size above 128: the plain attention kernel
     "head 160": dict(hidden_size=320, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1, head_dim=160,
                      intermediate_size=520, vocab_size=777, tie_word_embeddings=True),
@@ -47,7 +53,7 @@ UNUSUAL = {
 @pytest.mark.parametrize("case", sorted(UNUSUAL))
 def test_sizes_that_the_fast_kernels_do_not_take(tmp_path, case, dtype):
     """Whole and with the last tokens one by one: every size the configuration allows gives the right
-    result, through whichever kernel takes it."""
+    result, through whichever kernel takes it (also sizes that take another variant of a fast kernel)."""
     from longbow_quarrel_b200.engine import Engine
     overrides = {"max_position_embeddings": 512, **UNUSUAL[case]}
     folder = make_model_folder(tmp_path, "A", seed=4, overrides=overrides)
